@@ -1,0 +1,96 @@
+"""ctypes binding of libhtree_b200.so (the C ABI declared in include/htree_b200.h).
+
+There is no CPU or PyTorch fallback: if the library has not been built, loading raises with the build command.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libhtree_b200.so")
+
+MAX_LEVELS = 12
+F32, BF16, F16 = 0, 1, 2
+FWD_SELECT_ONLY = 1
+FWD_GENERIC = 2
+
+# every exported symbol of include/htree_b200.h; tests check that the library exports all of them
+SYMBOLS = (
+    "htree_b200_version",
+    "htree_b200_error_string",
+    "htree_b200_num_levels",
+    "htree_b200_level_sizes",
+    "htree_b200_build_tree",
+    "htree_b200_forward",
+    "htree_b200_backward",
+)
+
+
+class HtreeShape(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_int32) for n in
+                ("B", "T", "H", "H_kv", "K", "V", "compression_rate", "top_k", "max_top_nodes", "dtype")]
+
+
+class HtreeTrace(ctypes.Structure):
+    _fields_ = [("layer_max", ctypes.c_void_p), ("layer_sum", ctypes.c_void_p), ("layer_out", ctypes.c_void_p)]
+
+
+class HtreeError(RuntimeError):
+    def __init__(self, code: int, what: str):
+        super().__init__(f"htree_b200 {what} failed with code {code}: {error_string(code)}")
+        self.code = code
+
+
+_lib = None
+
+
+def lib() -> ctypes.CDLL:
+    """Load the shared library once.  Raises if it is missing: the CUDA extension is the only implementation."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -m htree_b200.build` (nvcc, sm_100a). "
+                "htree_b200 has no fallback implementation.")
+        L = ctypes.CDLL(LIB_PATH)
+        vp, i32, u32, f32 = ctypes.c_void_p, ctypes.c_int32, ctypes.c_uint32, ctypes.c_float
+        L.htree_b200_version.restype = ctypes.c_int
+        L.htree_b200_error_string.restype = ctypes.c_char_p
+        L.htree_b200_error_string.argtypes = [ctypes.c_int]
+        L.htree_b200_num_levels.restype = ctypes.c_int
+        L.htree_b200_num_levels.argtypes = [i32, i32, i32]
+        L.htree_b200_level_sizes.restype = ctypes.c_int
+        L.htree_b200_level_sizes.argtypes = [i32, i32, i32, ctypes.POINTER(i32), i32]
+        L.htree_b200_build_tree.restype = ctypes.c_int
+        L.htree_b200_build_tree.argtypes = [ctypes.POINTER(HtreeShape), vp, vp, vp]
+        L.htree_b200_forward.restype = ctypes.c_int
+        L.htree_b200_forward.argtypes = [ctypes.POINTER(HtreeShape), vp, vp, vp, vp, vp, i32, f32, vp, vp, vp, vp,
+                                         ctypes.POINTER(HtreeTrace), vp, u32, vp]
+        L.htree_b200_backward.restype = ctypes.c_int
+        L.htree_b200_backward.argtypes = [ctypes.POINTER(HtreeShape), vp, vp, vp, vp, vp, i32, f32, vp, vp, vp, vp, vp,
+                                          vp, vp, vp, vp, u32, vp]
+        _lib = L
+    return _lib
+
+
+def error_string(code: int) -> str:
+    return lib().htree_b200_error_string(int(code)).decode()
+
+
+def check(code: int, what: str) -> None:
+    if code != 0:
+        raise HtreeError(code, what)
+
+
+def level_sizes(T: int, compression_rate: int, max_top_nodes: int):
+    buf = (ctypes.c_int32 * MAX_LEVELS)()
+    n = lib().htree_b200_level_sizes(int(T), int(compression_rate), int(max_top_nodes), buf, MAX_LEVELS)
+    if n < 0:
+        raise HtreeError(n, "level_sizes")
+    return [int(buf[i]) for i in range(n)]
+
+
+def ptr_array(ptrs):
+    """A C array of void* from a list of integer addresses (None -> NULL)."""
+    return (ctypes.c_void_p * len(ptrs))(*[ctypes.c_void_p(p) if p else None for p in ptrs])

@@ -1,0 +1,165 @@
+// extern "C" boundary of libhtree_b200: argument validation, parameter blocks, kernel dispatch.
+#include <cstring>
+
+#include "common.cuh"
+
+namespace htree {
+
+static int esize(int dtype) { return dtype == HTREE_F32 ? 4 : 2; }
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+static int level_sizes(int T, int CR, int MTN, int32_t* ln) {
+    if (T <= 0 || CR < 2 || MTN < 1) return HTREE_E_SHAPE;
+    int L = 1, n = T;
+    ln[0] = T;
+    while (n > MTN) {
+        n = (n + CR - 1) / CR;
+        if (L >= HTREE_MAX_LEVELS) return HTREE_E_LEVELS;
+        ln[L++] = n;
+    }
+    return L;
+}
+
+static int check_shape(const HtreeShape* s, int32_t* ln, bool check_top = true) {
+    if (!s) return HTREE_E_NULL;
+    if (s->B <= 0 || s->T <= 0 || s->H <= 0 || s->H_kv <= 0 || s->K <= 0 || s->V <= 0 || s->top_k <= 0) return HTREE_E_SHAPE;
+    if (s->H % s->H_kv != 0 || (s->K & 1)) return HTREE_E_SHAPE;
+    if (s->dtype != HTREE_F32 && s->dtype != HTREE_BF16 && s->dtype != HTREE_F16) return HTREE_E_DTYPE;
+    if ((int64_t)s->B * s->H_kv > 65535) return HTREE_E_UNSUPPORTED;
+    const int L = level_sizes(s->T, s->compression_rate, s->max_top_nodes, ln);
+    if (L < 0) return L;
+    if (check_top && (int64_t)ln[L - 1] > (int64_t)s->top_k * s->compression_rate) return HTREE_E_TOPLEVEL;
+    // 16-byte rows: K, V multiples of 8 keep every vector load of every kernel aligned for all storage types
+    if (s->K % 8 != 0 || s->V % 8 != 0) return HTREE_E_ALIGN;
+    return L;
+}
+
+static int fill_params(AttnParams& p, const HtreeShape* s, int L, const int32_t* ln, const void* q, void* const* lk,
+                       void* const* lv, const float* cosc, const float* sinc, int32_t n_pos, float scale,
+                       int32_t* const* parents, int32_t* status, uint32_t flags) {
+    std::memset(&p, 0, sizeof(p));
+    if (!q || !lk || !lv || !cosc || !sinc) return HTREE_E_NULL;
+    if ((int64_t)n_pos < (int64_t)s->top_k * s->compression_rate) return HTREE_E_ROPE;
+    if (!aligned16(q) || !aligned16(cosc) || !aligned16(sinc)) return HTREE_E_ALIGN;
+    p.q = q;
+    int64_t pw = 1;
+    for (int l = 0; l < L; ++l) {
+        if (!lk[l] || !lv[l]) return HTREE_E_NULL;
+        if (!aligned16(lk[l]) || !aligned16(lv[l])) return HTREE_E_ALIGN;
+        p.lk[l] = lk[l]; p.lv[l] = lv[l]; p.ln[l] = ln[l]; p.lpow[l] = pw;
+        p.parents[l] = parents ? parents[l] : nullptr;
+        pw *= s->compression_rate;
+    }
+    p.cosc = cosc; p.sinc = sinc; p.status = status;
+    p.B = s->B; p.T = s->T; p.H = s->H; p.Hkv = s->H_kv; p.K = s->K; p.V = s->V;
+    p.CR = s->compression_rate; p.TK = s->top_k; p.L = L; p.G = s->H / s->H_kv; p.n_pos = n_pos;
+    p.scale = scale; p.flags = flags;
+    return 0;
+}
+
+}  // namespace htree
+
+using namespace htree;
+
+extern "C" {
+
+int htree_b200_version(void) { return HTREE_B200_VERSION; }
+
+const char* htree_b200_error_string(int code) {
+    switch (code) {
+        case 0: return "success";
+        case HTREE_E_NULL: return "a required pointer is NULL";
+        case HTREE_E_SHAPE: return "invalid shape: sizes must be positive, H divisible by H_kv, K even";
+        case HTREE_E_DTYPE: return "unknown storage type";
+        case HTREE_E_LEVELS: return "too many tree levels";
+        case HTREE_E_TOPLEVEL: return "top tree level is longer than top_k*compression_rate";
+        case HTREE_E_ROPE: return "cos/sin tables have fewer than top_k*compression_rate rows";
+        case HTREE_E_ALIGN: return "pointers must be 16-byte aligned and K, V multiples of 8";
+        case HTREE_E_UNSUPPORTED: return "shape not supported by the compiled kernels";
+        case HTREE_E_NODEVICE: return "no usable CUDA device";
+        default: return code > 0 ? cudaGetErrorString((cudaError_t)code) : "unknown htree_b200 error";
+    }
+}
+
+int htree_b200_num_levels(int32_t T, int32_t CR, int32_t MTN) {
+    int32_t ln[HTREE_MAX_LEVELS];
+    return level_sizes(T, CR, MTN, ln);
+}
+
+int htree_b200_level_sizes(int32_t T, int32_t CR, int32_t MTN, int32_t* sizes, int32_t cap) {
+    int32_t ln[HTREE_MAX_LEVELS];
+    const int L = level_sizes(T, CR, MTN, ln);
+    if (L < 0) return L;
+    if (!sizes) return HTREE_E_NULL;
+    for (int l = 0; l < L && l < cap; ++l) sizes[l] = ln[l];
+    return L;
+}
+
+int htree_b200_build_tree(const HtreeShape* shape, void* const* layers_k, void* const* layers_v, void* stream) {
+    int32_t ln[HTREE_MAX_LEVELS];
+    const int L = check_shape(shape, ln, false);   // top_k plays no role in the tree
+    if (L < 0) return L;
+    if (!layers_k || !layers_v) return HTREE_E_NULL;
+    for (int l = 0; l < L; ++l) {
+        if (!layers_k[l] || !layers_v[l]) return HTREE_E_NULL;
+        if (!aligned16(layers_k[l]) || !aligned16(layers_v[l])) return HTREE_E_ALIGN;
+    }
+    const int es = esize(shape->dtype);
+    if ((shape->H_kv * shape->K * es) % 16 || (shape->H_kv * shape->V * es) % 16) return HTREE_E_ALIGN;
+    return launch_tree_build(*shape, L, ln, layers_k, layers_v, (cudaStream_t)stream);
+}
+
+int htree_b200_forward(const HtreeShape* shape, const void* q, void* const* layers_k, void* const* layers_v,
+                       const float* cos_cache, const float* sin_cache, int32_t n_pos, float scale, void* out,
+                       float* gmax, float* gsum, int32_t* const* parents, const HtreeTrace* trace, int32_t* status,
+                       uint32_t flags, void* stream) {
+    int32_t ln[HTREE_MAX_LEVELS];
+    const int L = check_shape(shape, ln);
+    if (L < 0) return L;
+    AttnParams p;
+    int rc = fill_params(p, shape, L, ln, q, layers_k, layers_v, cos_cache, sin_cache, n_pos, scale, parents, status, flags);
+    if (rc) return rc;
+    const bool select_only = (flags & HTREE_FWD_SELECT_ONLY) != 0;
+    if (select_only) {
+        if (!parents) return HTREE_E_NULL;
+    } else {
+        if (!out || !gmax || !gsum) return HTREE_E_NULL;
+        if (!aligned16(out)) return HTREE_E_ALIGN;
+    }
+    p.out = out; p.gmax = gmax; p.gsum = gsum;
+    if (trace) { p.tr_max = trace->layer_max; p.tr_sum = trace->layer_sum; p.tr_out = trace->layer_out; }
+    return launch_fwd_generic(p, shape->dtype, (cudaStream_t)stream);
+}
+
+int htree_b200_backward(const HtreeShape* shape, const void* q, void* const* layers_k, void* const* layers_v,
+                        const float* cos_cache, const float* sin_cache, int32_t n_pos, float scale, const void* out,
+                        const void* dO, const float* gmax, const float* gsum, int32_t* const* parents, float* dq,
+                        float* const* dk_levels, float* const* dv_levels, int32_t* status, uint32_t flags,
+                        void* stream) {
+    int32_t ln[HTREE_MAX_LEVELS];
+    const int L = check_shape(shape, ln);
+    if (L < 0) return L;
+    if (!out || !dO || !gmax || !gsum || !parents || !dq || !dk_levels || !dv_levels) return HTREE_E_NULL;
+    AttnParams p;
+    int rc = fill_params(p, shape, L, ln, q, layers_k, layers_v, cos_cache, sin_cache, n_pos, scale, parents, status, flags);
+    if (rc) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    for (int l = 0; l < L; ++l) {
+        if (!parents[l] || !dk_levels[l] || !dv_levels[l]) return HTREE_E_NULL;
+        if (!aligned16(dk_levels[l]) || !aligned16(dv_levels[l])) return HTREE_E_ALIGN;
+        p.dk[l] = dk_levels[l]; p.dv[l] = dv_levels[l];
+    }
+    for (int l = 0; l < L; ++l) {   // gradient accumulators start at zero (src/backward.py:979-981)
+        const size_t rows = (size_t)shape->B * ln[l] * shape->H_kv;
+        cudaError_t e = cudaMemsetAsync(dk_levels[l], 0, rows * shape->K * sizeof(float), st);
+        if (e == cudaSuccess) e = cudaMemsetAsync(dv_levels[l], 0, rows * shape->V * sizeof(float), st);
+        if (e != cudaSuccess) return (int)e;
+    }
+    p.out = const_cast<void*>(out); p.dO = dO; p.gmax = const_cast<float*>(gmax); p.gsum = const_cast<float*>(gsum);
+    p.dq = dq;
+    rc = launch_bwd_generic(p, shape->dtype, st);
+    if (rc) return rc;
+    return launch_tree_backward(*shape, L, ln, dk_levels, dv_levels, st);
+}
+
+}  // extern "C"

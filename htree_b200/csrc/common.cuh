@@ -1,0 +1,109 @@
+// Shared declarations of the htree_b200 kernels: parameter blocks, storage-type helpers, block primitives.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/htree_b200.h"
+
+namespace htree {
+
+constexpr float kNegInf = -1.0e10f;      // HTREE_SCORE_NEG_INF of the reference (src/parallel.py:75)
+constexpr float kHasMass = 1.0e-10f;     // "has contribution" guard of the level merge (src/parallel.py:289-314)
+constexpr float kForcedImportance = 1.0e6f;  // importance given to the right-most candidate (src/parallel.py:745)
+
+// Everything the attention kernels need, passed by value as a __grid_constant__ block.
+struct AttnParams {
+    const void* q;
+    const void* lk[HTREE_MAX_LEVELS];
+    const void* lv[HTREE_MAX_LEVELS];
+    int32_t ln[HTREE_MAX_LEVELS];   // N_l
+    int64_t lpow[HTREE_MAX_LEVELS]; // CR^l
+    const float* cosc;
+    const float* sinc;
+    int32_t* parents[HTREE_MAX_LEVELS];  // may be all NULL in the forward
+    int32_t* status;
+    // forward outputs
+    void* out;
+    float* gmax;
+    float* gsum;
+    float* tr_max;
+    float* tr_sum;
+    float* tr_out;
+    // backward inputs / outputs
+    const void* dO;
+    float* dq;
+    float* dk[HTREE_MAX_LEVELS];
+    float* dv[HTREE_MAX_LEVELS];
+    int32_t B, T, H, Hkv, K, V, CR, TK, L, G, n_pos;
+    float scale;
+    uint32_t flags;
+};
+
+template <typename T> __device__ __forceinline__ float to_f(T x);
+template <> __device__ __forceinline__ float to_f<float>(float x) { return x; }
+template <> __device__ __forceinline__ float to_f<__nv_bfloat16>(__nv_bfloat16 x) { return __bfloat162float(x); }
+template <> __device__ __forceinline__ float to_f<__half>(__half x) { return __half2float(x); }
+
+template <typename T> __device__ __forceinline__ T from_f(float x);
+template <> __device__ __forceinline__ float from_f<float>(float x) { return x; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
+template <> __device__ __forceinline__ __half from_f<__half>(float x) { return __float2half_rn(x); }
+
+// Four consecutive elements as floats with one vector load (pointer must be aligned to 4 elements).
+template <typename T> __device__ __forceinline__ void load4(const T* p, float (&o)[4]);
+template <> __device__ __forceinline__ void load4<float>(const float* p, float (&o)[4]) {
+    float4 x = __ldg(reinterpret_cast<const float4*>(p));
+    o[0] = x.x; o[1] = x.y; o[2] = x.z; o[3] = x.w;
+}
+template <> __device__ __forceinline__ void load4<__nv_bfloat16>(const __nv_bfloat16* p, float (&o)[4]) {
+    uint2 x = __ldg(reinterpret_cast<const uint2*>(p));
+    o[0] = __uint_as_float(x.x << 16); o[1] = __uint_as_float(x.x & 0xffff0000u);
+    o[2] = __uint_as_float(x.y << 16); o[3] = __uint_as_float(x.y & 0xffff0000u);
+}
+template <> __device__ __forceinline__ void load4<__half>(const __half* p, float (&o)[4]) {
+    uint2 x = __ldg(reinterpret_cast<const uint2*>(p));
+    float2 a = __half22float2(*reinterpret_cast<__half2*>(&x.x));
+    float2 b = __half22float2(*reinterpret_cast<__half2*>(&x.y));
+    o[0] = a.x; o[1] = a.y; o[2] = b.x; o[3] = b.y;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// Exclusive scan of one flag per thread over the block, in thread order.  `wtot` is shared scratch of NT/32 ints.
+// Returns the number of set flags in lower threads; *total receives the block total.  Two barriers.
+template <int NT>
+__device__ __forceinline__ int block_scan_flag(bool f, int* wtot, int* total) {
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    unsigned m = __ballot_sync(0xffffffffu, f);
+    if (lane == 0) wtot[w] = __popc(m);
+    __syncthreads();
+    int before = 0, tot = 0;
+#pragma unroll
+    for (int i = 0; i < NT / 32; ++i) {
+        int c = wtot[i];
+        if (i < w) before += c;
+        tot += c;
+    }
+    __syncthreads();
+    *total = tot;
+    return before + __popc(m & ((1u << lane) - 1u));
+}
+
+// launchers implemented in the .cu files (return cudaError_t as int)
+int launch_tree_build(const HtreeShape& s, int L, const int32_t* ln, void* const* lk, void* const* lv, cudaStream_t st);
+int launch_tree_backward(const HtreeShape& s, int L, const int32_t* ln, float* const* dk, float* const* dv, cudaStream_t st);
+int launch_fwd_generic(const AttnParams& p, int dtype, cudaStream_t st);
+int launch_bwd_generic(const AttnParams& p, int dtype, cudaStream_t st);
+
+}  // namespace htree

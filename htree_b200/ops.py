@@ -1,0 +1,292 @@
+"""Host side of the htree operator: the reference's Python entry points over the C ABI of libhtree_b200.
+
+Same names, keyword arguments, tensor layouts and return values as the reference (skywong14/htree):
+    htree_forward                  src/parallel.py:874-1159
+    htree_backward                 src/backward.py:941-1119
+    HTreeTritonFunction            src/backward.py:1126-1193   (alias of HTreeFunction here)
+    htree_forward_triton_autograd  src/backward.py:1196-1208
+    LayerTrace                     src/naive.py:13-19
+PyTorch supplies device memory and the current stream only; all arithmetic runs in the CUDA library.  There is no
+CPU path: tensors must live on a CUDA device and the library must have been built.
+
+Differences from the reference that callers can rely on:
+  * `max_top_nodes` may be smaller than `top_k_per_layer * compression_rate` (the reference asserts equality).  The
+    additional top levels then hold at most top_k nodes, every candidate is kept and nothing is accumulated there, so
+    the result equals the reference called with max_top_nodes = top_k_per_layer * compression_rate.
+  * sizes need not be powers of two, and top_k_per_layer need not be a multiple of 64 or of compression_rate.
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+from . import _lib
+
+HTREE_SCORE_NEG_INF: float = -1.0e10                                  # src/parallel.py:75
+HTREE_SCORE_VALID_THRESHOLD: float = HTREE_SCORE_NEG_INF * 0.9         # src/parallel.py:81
+
+_DTYPES = {torch.float32: _lib.F32, torch.bfloat16: _lib.BF16, torch.float16: _lib.F16}
+
+# Keep the per-level selections from the forward for the backward of the autograd function (True), or rebuild them
+# in the backward with the selection-only pass like the reference does (False; saves L*B*T*H_kv*top_k*4 bytes).
+SAVE_SELECTIONS_FOR_BACKWARD = True
+
+
+@dataclass
+class LayerTrace:
+    layer_idx: int
+    selected_parents: Optional[torch.Tensor]
+    layer_max: torch.Tensor
+    layer_sum: torch.Tensor
+    layer_output: torch.Tensor
+
+
+_rope_tables: Dict[Tuple, Tuple[torch.Tensor, torch.Tensor]] = {}
+_status_words: Dict[torch.device, torch.Tensor] = {}
+
+
+def rope_cache(k_dim: int, cache_size: int, rope_base: float, device) -> Tuple[torch.Tensor, torch.Tensor]:
+    """cos/sin tables [cache_size, k_dim/2] fp32 (src/parallel.py:983-988), built once per configuration.
+
+    The tables are evaluated with torch's CPU float32 kernels and copied to the device: the angle pos*inv_freq is
+    rounded to float32 before the cosine, so results only match the reference's CPU oracle bit for bit when
+    inv_freq comes out of the same pow implementation."""
+    key = (int(k_dim), int(cache_size), float(rope_base), torch.device(device))
+    hit = _rope_tables.get(key)
+    if hit is None:
+        inv_freq = 1.0 / (rope_base ** (torch.arange(0, k_dim, 2, dtype=torch.float32) / k_dim))
+        freqs = torch.outer(torch.arange(cache_size, dtype=torch.float32), inv_freq)
+        hit = (freqs.cos().to(device).contiguous(), freqs.sin().to(device).contiguous())
+        _rope_tables[key] = hit
+    return hit
+
+
+def _status(device) -> torch.Tensor:
+    device = torch.device(device)
+    w = _status_words.get(device)
+    if w is None:
+        w = torch.zeros(1, dtype=torch.int32, device=device)
+        _status_words[device] = w
+    return w
+
+
+def check_status(device=None) -> None:
+    """Synchronise and raise if a kernel flagged an out-of-range node index since the last check."""
+    device = torch.device(device if device is not None else torch.cuda.current_device())
+    if device.type == "cuda" and device.index is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    w = _status_words.get(device)
+    if w is not None:
+        v = int(w.item())
+        if v:
+            w.zero_()
+            raise RuntimeError(f"htree_b200 kernels reported device-side status 0x{v:x} (node index out of range)")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _validate(q, k, v, compression_rate, max_top_nodes, top_k_per_layer):
+    if q.dim() != 4 or k.dim() != 4 or v.dim() != 4:
+        raise ValueError("q/k/v must be rank-4 tensors")          # src/naive.py:141-142
+    if not (q.is_cuda and k.is_cuda and v.is_cuda):
+        raise RuntimeError("htree_b200 runs on CUDA tensors only; there is no CPU implementation")
+    B, T, H, K = q.shape
+    H_kv, V = k.shape[2], v.shape[-1]
+    assert H % H_kv == 0, f"H ({H}) must be divisible by H_kv ({H_kv})"                      # src/parallel.py:912
+    assert k.shape[2] == v.shape[2], "K and V must have same number of heads"                # src/parallel.py:914
+    assert tuple(k.shape[:2]) == (B, T) and tuple(v.shape[:2]) == (B, T) and k.shape[3] == K  # src/naive.py:146
+    assert q.dtype == k.dtype == v.dtype and q.dtype in _DTYPES, "q, k, v must share one of fp32/bf16/fp16"
+    assert max_top_nodes <= top_k_per_layer * compression_rate, (
+        f"max_top_nodes ({max_top_nodes}) must not exceed top_k_per_layer*compression_rate "
+        f"({top_k_per_layer}*{compression_rate})")                                            # cf. src/parallel.py:917-920
+    return _lib.HtreeShape(B, T, H, H_kv, K, V, int(compression_rate), int(top_k_per_layer), int(max_top_nodes),
+                           _DTYPES[q.dtype])
+
+
+def _ptrs(tensors) -> ctypes.Array:
+    return _lib.ptr_array([t.data_ptr() if t is not None else None for t in tensors])
+
+
+def build_tree(k: torch.Tensor, v: torch.Tensor, compression_rate: int, max_top_nodes: int):
+    """Mean-pool tree (src/parallel.py:941-976).  Returns (layers_k, layers_v); level 0 are k and v themselves."""
+    k = k.contiguous(); v = v.contiguous()
+    B, T, H_kv, K = k.shape
+    V = v.shape[-1]
+    sizes = _lib.level_sizes(T, compression_rate, max_top_nodes)
+    layers_k, layers_v = [k], [v]
+    for n in sizes[1:]:
+        layers_k.append(torch.empty(B, n, H_kv, K, dtype=k.dtype, device=k.device))
+        layers_v.append(torch.empty(B, n, H_kv, V, dtype=v.dtype, device=v.device))
+    if len(sizes) > 1:
+        shape = _lib.HtreeShape(B, T, H_kv, H_kv, K, V, int(compression_rate), 1, int(max_top_nodes),
+                                _DTYPES[k.dtype])   # H and top_k play no role in the tree
+        with torch.cuda.device(k.device):
+            _lib.check(_lib.lib().htree_b200_build_tree(ctypes.byref(shape), _ptrs(layers_k), _ptrs(layers_v),
+                                                        _stream()), "build_tree")
+    return layers_k, layers_v
+
+
+def _run_forward(shape, q, layers_k, layers_v, cos_cache, sin_cache, scale, out, gmax, gsum, parents, trace, flags):
+    with torch.cuda.device(q.device):
+        rc = _lib.lib().htree_b200_forward(
+            ctypes.byref(shape), q.data_ptr(), _ptrs(layers_k), _ptrs(layers_v), cos_cache.data_ptr(),
+            sin_cache.data_ptr(), cos_cache.shape[0], float(scale),
+            out.data_ptr() if out is not None else None, gmax.data_ptr() if gmax is not None else None,
+            gsum.data_ptr() if gsum is not None else None, _ptrs(parents) if parents is not None else None,
+            ctypes.byref(trace) if trace is not None else None, _status(q.device).data_ptr(), flags, _stream())
+    _lib.check(rc, "forward")
+
+
+def htree_forward(
+    q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
+    compression_rate: int = 16, max_top_nodes: int = 8192, top_k_per_layer: int = 512,
+    scale: Optional[float] = None, rope_base: float = 10000.0,
+    _save_for_backward: bool = False, _save_parents: bool = True,
+    return_trace: bool = False, _force_generic: bool = False,
+):
+    """htree forward.  q [B,T,H,K], k [B,T,H_kv,K], v [B,T,H_kv,V] -> out [B,T,H,V] in q's dtype.
+
+    Returns `out`, or `(out, bwd_ctx)` with `_save_for_backward` (the reference's contract, src/parallel.py:1139-1159),
+    with a third element — {"num_layers", "num_groups", "layers": {l: LayerTrace}} — when `return_trace` is set
+    (the shape of htree_forward_naive's trace, src/naive.py:225-234)."""
+    shape = _validate(q, k, v, compression_rate, max_top_nodes, top_k_per_layer)
+    B, T, H, K = q.shape
+    H_kv, V = k.shape[2], v.shape[-1]
+    if scale is None:
+        scale = K ** -0.5
+    q = q.contiguous(); k = k.contiguous(); v = v.contiguous()
+    dev = q.device
+    layers_k, layers_v = build_tree(k, v, compression_rate, max_top_nodes)
+    L = len(layers_k)
+    cos_cache, sin_cache = rope_cache(K, top_k_per_layer * compression_rate + 1024, rope_base, dev)
+    out = torch.empty(B, T, H, V, dtype=q.dtype, device=dev)
+    gmax = torch.empty(B, T, H, dtype=torch.float32, device=dev)
+    gsum = torch.empty(B, T, H, dtype=torch.float32, device=dev)
+    want_parents = (_save_for_backward and _save_parents) or return_trace
+    parents = [torch.empty(B, T, H_kv, top_k_per_layer, dtype=torch.int32, device=dev) for _ in range(L)] \
+        if want_parents else None
+    trace = tr = None
+    if return_trace:
+        tr = (torch.empty(L, B, T, H, dtype=torch.float32, device=dev),
+              torch.empty(L, B, T, H, dtype=torch.float32, device=dev),
+              torch.empty(L, B, T, H, V, dtype=torch.float32, device=dev))
+        trace = _lib.HtreeTrace(tr[0].data_ptr(), tr[1].data_ptr(), tr[2].data_ptr())
+    flags = _lib.FWD_GENERIC if (_force_generic or return_trace) else 0
+    _run_forward(shape, q, layers_k, layers_v, cos_cache, sin_cache, scale, out, gmax, gsum, parents, trace, flags)
+    if not (_save_for_backward or return_trace):
+        return out
+    result = [out]
+    if _save_for_backward:
+        G = H // H_kv
+        result.append(dict(
+            global_max=gmax, global_sum=gsum,
+            per_layer_parents={l: parents[l] for l in range(L)} if (_save_parents and parents is not None) else None,
+            layers_k=layers_k, layers_v=layers_v, cos_cache=cos_cache, sin_cache=sin_cache, num_layers=L,
+            compression_rate=compression_rate, top_k_per_layer=top_k_per_layer, max_top_nodes=max_top_nodes,
+            scale=scale, NUM_GROUPS=G,
+            # tuning constants of the reference's Triton kernels; kept so that code reading them keeps working
+            G_PAD=max(16, 1 << (G - 1).bit_length()), TILE_P=4, DROP_BLOCK=64,
+        ))
+    if return_trace:
+        check_status(dev)
+        layers = {l: LayerTrace(l, parents[l - 1] if l > 0 else None, tr[0][l], tr[1][l], tr[2][l]) for l in range(L)}
+        result.append({"num_layers": L, "num_groups": H // H_kv, "selection_mode": "parallel_importance",
+                       "layers": layers})
+    return tuple(result)
+
+
+def recompute_parents(q, layers_k, layers_v, cos_cache, sin_cache, compression_rate, top_k_per_layer,
+                      max_top_nodes, scale) -> Dict[int, torch.Tensor]:
+    """Selection-only replay of the forward (the reference's _recompute_parents, src/backward.py:881-934)."""
+    B, T, H, K = q.shape
+    H_kv, V = layers_k[0].shape[2], layers_v[0].shape[-1]
+    shape = _lib.HtreeShape(B, T, H, H_kv, K, V, int(compression_rate), int(top_k_per_layer), int(max_top_nodes),
+                            _DTYPES[q.dtype])
+    L = len(layers_k)
+    parents = [torch.empty(B, T, H_kv, top_k_per_layer, dtype=torch.int32, device=q.device) for _ in range(L)]
+    _run_forward(shape, q.contiguous(), layers_k, layers_v, cos_cache, sin_cache, scale, None, None, None, parents,
+                 None, _lib.FWD_SELECT_ONLY)
+    return {l: parents[l] for l in range(L)}
+
+
+def htree_backward(dO: torch.Tensor, q: torch.Tensor, output: torch.Tensor, bwd_ctx: dict):
+    """Backward given the forward context; returns fp32 (dq, dk, dv) with the shapes of q, k, v
+    (src/backward.py:941-1119).  If bwd_ctx['per_layer_parents'] is None the selections are rebuilt first."""
+    B, T, H, K = q.shape
+    layers_k, layers_v = bwd_ctx["layers_k"], bwd_ctx["layers_v"]
+    H_kv, V = layers_k[0].shape[2], layers_v[0].shape[-1]
+    L = bwd_ctx["num_layers"]
+    CR, TK, MTN = bwd_ctx["compression_rate"], bwd_ctx["top_k_per_layer"], bwd_ctx["max_top_nodes"]
+    scale = bwd_ctx["scale"]
+    cos_cache, sin_cache = bwd_ctx["cos_cache"], bwd_ctx["sin_cache"]
+    dev = q.device
+    q = q.contiguous()
+    dO = dO.contiguous().to(q.dtype)
+    output = output.contiguous()
+    parents = bwd_ctx.get("per_layer_parents")
+    if parents is None:
+        parents = recompute_parents(q, layers_k, layers_v, cos_cache, sin_cache, CR, TK, MTN, scale)
+    shape = _lib.HtreeShape(B, T, H, H_kv, K, V, int(CR), int(TK), int(MTN), _DTYPES[q.dtype])
+    dq = torch.empty(B, T, H, K, dtype=torch.float32, device=dev)
+    dk_levels = [torch.empty(x.shape, dtype=torch.float32, device=dev) for x in layers_k]
+    dv_levels = [torch.empty(x.shape, dtype=torch.float32, device=dev) for x in layers_v]
+    with torch.cuda.device(dev):
+        rc = _lib.lib().htree_b200_backward(
+            ctypes.byref(shape), q.data_ptr(), _ptrs(layers_k), _ptrs(layers_v), cos_cache.data_ptr(),
+            sin_cache.data_ptr(), cos_cache.shape[0], float(scale), output.data_ptr(), dO.data_ptr(),
+            bwd_ctx["global_max"].data_ptr(), bwd_ctx["global_sum"].data_ptr(),
+            _ptrs([parents[l] for l in range(L)]), dq.data_ptr(), _ptrs(dk_levels), _ptrs(dv_levels),
+            _status(dev).data_ptr(), 0, _stream())
+    _lib.check(rc, "backward")
+    return dq, dk_levels[0], dv_levels[0]
+
+
+class HTreeFunction(torch.autograd.Function):
+    """Differentiable htree attention (the reference's HTreeTritonFunction, src/backward.py:1126-1193)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, compression_rate, max_top_nodes, top_k_per_layer, scale, rope_base):
+        save = SAVE_SELECTIONS_FOR_BACKWARD
+        output, bwd_ctx = htree_forward(q, k, v, compression_rate=compression_rate, max_top_nodes=max_top_nodes,
+                                        top_k_per_layer=top_k_per_layer, scale=scale, rope_base=rope_base,
+                                        _save_for_backward=True, _save_parents=save)
+        ctx.save_for_backward(q, k, v, output, bwd_ctx["global_max"], bwd_ctx["global_sum"])
+        ctx.bwd_ctx = bwd_ctx
+        if not save:   # like the reference: drop the pooled levels and rebuild them in backward
+            bwd_ctx["layers_k"] = bwd_ctx["layers_v"] = None
+        return output
+
+    @staticmethod
+    def backward(ctx, dO):
+        q, k, v, output, gmax, gsum = ctx.saved_tensors
+        c = dict(ctx.bwd_ctx)
+        if c["layers_k"] is None:
+            c["layers_k"], c["layers_v"] = build_tree(k, v, c["compression_rate"], c["max_top_nodes"])
+        dq, dk, dv = htree_backward(dO, q, output, c)
+        return dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype), None, None, None, None, None
+
+
+HTreeTritonFunction = HTreeFunction   # drop-in name of the reference
+
+
+def htree_forward_autograd(q, k, v, compression_rate: int = 16, max_top_nodes: int = 8192,
+                           top_k_per_layer: int = 512, scale: Optional[float] = None, rope_base: float = 10000.0):
+    """Differentiable forward (signature of htree_forward_triton_autograd, src/backward.py:1196-1208)."""
+    if scale is None:
+        scale = q.shape[-1] ** -0.5
+    return HTreeFunction.apply(q.contiguous(), k.contiguous(), v.contiguous(), compression_rate, max_top_nodes,
+                               top_k_per_layer, scale, rope_base)
+
+
+htree_forward_triton_autograd = htree_forward_autograd   # drop-in name of the reference
+
+__all__ = [
+    "HTREE_SCORE_NEG_INF", "HTREE_SCORE_VALID_THRESHOLD", "LayerTrace", "build_tree", "rope_cache",
+    "htree_forward", "htree_backward", "recompute_parents", "HTreeFunction", "HTreeTritonFunction",
+    "htree_forward_autograd", "htree_forward_triton_autograd", "check_status",
+]

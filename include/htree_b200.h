@@ -1,0 +1,114 @@
+/*
+ * htree_b200 — C ABI of the sm_100a implementation of htree hierarchical tree sparse attention.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream handle; no entry point below allocates
+ * memory or keeps state between calls, work is enqueued asynchronously on `stream` of the current device, and any
+ * host thread may call.  Return value: 0 on success, a negative HTREE_E_* code when an argument is rejected before
+ * anything is launched, or a positive cudaError_t reported by a launch.  htree_b200_error_string() explains both.
+ *
+ * Tensor layouts are the reference's (skywong14/htree, src/parallel.py:874-905):
+ *     q   [B, T, H,    K]      k  [B, T, H_kv, K]      v  [B, T, H_kv, V]      out [B, T, H, V]
+ * all contiguous, all of one storage type `dtype`.  Tree level l (l = 0 are the leaves k, v themselves) holds
+ *     layers_k[l] [B, N_l, H_kv, K],  layers_v[l] [B, N_l, H_kv, V],   N_0 = T, N_{l+1} = ceil(N_l / CR)
+ * and pooling stops at the first level with N_l <= max_top_nodes (src/parallel.py:941-945).
+ */
+#ifndef HTREE_B200_H
+#define HTREE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define HTREE_B200_VERSION 1
+#define HTREE_MAX_LEVELS 12
+
+/* storage types */
+#define HTREE_F32 0
+#define HTREE_BF16 1
+#define HTREE_F16 2
+
+/* error codes (negative) */
+#define HTREE_E_NULL (-1)        /* a required pointer is NULL */
+#define HTREE_E_SHAPE (-2)       /* a size is non-positive, H % H_kv != 0, or K is odd */
+#define HTREE_E_DTYPE (-3)       /* unknown storage type */
+#define HTREE_E_LEVELS (-4)      /* more than HTREE_MAX_LEVELS levels, or level sizes inconsistent with T, CR */
+#define HTREE_E_TOPLEVEL (-5)    /* top level longer than top_k * compression_rate */
+#define HTREE_E_ROPE (-6)        /* cos/sin tables shorter than top_k * compression_rate rows */
+#define HTREE_E_ALIGN (-7)       /* a pointer or row size breaks the 16-byte alignment the kernels need */
+#define HTREE_E_UNSUPPORTED (-8) /* shape outside what the kernels were built for (e.g. shared memory need) */
+#define HTREE_E_NODEVICE (-9)    /* no CUDA device / wrong architecture */
+
+/* forward flags */
+#define HTREE_FWD_SELECT_ONLY 1u /* rebuild the selections only: no V reads, no accumulation, out/gmax/gsum untouched */
+#define HTREE_FWD_GENERIC 2u     /* force the dtype-generic fp32-arithmetic kernel even where a tensor-core kernel exists */
+
+/* Problem description shared by all entry points (mirrors the keyword arguments of htree_forward,
+ * src/parallel.py:874-885). */
+typedef struct HtreeShape {
+    int32_t B, T, H, H_kv, K, V;
+    int32_t compression_rate;
+    int32_t top_k;          /* top_k_per_layer */
+    int32_t max_top_nodes;  /* may be smaller than top_k*compression_rate; the reference asserts equality */
+    int32_t dtype;          /* HTREE_F32 / HTREE_BF16 / HTREE_F16 */
+} HtreeShape;
+
+/* Optional per-level accumulator dump, the reference's LayerTrace (src/naive.py:13-19; filled by the harness in
+ * correctness_test.py:168-347).  Arrays are indexed [level][...]: layer_max/layer_sum [L][B,T,H] fp32,
+ * layer_out [L][B,T,H,V] fp32 (un-normalised).  Any pointer may be NULL. */
+typedef struct HtreeTrace {
+    float* layer_max;
+    float* layer_sum;
+    float* layer_out;
+} HtreeTrace;
+
+int htree_b200_version(void);
+const char* htree_b200_error_string(int code);
+
+/* Number of tree levels for a sequence length, and their lengths N_l (level loop of src/parallel.py:941-945).
+ * htree_b200_level_sizes writes at most `cap` entries and returns the level count (or HTREE_E_LEVELS). */
+int htree_b200_num_levels(int32_t T, int32_t compression_rate, int32_t max_top_nodes);
+int htree_b200_level_sizes(int32_t T, int32_t compression_rate, int32_t max_top_nodes, int32_t* sizes, int32_t cap);
+
+/* Mean-pool tree build: replaces htree_build_kernel and its per-level launch loop (src/parallel.py:87-181, 955-976)
+ * and _recompute_tree_build (src/backward.py:848-878).  layers_k[0]/layers_v[0] are the inputs k, v; levels
+ * 1..L-1 are written (tail parents average only their valid children; fp32 accumulation, one rounding). */
+int htree_b200_build_tree(const HtreeShape* shape, void* const* layers_k, void* const* layers_v, void* stream);
+
+/* Fused forward over all levels: replaces the per-level launches of htree_select_accumulate_gqa_kernel,
+ * htree_bottom_accumulate_gqa_kernel, htree_merge_to_global_kernel and htree_final_normalize_kernel together with
+ * the host-side state and virtual-parent initialisation (src/parallel.py:995-1134), and — with
+ * HTREE_FWD_SELECT_ONLY — htree_recompute_selection_kernel / _recompute_parents (src/parallel.py:1167-1399,
+ * src/backward.py:881-934).
+ *   cos_cache, sin_cache  [n_pos, K/2] fp32 RoPE tables (src/parallel.py:983-988); n_pos >= top_k*compression_rate
+ *   out [B,T,H,V] in `dtype`; gmax, gsum [B,T,H] fp32 (global_max / global_sum of bwd_ctx)
+ *   parents  NULL, or L pointers: parents[l] [B,T,H_kv,top_k] int32 receives the parent list CONSUMED at level l,
+ *            ascending and -1 padded (per_layer_parents of bwd_ctx, src/parallel.py:1039-1044)
+ *   trace    NULL or per-level accumulator dumps
+ *   status   NULL or one int32 on the device, OR-ed with a non-zero code if a kernel met an out-of-range node index
+ */
+int htree_b200_forward(const HtreeShape* shape, const void* q, void* const* layers_k, void* const* layers_v,
+                       const float* cos_cache, const float* sin_cache, int32_t n_pos, float scale, void* out,
+                       float* gmax, float* gsum, int32_t* const* parents, const HtreeTrace* trace, int32_t* status,
+                       uint32_t flags, void* stream);
+
+/* Backward: replaces htree_backward and every kernel it launches (preprocess_delta, dq_bottom/upper,
+ * build_parent_mask, dkv_bottom/upper, tree_backward; src/backward.py:45-841, 941-1119).
+ *   out, dO [B,T,H,V] in `dtype`; gmax, gsum from the forward; parents[l] as written by the forward (required)
+ *   dq [B,T,H,K] fp32 (written)
+ *   dk_levels[l] [B,N_l,H_kv,K] fp32, dv_levels[l] [B,N_l,H_kv,V] fp32 for every level: zero-filled by this call,
+ *   accumulated, then folded top-down by the mean-pool gradient; level 0 holds dk, dv on return and levels >= 1 are
+ *   scratch (the reference's dk_layers / dv_layers, src/backward.py:979-981).
+ */
+int htree_b200_backward(const HtreeShape* shape, const void* q, void* const* layers_k, void* const* layers_v,
+                        const float* cos_cache, const float* sin_cache, int32_t n_pos, float scale, const void* out,
+                        const void* dO, const float* gmax, const float* gsum, int32_t* const* parents, float* dq,
+                        float* const* dk_levels, float* const* dv_levels, int32_t* status, uint32_t flags,
+                        void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HTREE_B200_H */

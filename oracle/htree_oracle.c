@@ -179,13 +179,16 @@ static int64_t ipow(int64_t b, int e) { int64_t r = 1; while (e-- > 0) r *= b; r
  *   tr_max,tr_sum [L,nq,G], tr_out [L,nq,G,V] or NULL: per-level accumulator state (LayerTrace, src/naive.py:13-19)
  *   gap       [L,nq] or NULL: relative gap (imp_TK - imp_{TK+1}) / imp_TK between the last kept and the first
  *             dropped importance at levels that drop something, else +inf.  Used to classify near-ties.
+ *   imp_out   [L,nq,TK*CR] or NULL: shared importance of every candidate position at the upper levels (right-most
+ *             forced to 1e6), -1 where there is no candidate and at the leaf level.
  * Returns 0, or -1 on allocation failure, -2 if a node index leaves its level, -3 if a position leaves the tables.
  */
 int ho_forward(const HoShape* sh, const float* q, const float* const* layers_k, const float* const* layers_v,
                const int32_t* level_n, const float* cosc, const float* sinc, const int32_t* queries, int64_t nq,
                float* out, float* gmax, float* gsum, int32_t* parents, float* tr_max, float* tr_sum, float* tr_out,
-               float* gap) {
+               float* gap, float* imp_out) {
     const int G = sh->H / sh->H_kv, K = sh->K, V = sh->V, CR = sh->CR, TK = sh->TK, L = sh->L, half = K / 2;
+    const int64_t maxc = (int64_t)TK * CR;
     int status = 0;
     #pragma omp parallel
     {
@@ -262,6 +265,10 @@ int ho_forward(const HoShape* sh, const float* q, const float* const* layers_k, 
                     for (; n < TK; ++n) w.npar[n] = -1;
                 }
                 if (gap) gap[(int64_t)l * nq + qi] = gapv;
+                if (imp_out) {
+                    float* io = imp_out + ((int64_t)l * nq + qi) * maxc;
+                    for (int64_t j = 0; j < maxc; ++j) io[j] = (l > 0 && j < nc) ? w.imp[j] : -1.f;
+                }
 
                 /* accumulate the unselected candidates (src/naive.py:73-85, 209-213) */
                 float lm[64], ls[64];

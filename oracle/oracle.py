@@ -119,13 +119,15 @@ def _ptr_array(arrs: Sequence[np.ndarray]):
 
 
 def forward(q, k, v, compression_rate=16, max_top_nodes=8192, top_k_per_layer=512, scale=None, rope_base=10000.0,
-            dtype="float32", queries=None, return_trace=False, layers=None, cache=None) -> Dict[str, np.ndarray]:
+            dtype="float32", queries=None, return_trace=False, layers=None, cache=None,
+            return_importance=False) -> Dict[str, np.ndarray]:
     """htree forward on the host.  Mirrors htree_forward_naive (src/naive.py:133-234).
 
     `max_top_nodes` may be smaller than top_k*compression_rate (the reference asserts equality; the extra top levels
     this creates select every candidate, so results equal the reference called with max_top_nodes = top_k*CR
     whenever both are defined).  `queries`: optional int32 [nq,3] array of (b, t, h_kv) groups; default all groups.
-    Returns dict: out [nq,G,V] (un-rounded), out_rounded, gmax, gsum [nq,G], parents [L,nq,TK], gap [L,nq] and,
+    Returns dict: out [nq,G,V] (un-rounded), out_rounded, gmax, gsum [nq,G], parents [L,nq,TK], gap [L,nq],
+    importance [L,nq,TK*CR] with return_importance, and,
     with return_trace, tr_max/tr_sum [L,nq,G], tr_out [L,nq,G,V].  With queries=None the arrays are reshaped to the
     reference layouts ([B,T,H,V] etc.).
     """
@@ -155,15 +157,18 @@ def forward(q, k, v, compression_rate=16, max_top_nodes=8192, top_k_per_layer=51
     if return_trace:
         tr_max = np.empty((L, nq, G), np.float32); tr_sum = np.empty((L, nq, G), np.float32)
         tr_out = np.empty((L, nq, G, V), np.float32)
+    imp = np.empty((L, nq, TK * CR), np.float32) if return_importance else None
     rc = lib.ho_forward(ctypes.byref(sh), _fp(q), _ptr_array(lk), _ptr_array(lv), _fp(level_n), _fp(cosc), _fp(sinc),
                         _fp(qarr), ctypes.c_int64(nq), _fp(out), _fp(gmax), _fp(gsum), _fp(parents), _fp(tr_max),
-                        _fp(tr_sum), _fp(tr_out), _fp(gap))
+                        _fp(tr_sum), _fp(tr_out), _fp(gap), _fp(imp))
     if rc != 0:
         raise RuntimeError(f"oracle forward failed with status {rc}")
     res = dict(out=out, out_rounded=round_storage(out, dtype), gmax=gmax, gsum=gsum, parents=parents, gap=gap,
                layers_k=lk, layers_v=lv, cos=cosc, sin=sinc, num_layers=L, scale=float(scale))
     if return_trace:
         res.update(tr_max=tr_max, tr_sum=tr_sum, tr_out=tr_out)
+    if return_importance:
+        res["importance"] = imp        # [L, nq, TK*CR], always indexed by flat group number
     if queries is None:
         res["out"] = out.reshape(B, T, H, V); res["out_rounded"] = res["out_rounded"].reshape(B, T, H, V)
         res["gmax"] = gmax.reshape(B, T, H); res["gsum"] = gsum.reshape(B, T, H)
