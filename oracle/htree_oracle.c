@@ -222,7 +222,7 @@ int ho_forward(const HoShape* sh, const float* q, const float* const* layers_k, 
                 np = 0; while (np < TK && w.par[np] >= 0) ++np;
                 int rci = (int)((t / ipow(CR, l)) % CR);
                 int nc = (np - 1) * CR + rci + 1, rp = nc - 1;
-                if (rp >= sh->n_pos) { status = -3; continue; }
+                if (nc < 1 || rp >= sh->n_pos) { status = -3; continue; }
                 /* rotated, scaled queries (src/naive.py:197-198) */
                 for (int g = 0; g < G; ++g) {
                     rope_fwd(qg + (int64_t)g * K, cosc + (int64_t)rp * half, sinc + (int64_t)rp * half, w.qr + g * K, K);
@@ -319,88 +319,138 @@ int ho_forward(const HoShape* sh, const float* q, const float* const* layers_k, 
 }
 
 /*
- * Backward for every group of the tensors (src/naive.py:333-386), selections taken as constants.
- *   out      [B,T,H,V] forward output AS STORED (already rounded to the input dtype), dO [B,T,H,V]
- *   gmax,gsum [B,T,H];  parents [L,B,T,H_kv,TK] consumed lists
- *   dq       [B,T,H,K] (written); dk_layers[l], dv_layers[l] (zero-filled by the caller, accumulated)
- * Parallel over (b,h_kv) units only, serial and in query order within a unit, so the float sums are deterministic.
- * The mean-pool gradient step is ho_tree_backward_level(), applied by the caller from the top level down.
+ * Backward for one group: adds into dk_layers/dv_layers (with atomics if `atomic`), writes dq [G,K].
+ * Per-group arrays (out, dO, gmax, gsum, dq) are addressed by the flat group index qi; for the full tensors
+ * [B,T,H,*] this is the same memory as [B*T*H_kv, G, *].
  */
-int ho_backward(const HoShape* sh, const float* q, const float* const* layers_k, const float* const* layers_v,
-                const int32_t* level_n, const float* cosc, const float* sinc, const float* out, const float* dO,
-                const float* gmax, const float* gsum, const int32_t* parents, float* dq, float* const* dk_layers,
-                float* const* dv_layers) {
+static int backward_group(const HoShape* sh, const float* q, const float* const* layers_k, const float* const* layers_v,
+                          const int32_t* level_n, const float* cosc, const float* sinc, const float* out,
+                          const float* dO, const float* gmax, const float* gsum, const int32_t* parents, int64_t nq,
+                          int64_t qi, int b, int t, int hk, float* dq, float* const* dk_layers, float* const* dv_layers,
+                          int atomic, float* qr, float* kr, float* dqr, float* dkr, float* tmp, float* Dg) {
     const int G = sh->H / sh->H_kv, K = sh->K, V = sh->V, CR = sh->CR, TK = sh->TK, L = sh->L, half = K / 2;
-    const int64_t nq = (int64_t)sh->B * sh->T * sh->H_kv;
     int status = 0;
-    #pragma omp parallel for collapse(2) schedule(dynamic, 1)
-    for (int b = 0; b < sh->B; ++b)
-        for (int hk = 0; hk < sh->H_kv; ++hk) {
-            float* qr = (float*)malloc(sizeof(float) * G * K);
-            float* kr = (float*)malloc(sizeof(float) * K);
-            float* dqr = (float*)malloc(sizeof(float) * G * K);
-            float* dkr = (float*)malloc(sizeof(float) * K);
-            float* tmp = (float*)malloc(sizeof(float) * K);
-            float* Dg = (float*)malloc(sizeof(float) * G);
-            for (int t = 0; t < sh->T; ++t) {
-                int64_t qi = ((int64_t)b * sh->T + t) * sh->H_kv + hk;
-                int64_t hbase = ((int64_t)b * sh->T + t) * sh->H + (int64_t)hk * G;
-                for (int g = 0; g < G; ++g) { /* D = sum_v dO * out (src/naive.py:333) */
-                    float s = 0.f;
-                    for (int d = 0; d < V; ++d) s += dO[(hbase + g) * V + d] * out[(hbase + g) * V + d];
-                    Dg[g] = s;
-                    for (int d = 0; d < K; ++d) dq[(hbase + g) * K + d] = 0.f;
-                }
-                for (int l = L - 1; l >= 0; --l) {
-                    const int Nl = level_n[l];
-                    const int32_t* par = parents + ((int64_t)l * nq + qi) * TK;
-                    const int32_t* nxt = l > 0 ? parents + ((int64_t)(l - 1) * nq + qi) * TK : NULL;
-                    int np = 0; while (np < TK && par[np] >= 0) ++np;
-                    if (np <= 0) continue;
-                    int rci = (int)((t / ipow(CR, l)) % CR);
-                    int nc = (np - 1) * CR + rci + 1, rp = nc - 1;
-                    const float* cq = cosc + (int64_t)rp * half; const float* sq = sinc + (int64_t)rp * half;
-                    for (int g = 0; g < G; ++g) {
-                        rope_fwd(q + (hbase + g) * K, cq, sq, qr + g * K, K);
-                        for (int d = 0; d < K; ++d) qr[g * K + d] *= sh->scale;
+    const float* qg = q + (((int64_t)b * sh->T + t) * sh->H + (int64_t)hk * G) * K;
+    const int64_t hb = qi * G;
+    for (int g = 0; g < G; ++g) { /* D = sum_v dO * out (src/naive.py:333) */
+        float s = 0.f;
+        for (int d = 0; d < V; ++d) s += dO[(hb + g) * V + d] * out[(hb + g) * V + d];
+        Dg[g] = s;
+        for (int d = 0; d < K; ++d) dq[(hb + g) * K + d] = 0.f;
+    }
+    for (int l = L - 1; l >= 0; --l) {
+        const int Nl = level_n[l];
+        const int32_t* par = parents + ((int64_t)l * nq + qi) * TK;
+        const int32_t* nxt = l > 0 ? parents + ((int64_t)(l - 1) * nq + qi) * TK : NULL;
+        int np = 0; while (np < TK && par[np] >= 0) ++np;
+        if (np <= 0) continue;
+        int rci = (int)((t / ipow(CR, l)) % CR);
+        int nc = (np - 1) * CR + rci + 1, rp = nc - 1;
+        const float* cq = cosc + (int64_t)rp * half; const float* sq = sinc + (int64_t)rp * half;
+        for (int g = 0; g < G; ++g) {
+            rope_fwd(qg + (int64_t)g * K, cq, sq, qr + g * K, K);
+            for (int d = 0; d < K; ++d) qr[g * K + d] *= sh->scale;
+        }
+        memset(dqr, 0, sizeof(float) * G * K);
+        int ns = 0; /* walk the (sorted) next-level selection in step with the (ascending) node ids */
+        for (int j = 0; j < nc; ++j) {
+            int node = par[j / CR] * CR + j % CR;
+            if (node < 0 || node >= Nl) { status = -2; continue; }
+            if (nxt) {
+                while (ns < TK && nxt[ns] >= 0 && nxt[ns] < node) ++ns;
+                if (ns < TK && nxt[ns] == node) continue; /* selected: expanded below, not accumulated */
+            }
+            const float* ck = cosc + (int64_t)j * half; const float* sk = sinc + (int64_t)j * half;
+            const float* kn = layers_k[l] + (((int64_t)b * Nl + node) * sh->H_kv + hk) * K;
+            const float* vn = layers_v[l] + (((int64_t)b * Nl + node) * sh->H_kv + hk) * V;
+            float* dkn = dk_layers[l] + (((int64_t)b * Nl + node) * sh->H_kv + hk) * K;
+            float* dvn = dv_layers[l] + (((int64_t)b * Nl + node) * sh->H_kv + hk) * V;
+            rope_fwd(kn, ck, sk, kr, K);
+            memset(dkr, 0, sizeof(float) * K);
+            for (int g = 0; g < G; ++g) {
+                float s = 0.f;
+                for (int d = 0; d < K; ++d) s += qr[g * K + d] * kr[d];
+                float P = expf(s - gmax[hb + g]) / gsum[hb + g];                 /* src/naive.py:379 */
+                float dP = 0.f;
+                for (int d = 0; d < V; ++d) dP += dO[(hb + g) * V + d] * vn[d];
+                float dS = P * (dP - Dg[g]);                                     /* src/naive.py:382 */
+                for (int d = 0; d < K; ++d) { dqr[g * K + d] += dS * kr[d]; dkr[d] += dS * qr[g * K + d]; }
+                if (atomic) {
+                    for (int d = 0; d < V; ++d) {
+                        float add = P * dO[(hb + g) * V + d];
+                        #pragma omp atomic
+                        dvn[d] += add;
                     }
-                    memset(dqr, 0, sizeof(float) * G * K);
-                    int ns = 0; /* walk the (sorted) next-level selection in step with the (ascending) node ids */
-                    for (int j = 0; j < nc; ++j) {
-                        int node = par[j / CR] * CR + j % CR;
-                        if (node < 0 || node >= Nl) { status = -2; continue; }
-                        if (nxt) {
-                            while (ns < TK && nxt[ns] >= 0 && nxt[ns] < node) ++ns;
-                            if (ns < TK && nxt[ns] == node) continue; /* selected: expanded below, not accumulated */
-                        }
-                        const float* ck = cosc + (int64_t)j * half; const float* sk = sinc + (int64_t)j * half;
-                        const float* kn = layers_k[l] + (((int64_t)b * Nl + node) * sh->H_kv + hk) * K;
-                        const float* vn = layers_v[l] + (((int64_t)b * Nl + node) * sh->H_kv + hk) * V;
-                        float* dkn = dk_layers[l] + (((int64_t)b * Nl + node) * sh->H_kv + hk) * K;
-                        float* dvn = dv_layers[l] + (((int64_t)b * Nl + node) * sh->H_kv + hk) * V;
-                        rope_fwd(kn, ck, sk, kr, K);
-                        memset(dkr, 0, sizeof(float) * K);
-                        for (int g = 0; g < G; ++g) {
-                            float s = 0.f;
-                            for (int d = 0; d < K; ++d) s += qr[g * K + d] * kr[d];
-                            float P = expf(s - gmax[hbase + g]) / gsum[hbase + g];       /* src/naive.py:379 */
-                            float dP = 0.f;
-                            for (int d = 0; d < V; ++d) dP += dO[(hbase + g) * V + d] * vn[d];
-                            float dS = P * (dP - Dg[g]);                                 /* src/naive.py:382 */
-                            for (int d = 0; d < K; ++d) { dqr[g * K + d] += dS * kr[d]; dkr[d] += dS * qr[g * K + d]; }
-                            for (int d = 0; d < V; ++d) dvn[d] += P * dO[(hbase + g) * V + d];
-                        }
-                        rope_inv(dkr, ck, sk, tmp, K);                                   /* src/naive.py:385 */
-                        for (int d = 0; d < K; ++d) dkn[d] += tmp[d];
-                    }
-                    for (int g = 0; g < G; ++g) {                                        /* src/naive.py:384 */
-                        rope_inv(dqr + g * K, cq, sq, tmp, K);
-                        for (int d = 0; d < K; ++d) dq[(hbase + g) * K + d] += sh->scale * tmp[d];
-                    }
+                } else {
+                    for (int d = 0; d < V; ++d) dvn[d] += P * dO[(hb + g) * V + d];
                 }
             }
-            free(qr); free(kr); free(dqr); free(dkr); free(tmp); free(Dg);
+            rope_inv(dkr, ck, sk, tmp, K);                                       /* src/naive.py:385 */
+            if (atomic) {
+                for (int d = 0; d < K; ++d) {
+                    #pragma omp atomic
+                    dkn[d] += tmp[d];
+                }
+            } else {
+                for (int d = 0; d < K; ++d) dkn[d] += tmp[d];
+            }
         }
+        for (int g = 0; g < G; ++g) {                                            /* src/naive.py:384 */
+            rope_inv(dqr + g * K, cq, sq, tmp, K);
+            for (int d = 0; d < K; ++d) dq[(hb + g) * K + d] += sh->scale * tmp[d];
+        }
+    }
+    return status;
+}
+
+/*
+ * Backward (src/naive.py:333-386), selections taken as constants.
+ *   queries NULL: every group of the tensors.  out (AS STORED, i.e. rounded to the input dtype), dO [B,T,H,V];
+ *     gmax, gsum [B,T,H]; parents [L,B,T,H_kv,TK]; dq [B,T,H,K].  Parallel over (b,h_kv) units only, serial and in
+ *     query order inside a unit, so the float sums are deterministic.
+ *   queries [nq,3] (b,t,h_kv): only those groups; out, dO [nq,G,V]; gmax, gsum [nq,G]; parents [L,nq,TK];
+ *     dq [nq,G,K].  Parallel over groups with atomic adds into dk/dv (summation order not deterministic); meant for
+ *     timing a bounded sample and for checking dq of sampled queries.
+ *   dk_layers[l], dv_layers[l]: zero-filled by the caller, accumulated here.  The mean-pool gradient step is
+ *   ho_tree_backward_level(), applied by the caller from the top level down.
+ */
+int ho_backward(const HoShape* sh, const float* q, const float* const* layers_k, const float* const* layers_v,
+                const int32_t* level_n, const float* cosc, const float* sinc, const int32_t* queries, int64_t nq_in,
+                const float* out, const float* dO, const float* gmax, const float* gsum, const int32_t* parents,
+                float* dq, float* const* dk_layers, float* const* dv_layers) {
+    const int G = sh->H / sh->H_kv, K = sh->K;
+    const int64_t nq = queries ? nq_in : (int64_t)sh->B * sh->T * sh->H_kv;
+    int status = 0;
+    #pragma omp parallel
+    {
+        float* qr = (float*)malloc(sizeof(float) * G * K);
+        float* kr = (float*)malloc(sizeof(float) * K);
+        float* dqr = (float*)malloc(sizeof(float) * G * K);
+        float* dkr = (float*)malloc(sizeof(float) * K);
+        float* tmp = (float*)malloc(sizeof(float) * K);
+        float* Dg = (float*)malloc(sizeof(float) * G);
+        if (queries) {
+            #pragma omp for schedule(dynamic, 4)
+            for (int64_t qi = 0; qi < nq; ++qi) {
+                int rc = backward_group(sh, q, layers_k, layers_v, level_n, cosc, sinc, out, dO, gmax, gsum, parents, nq,
+                                        qi, queries[3 * qi], queries[3 * qi + 1], queries[3 * qi + 2], dq, dk_layers,
+                                        dv_layers, 1, qr, kr, dqr, dkr, tmp, Dg);
+                if (rc) status = rc;
+            }
+        } else {
+            #pragma omp for collapse(2) schedule(dynamic, 1)
+            for (int b = 0; b < sh->B; ++b)
+                for (int hk = 0; hk < sh->H_kv; ++hk)
+                    for (int t = 0; t < sh->T; ++t) {
+                        int64_t qi = ((int64_t)b * sh->T + t) * sh->H_kv + hk;
+                        int rc = backward_group(sh, q, layers_k, layers_v, level_n, cosc, sinc, out, dO, gmax, gsum,
+                                                parents, nq, qi, b, t, hk, dq, dk_layers, dv_layers, 0, qr, kr, dqr,
+                                                dkr, tmp, Dg);
+                        if (rc) status = rc;
+                    }
+        }
+        free(qr); free(kr); free(dqr); free(dkr); free(tmp); free(Dg);
+    }
     return status;
 }
 

@@ -179,25 +179,38 @@ def forward(q, k, v, compression_rate=16, max_top_nodes=8192, top_k_per_layer=51
     return res
 
 
-def backward(q, fwd: Dict[str, np.ndarray], dO, compression_rate=16, top_k_per_layer=512, dtype="float32"):
-    """Analytical backward (src/naive.py:321-396) given a full-tensor forward() result.  Returns (dq, dk, dv)
-    rounded to `dtype` like the reference's autograd function, plus the un-rounded fp32 versions."""
+def backward(q, fwd: Dict[str, np.ndarray], dO, compression_rate=16, top_k_per_layer=512, dtype="float32",
+             queries=None):
+    """Analytical backward (src/naive.py:321-396) given a forward() result.
+
+    queries=None: `fwd` must be a full-tensor result; returns dq, dk, dv rounded to `dtype` like the reference's
+    autograd function, plus the un-rounded fp32 versions (dq_f32, ...).
+    queries [nq,3]: `fwd` must come from forward(queries=...) with the same list and dO is [nq,G,V]; returns dq_f32
+    [nq,G,K] for those groups and the partial dk_f32/dv_f32 they contribute (before the mean-pool step)."""
     lib = _load()
     q = _f32(q); dO = _f32(dO)
     B, T, H, K = q.shape
     lk, lv = fwd["layers_k"], fwd["layers_v"]
     Hkv, V, L = lk[0].shape[2], lv[0].shape[3], len(lk)
+    G = H // Hkv
     sh = _Shape(B, T, H, Hkv, K, V, int(compression_rate), int(top_k_per_layer), L, fwd["cos"].shape[0], fwd["scale"])
     level_n = np.array([a.shape[1] for a in lk], np.int32)
     out_st = _f32(fwd["out_rounded"])
-    dq = np.zeros_like(q)
     dks = [np.zeros_like(a) for a in lk]; dvs = [np.zeros_like(a) for a in lv]
     parents = np.ascontiguousarray(fwd["parents"], np.int32)
+    if queries is None:
+        qarr, nq = None, B * T * Hkv
+        dq = np.zeros_like(q)
+    else:
+        qarr = np.ascontiguousarray(queries, np.int32).reshape(-1, 3); nq = qarr.shape[0]
+        dq = np.zeros((nq, G, K), np.float32)
     rc = lib.ho_backward(ctypes.byref(sh), _fp(q), _ptr_array(lk), _ptr_array(lv), _fp(level_n), _fp(fwd["cos"]),
-                         _fp(fwd["sin"]), _fp(out_st), _fp(dO), _fp(_f32(fwd["gmax"])), _fp(_f32(fwd["gsum"])),
-                         _fp(parents), _fp(dq), _ptr_array(dks), _ptr_array(dvs))
+                         _fp(fwd["sin"]), _fp(qarr), ctypes.c_int64(nq), _fp(out_st), _fp(dO), _fp(_f32(fwd["gmax"])),
+                         _fp(_f32(fwd["gsum"])), _fp(parents), _fp(dq), _ptr_array(dks), _ptr_array(dvs))
     if rc != 0:
         raise RuntimeError(f"oracle backward failed with status {rc}")
+    if queries is not None:
+        return dict(dq_f32=dq, dk_levels=dks, dv_levels=dvs)
     for l in range(L - 1, 0, -1):
         n_child = lk[l - 1].shape[1]
         lib.ho_tree_backward_level(_fp(dks[l]), _fp(dks[l - 1]), B, n_child, Hkv, K, int(compression_rate))

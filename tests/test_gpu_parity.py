@@ -1,0 +1,227 @@
+"""GPU parity tests: the CUDA path, called through htree_b200.ops -> C ABI, against the golden fixtures made by the
+reference's naive path and against the CPU oracle on the same seeded inputs.
+
+Bar (stated per assertion): selections identical except documented near-ties; fp32 outputs/gradients within 1e-4
+relative; bf16/fp16 outputs within 2e-2 absolute."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle
+from tests import parity
+
+pytestmark = pytest.mark.gpu
+CASES = parity.golden_cases()
+DEV = "cuda"
+
+# near-tie window (relative importance distance to the Top-K boundary) by storage type, generic fp32-arithmetic kernel
+EPS_SEL = {"float32": 2e-5, "bfloat16": 2e-5, "float16": 2e-5}
+OUT_TOL = {"float32": None, "bfloat16": 2e-2, "float16": 2e-2}    # absolute; fp32 uses 1e-4 relative
+
+
+def _ops():
+    import htree_b200
+    return htree_b200
+
+
+def run_ours(c, q, k, v, trace=True, generic=True):
+    ops = _ops()
+    res = ops.htree_forward(q.to(DEV), k.to(DEV), v.to(DEV), c["CR"], c["MTN"], c["TK"], _save_for_backward=True,
+                            return_trace=trace, _force_generic=generic)
+    torch.cuda.synchronize()
+    ops.check_status()
+    return res
+
+
+def assert_out_close(ours, ref, dtype, what="out"):
+    if dtype == "float32":
+        scale = max(1e-6, float(np.abs(ref).max()))
+        assert float(np.abs(ours - ref).max()) <= 1e-4 * scale, f"{what}: fp32 must be within 1e-4 relative"
+    else:
+        assert float(np.abs(ours - ref).max()) <= OUT_TOL[dtype], f"{what}: {dtype} must be within 2e-2 absolute"
+
+
+def compare_with_oracle(c, q, k, v, ours_parents, ref, eps):
+    """Level-by-level selection comparison (top level first); a level is only compared on groups whose earlier levels
+    agreed (cf. correctness_test.py:431-460).  Returns (rows_exact_everywhere mask [n], near_ties)."""
+    L = ref["num_layers"]
+    TK = c["TK"]
+    n = ref["parents"][0].reshape(-1, TK).shape[0]
+    same = np.ones(n, bool)
+    near_total = 0
+    for l in range(L - 1, 0, -1):
+        o = ours_parents[l - 1].reshape(-1, TK)
+        r = ref["parents"][l - 1].reshape(-1, TK)
+        rows = np.nonzero(same)[0]
+        ex, near, bad = parity.compare_selections(o[rows], r[rows], ref["importance"][l][rows],
+                                                  ref["parents"][l].reshape(-1, TK)[rows], c["CR"], eps)
+        assert bad == 0, f"level {l}: {bad} selection mismatches that are not near-ties"
+        near_total += near
+        same &= (o == r).all(-1)
+    return same, near_total
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16", "float16"])
+def test_tree_build_bit_exact(dtype):
+    ops = _ops()
+    _, k, v, _ = parity.make_inputs(2, 1237, 4, 2, 32, 16, dtype, 3)
+    lk, lv = ops.build_tree(k.to(DEV), v.to(DEV), 4, 10)
+    rk, rv = oracle.build_tree(parity.f32(k), parity.f32(v), 4, 10, dtype)
+    assert [x.shape[1] for x in lk] == [x.shape[1] for x in rk] == [1237, 310, 78, 20, 5]
+    for a, b in zip(lk[1:] + lv[1:], rk[1:] + rv[1:]):
+        assert np.array_equal(parity.f32(a), b)      # fp32 sum in child order, one division, one rounding
+
+
+@pytest.mark.parametrize("name", sorted(CASES))
+def test_forward_against_golden(name):
+    c = CASES[name]
+    g = parity.load_golden(name)
+    q, k, v, dO = parity.case_inputs(c)
+    out, ctx, tr = run_ours(c, q, k, v)
+    ref = oracle.forward(parity.f32(q), parity.f32(k), parity.f32(v), c["CR"], c["MTN"], c["TK"], dtype=c["dtype"],
+                         return_importance=True)
+    L, Lg = ctx["num_layers"], int(g["num_layers"])
+    assert L == ref["num_layers"] >= Lg
+    ours_parents = [ctx["per_layer_parents"][l].cpu().numpy() for l in range(L)]
+    same, near = compare_with_oracle(c, q, k, v, ours_parents, ref, EPS_SEL[c["dtype"]])
+    # against the reference's own tensors: selections, then outputs on the groups that agree everywhere
+    for l in range(1, Lg):
+        o = ours_parents[l - 1].reshape(-1, c["TK"]); r = g[f"sel_{l}"].reshape(-1, c["TK"])
+        assert ((o == r).all(-1) | ~same).all()
+    G = c["H"] // c["H_kv"]
+    rows = np.repeat(same, G).reshape(c["B"], c["T"], c["H"])
+    assert rows.mean() > 0.99
+    o = parity.f32(out); gr = g["out"]
+    assert_out_close(o[rows], gr[rows], c["dtype"])
+    for l in range(Lg):
+        lm = parity.f32(tr["layers"][l].layer_max); ls = parity.f32(tr["layers"][l].layer_sum)
+        assert np.allclose(lm[rows], g[f"lmax_{l}"][rows], rtol=1e-4, atol=1e-4)
+        assert np.allclose(ls[rows], g[f"lsum_{l}"][rows], rtol=1e-4, atol=1e-6)
+        if f"lout_{l}" in g:
+            lo = parity.f32(tr["layers"][l].layer_output)
+            assert np.allclose(lo[rows], g[f"lout_{l}"][rows], rtol=1e-4, atol=1e-4)
+
+
+@pytest.mark.parametrize("name", sorted(n for n, c in CASES.items() if c["bwd"]))
+def test_backward_against_golden(name):
+    ops = _ops()
+    c = CASES[name]
+    g = parity.load_golden(name)
+    q, k, v, dO = parity.case_inputs(c)
+    out, ctx = ops.htree_forward(q.to(DEV), k.to(DEV), v.to(DEV), c["CR"], c["MTN"], c["TK"], _save_for_backward=True,
+                                 _force_generic=True)
+    dq, dk, dv = ops.htree_backward(dO.to(DEV), q.to(DEV), out, ctx)
+    torch.cuda.synchronize(); ops.check_status()
+    # the golden gradients assume the reference's selections: require identical selections for this comparison
+    Lg = int(g["num_layers"])
+    for l in range(1, Lg):
+        assert np.array_equal(ctx["per_layer_parents"][l - 1].cpu().numpy(), g[f"sel_{l}"])
+    tol = {"float32": 1e-4, "bfloat16": 2e-2, "float16": 4e-3}[c["dtype"]]
+    for nm, t in (("dq", dq), ("dk", dk), ("dv", dv)):
+        ref = g[nm]
+        got = parity.f32(t.to(parity.TDT[c["dtype"]]))          # the reference returns gradients in the input dtype
+        assert float(np.abs(got - ref).max()) <= tol * max(1.0, float(np.abs(ref).max())), nm
+
+
+def test_selection_only_replay_and_autograd_recompute():
+    ops = _ops()
+    c = CASES["f32_T300_cr4_tk8"]
+    q, k, v, dO = (x.to(DEV) for x in parity.case_inputs(c))
+    out, ctx = ops.htree_forward(q, k, v, c["CR"], c["MTN"], c["TK"], _save_for_backward=True)
+    again = ops.recompute_parents(q, ctx["layers_k"], ctx["layers_v"], ctx["cos_cache"], ctx["sin_cache"], c["CR"],
+                                  c["TK"], c["MTN"], ctx["scale"])
+    for l in range(ctx["num_layers"]):
+        assert torch.equal(again[l], ctx["per_layer_parents"][l])
+    grads = []
+    for save in (True, False):
+        ops.ops.SAVE_SELECTIONS_FOR_BACKWARD = save
+        try:
+            qq, kk, vv = (x.clone().requires_grad_(True) for x in (q, k, v))
+            o = ops.htree_forward_triton_autograd(qq, kk, vv, c["CR"], c["MTN"], c["TK"])
+            o.backward(dO)
+            grads.append((qq.grad, kk.grad, vv.grad))
+            assert torch.equal(o, out)
+        finally:
+            ops.ops.SAVE_SELECTIONS_FOR_BACKWARD = True
+    for a, b in zip(*grads):
+        assert torch.allclose(a, b, rtol=1e-5, atol=1e-6)       # atomics: summation order differs run to run
+    g = parity.load_golden("f32_T300_cr4_tk8")
+    assert float((grads[0][0].cpu() - torch.from_numpy(g["dq"])).abs().max()) < 1e-4
+
+
+def _dense_reference(q, k, v, rope_base=10000.0):
+    """Plain PyTorch fp32 causal attention with half-split RoPE at absolute positions, GQA-broadcast."""
+    B, T, H, K = q.shape
+    Hkv = k.shape[2]
+    G = H // Hkv
+    half = K // 2
+    inv = 1.0 / (rope_base ** (torch.arange(0, K, 2, dtype=torch.float32, device=q.device) / K))
+    fr = torch.outer(torch.arange(T, dtype=torch.float32, device=q.device), inv)
+    cs, sn = fr.cos()[None, :, None, :], fr.sin()[None, :, None, :]
+
+    def rope(x):
+        lo, hi = x[..., :half], x[..., half:]
+        return torch.cat([lo * cs - hi * sn, lo * sn + hi * cs], -1)
+
+    qr = rope(q.float()) * K ** -0.5
+    kr = rope(k.float()).repeat_interleave(G, dim=2)
+    vv = v.float().repeat_interleave(G, dim=2)
+    s = torch.einsum("bthk,bjhk->bhtj", qr, kr)
+    s = s.masked_fill(torch.triu(torch.ones(T, T, dtype=torch.bool, device=q.device), 1), float("-inf"))
+    return torch.einsum("bhtj,bjhv->bthv", s.softmax(-1), vv)
+
+
+@pytest.mark.parametrize("dtype,cr,mtn,tk", [("float32", 4, 8, 64), ("float32", 16, 300, 32), ("bfloat16", 8, 16, 64)])
+def test_dense_equivalence(dtype, cr, mtn, tk):
+    """If no level ever drops a candidate the operator is ordinary causal attention (known-answer test)."""
+    ops = _ops()
+    q, k, v, _ = (x.to(DEV) for x in parity.make_inputs(2, 200, 8, 2, 32, 16, dtype, 9))
+    out = ops.htree_forward(q, k, v, cr, mtn, tk)
+    ref = _dense_reference(q, k, v)
+    assert_out_close(parity.f32(out), parity.f32(ref.to(q.dtype)), dtype)
+
+
+def test_causality_and_forced_rightmost():
+    ops = _ops()
+    q, k, v, _ = (x.to(DEV) for x in parity.make_inputs(1, 700, 4, 2, 16, 16, "float32", 7))
+    a, ctx = ops.htree_forward(q, k, v, 4, 32, 8, _save_for_backward=True)
+    t0 = 333
+    k2, v2 = k.clone(), v.clone()
+    k2[:, t0 + 1:] += 3.0; v2[:, t0 + 1:] -= 2.0
+    b = ops.htree_forward(q, k2, v2, 4, 32, 8)
+    assert torch.equal(a[:, : t0 + 1], b[:, : t0 + 1])
+    # the node containing t is kept at every level (src/naive.py:93)
+    t = torch.arange(700, device=DEV)
+    for l in range(1, ctx["num_layers"]):
+        sel = ctx["per_layer_parents"][l - 1]                       # selection made at level l
+        assert (sel == (t // 4 ** l)[None, :, None, None]).any(-1).all()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_headline_cpu_case_full(dtype):
+    """BASELINE config 1 shapes (B=1,T=2048,H=8,H_kv=2,D=64,CR=16,max_top_nodes=64,Top-K=32), every group against the oracle,
+    forward and backward."""
+    ops = _ops()
+    c = dict(B=1, T=2048, H=8, H_kv=2, K=64, V=64, CR=16, TK=32, MTN=64, dtype=dtype, seed=0)
+    q, k, v, dO = parity.case_inputs(c)
+    out, ctx, tr = run_ours(c, q, k, v)
+    ref = oracle.forward(parity.f32(q), parity.f32(k), parity.f32(v), 16, 64, 32, dtype=dtype, return_importance=True)
+    L = ctx["num_layers"]
+    assert L == 3
+    ours_parents = [ctx["per_layer_parents"][l].cpu().numpy() for l in range(L)]
+    same, near = compare_with_oracle(c, q, k, v, ours_parents, ref, EPS_SEL[dtype])
+    assert same.mean() > 0.995
+    rows = np.repeat(same, 4).reshape(1, 2048, 8)
+    assert_out_close(parity.f32(out)[rows], ref["out_rounded"][rows], dtype)
+    # backward with OUR selections substituted into the oracle (gradient arithmetic is what is being compared)
+    fwd = dict(ref)
+    fwd["parents"] = np.stack(ours_parents)
+    if not same.all():
+        fwd["gmax"] = parity.f32(ctx["global_max"]); fwd["gsum"] = parity.f32(ctx["global_sum"])
+        fwd["out_rounded"] = parity.f32(out)
+    gref = oracle.backward(parity.f32(q), fwd, parity.f32(dO), 16, 32, dtype)
+    dq, dk, dv = ops.htree_backward(dO.to(DEV), q.to(DEV), out, ctx)
+    for nm, t in (("dq", dq), ("dk", dk), ("dv", dv)):
+        r = gref[nm + "_f32"]
+        tol = 1e-4 if dtype == "float32" else 2e-3      # bf16: gmax/gsum/out differ by storage rounding of out
+        assert float(np.abs(parity.f32(t) - r).max()) <= tol * max(1.0, float(np.abs(r).max())), nm
