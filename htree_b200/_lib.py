@@ -19,6 +19,7 @@ FWD_GENERIC = 2
 SYMBOLS = (
     "htree_b200_version",
     "htree_b200_error_string",
+    "htree_b200_launch_count",
     "htree_b200_num_levels",
     "htree_b200_level_sizes",
     "htree_b200_build_tree",
@@ -29,7 +30,8 @@ SYMBOLS = (
 
 class HtreeShape(ctypes.Structure):
     _fields_ = [(n, ctypes.c_int32) for n in
-                ("B", "T", "H", "H_kv", "K", "V", "compression_rate", "top_k", "max_top_nodes", "dtype")]
+                ("B", "T", "H", "H_kv", "K", "V", "compression_rate", "top_k", "max_top_nodes", "dtype", "T_q",
+                 "t_offset")]
 
 
 class HtreeTrace(ctypes.Structure):
@@ -58,6 +60,7 @@ def lib() -> ctypes.CDLL:
         L.htree_b200_version.restype = ctypes.c_int
         L.htree_b200_error_string.restype = ctypes.c_char_p
         L.htree_b200_error_string.argtypes = [ctypes.c_int]
+        L.htree_b200_launch_count.restype = ctypes.c_uint64
         L.htree_b200_num_levels.restype = ctypes.c_int
         L.htree_b200_num_levels.argtypes = [i32, i32, i32]
         L.htree_b200_level_sizes.restype = ctypes.c_int
@@ -72,6 +75,10 @@ def lib() -> ctypes.CDLL:
                                           vp, vp, vp, vp, u32, vp]
         _lib = L
     return _lib
+
+
+def launch_count() -> int:
+    return int(lib().htree_b200_launch_count())
 
 
 def error_string(code: int) -> str:

@@ -1,9 +1,13 @@
 // extern "C" boundary of libhtree_b200: argument validation, parameter blocks, kernel dispatch.
+#include <atomic>
 #include <cstring>
 
 #include "common.cuh"
 
 namespace htree {
+
+static std::atomic<unsigned long long> g_launches{0};
+void note_launch(int n) { g_launches.fetch_add((unsigned long long)n, std::memory_order_relaxed); }
 
 static int esize(int dtype) { return dtype == HTREE_F32 ? 4 : 2; }
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -31,6 +35,8 @@ static int check_shape(const HtreeShape* s, int32_t* ln, bool check_top = true) 
     if (check_top && (int64_t)ln[L - 1] > (int64_t)s->top_k * s->compression_rate) return HTREE_E_TOPLEVEL;
     // 16-byte rows: K, V multiples of 8 keep every vector load of every kernel aligned for all storage types
     if (s->K % 8 != 0 || s->V % 8 != 0) return HTREE_E_ALIGN;
+    if (s->T_q < 0 || s->t_offset < 0 || (s->T_q == 0 && s->t_offset != 0) ||
+        (int64_t)s->t_offset + s->T_q > s->T) return HTREE_E_WINDOW;
     return L;
 }
 
@@ -53,6 +59,7 @@ static int fill_params(AttnParams& p, const HtreeShape* s, int L, const int32_t*
     p.cosc = cosc; p.sinc = sinc; p.status = status;
     p.B = s->B; p.T = s->T; p.H = s->H; p.Hkv = s->H_kv; p.K = s->K; p.V = s->V;
     p.CR = s->compression_rate; p.TK = s->top_k; p.L = L; p.G = s->H / s->H_kv; p.n_pos = n_pos;
+    p.Tq = s->T_q > 0 ? s->T_q : s->T; p.t0 = s->t_offset;
     p.scale = scale; p.flags = flags;
     return 0;
 }
@@ -64,6 +71,8 @@ using namespace htree;
 extern "C" {
 
 int htree_b200_version(void) { return HTREE_B200_VERSION; }
+
+uint64_t htree_b200_launch_count(void) { return (uint64_t)htree::g_launches.load(std::memory_order_relaxed); }
 
 const char* htree_b200_error_string(int code) {
     switch (code) {
@@ -77,6 +86,7 @@ const char* htree_b200_error_string(int code) {
         case HTREE_E_ALIGN: return "pointers must be 16-byte aligned and K, V multiples of 8";
         case HTREE_E_UNSUPPORTED: return "shape not supported by the compiled kernels";
         case HTREE_E_NODEVICE: return "no usable CUDA device";
+        case HTREE_E_WINDOW: return "query window outside the sequence, or a window passed to the backward";
         default: return code > 0 ? cudaGetErrorString((cudaError_t)code) : "unknown htree_b200 error";
     }
 }
@@ -140,6 +150,7 @@ int htree_b200_backward(const HtreeShape* shape, const void* q, void* const* lay
     const int L = check_shape(shape, ln);
     if (L < 0) return L;
     if (!out || !dO || !gmax || !gsum || !parents || !dq || !dk_levels || !dv_levels) return HTREE_E_NULL;
+    if (shape->T_q != 0 && (shape->T_q != shape->T || shape->t_offset != 0)) return HTREE_E_WINDOW;
     AttnParams p;
     int rc = fill_params(p, shape, L, ln, q, layers_k, layers_v, cos_cache, sin_cache, n_pos, scale, parents, status, flags);
     if (rc) return rc;

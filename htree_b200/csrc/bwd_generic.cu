@@ -314,6 +314,7 @@ static int launch_bt(const AttnParams& p, cudaStream_t st) {
     bwd_generic_kernel<T, GPV><<<grid, NTB, smem, st>>>(p);
     if (GP == 4) { HT_LAUNCH(4) } else if (GP == 8) { HT_LAUNCH(8) } else { HT_LAUNCH(16) }
 #undef HT_LAUNCH
+    note_launch();
     return (int)cudaGetLastError();
 }
 

@@ -37,6 +37,7 @@ struct AttnParams {
     float* dk[HTREE_MAX_LEVELS];
     float* dv[HTREE_MAX_LEVELS];
     int32_t B, T, H, Hkv, K, V, CR, TK, L, G, n_pos;
+    int32_t Tq, t0;   // query window: rows 0..Tq-1 of q/out are sequence positions t0..t0+Tq-1
     float scale;
     uint32_t flags;
 };
@@ -99,6 +100,8 @@ __device__ __forceinline__ int block_scan_flag(bool f, int* wtot, int* total) {
     *total = tot;
     return before + __popc(m & ((1u << lane) - 1u));
 }
+
+void note_launch(int n = 1);   // diagnostic launch counter (api.cu)
 
 // launchers implemented in the .cu files (return cudaError_t as int)
 int launch_tree_build(const HtreeShape& s, int L, const int32_t* ln, void* const* lk, void* const* lv, cudaStream_t st);

@@ -86,11 +86,11 @@ __global__ void __launch_bounds__(NT) fwd_generic_kernel(const __grid_constant__
     float *gm = m.st, *gs = m.st + GPAD, *lm = m.st + 2 * GPAD, *ls = m.st + 3 * GPAD, *sg = m.st + 4 * GPAD, *sc = m.st + 5 * GPAD;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int t = blockIdx.x;
+    const int t = p.t0 + blockIdx.x;                                        // sequence position of this query
     const int b = blockIdx.y / p.Hkv, hk = blockIdx.y % p.Hkv;
     const bool select_only = (p.flags & HTREE_FWD_SELECT_ONLY) != 0;
-    const int64_t hbase = ((int64_t)b * p.T + t) * p.H + (int64_t)hk * G;   // first head of the group
-    const int64_t qidx = ((int64_t)b * p.T + t) * p.Hkv + hk;               // group index for parents
+    const int64_t hbase = ((int64_t)b * p.Tq + blockIdx.x) * p.H + (int64_t)hk * G;   // first head of the group
+    const int64_t qidx = ((int64_t)b * p.Tq + blockIdx.x) * p.Hkv + hk;               // group index for parents
     const T* qg = reinterpret_cast<const T*>(p.q) + hbase * K;
 
     // ---- state initialisation (src/parallel.py:995-997, 1026-1038) ----
@@ -326,11 +326,11 @@ __global__ void __launch_bounds__(NT) fwd_generic_kernel(const __grid_constant__
             }
 
             // ---- trace + 5. merge into the running state (src/naive.py:215-223) ----
-            if (p.tr_max) for (int g = tid; g < G; g += NT) p.tr_max[(int64_t)l * p.B * p.T * p.H + hbase + g] = lm[g];
-            if (p.tr_sum) for (int g = tid; g < G; g += NT) p.tr_sum[(int64_t)l * p.B * p.T * p.H + hbase + g] = ls[g];
+            if (p.tr_max) for (int g = tid; g < G; g += NT) p.tr_max[(int64_t)l * p.B * p.Tq * p.H + hbase + g] = lm[g];
+            if (p.tr_sum) for (int g = tid; g < G; g += NT) p.tr_sum[(int64_t)l * p.B * p.Tq * p.H + hbase + g] = ls[g];
             if (p.tr_out)
                 for (int i = tid; i < G * V; i += NT)
-                    p.tr_out[((int64_t)l * p.B * p.T * p.H + hbase) * V + i] = m.lo[i];
+                    p.tr_out[((int64_t)l * p.B * p.Tq * p.H + hbase) * V + i] = m.lo[i];
             for (int g = tid; g < GPAD; g += NT) {
                 const bool ch = ls[g] > kHasMass, gh = gs[g] > kHasMass;
                 const float nm = fmaxf(gm[g], lm[g]);
@@ -371,7 +371,7 @@ static int launch_t(const AttnParams& p, cudaStream_t st) {
     const int GPAD = (G + GP - 1) / GP * GP;
     const size_t smem = fwd_smem_layout(p.K, p.V, GPAD, GP, p.TK * p.CR, p.TK, nullptr, nullptr);
     if (smem > 227 * 1024) return HTREE_E_UNSUPPORTED;
-    dim3 grid(p.T, p.B * p.Hkv);
+    dim3 grid(p.Tq, p.B * p.Hkv);
     cudaError_t e;
 #define HT_LAUNCH(GPV)                                                                                              \
     e = cudaFuncSetAttribute(fwd_generic_kernel<T, GPV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
@@ -379,6 +379,7 @@ static int launch_t(const AttnParams& p, cudaStream_t st) {
     fwd_generic_kernel<T, GPV><<<grid, NT, smem, st>>>(p);
     if (GP == 4) { HT_LAUNCH(4) } else if (GP == 8) { HT_LAUNCH(8) } else { HT_LAUNCH(16) }
 #undef HT_LAUNCH
+    note_launch();
     return (int)cudaGetLastError();
 }
 

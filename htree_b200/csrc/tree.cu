@@ -114,6 +114,7 @@ static int build_levels(const HtreeShape& s, int L, const int32_t* ln, void* con
         dim3 grid((unsigned)((mx + 255) / 256), 2);
         if (s.compression_rate >= 16) tree_build_kernel<T, 16><<<grid, 256, 0, st>>>(a);
         else tree_build_kernel<T, 8><<<grid, 256, 0, st>>>(a);
+        note_launch();
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) return (int)e;
     }
@@ -166,6 +167,7 @@ int launch_tree_backward(const HtreeShape& s, int L, const int32_t* ln, float* c
         int64_t mx = a.total[0] > a.total[1] ? a.total[0] : a.total[1];
         dim3 grid((unsigned)((mx + 255) / 256), 2);
         tree_backward_kernel<<<grid, 256, 0, st>>>(a);
+        note_launch();
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) return (int)e;
     }

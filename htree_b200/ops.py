@@ -90,22 +90,25 @@ def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
-def _validate(q, k, v, compression_rate, max_top_nodes, top_k_per_layer):
+def _validate(q, k, v, compression_rate, max_top_nodes, top_k_per_layer, q_offset=None):
     if q.dim() != 4 or k.dim() != 4 or v.dim() != 4:
         raise ValueError("q/k/v must be rank-4 tensors")          # src/naive.py:141-142
     if not (q.is_cuda and k.is_cuda and v.is_cuda):
         raise RuntimeError("htree_b200 runs on CUDA tensors only; there is no CPU implementation")
-    B, T, H, K = q.shape
+    B, T_q, H, K = q.shape
+    T = T_q if q_offset is None else k.shape[1]
     H_kv, V = k.shape[2], v.shape[-1]
     assert H % H_kv == 0, f"H ({H}) must be divisible by H_kv ({H_kv})"                      # src/parallel.py:912
     assert k.shape[2] == v.shape[2], "K and V must have same number of heads"                # src/parallel.py:914
     assert tuple(k.shape[:2]) == (B, T) and tuple(v.shape[:2]) == (B, T) and k.shape[3] == K  # src/naive.py:146
+    if q_offset is not None:
+        assert 0 <= q_offset and q_offset + T_q <= T, "query window must lie inside the key/value sequence"
     assert q.dtype == k.dtype == v.dtype and q.dtype in _DTYPES, "q, k, v must share one of fp32/bf16/fp16"
     assert max_top_nodes <= top_k_per_layer * compression_rate, (
         f"max_top_nodes ({max_top_nodes}) must not exceed top_k_per_layer*compression_rate "
         f"({top_k_per_layer}*{compression_rate})")                                            # cf. src/parallel.py:917-920
     return _lib.HtreeShape(B, T, H, H_kv, K, V, int(compression_rate), int(top_k_per_layer), int(max_top_nodes),
-                           _DTYPES[q.dtype])
+                           _DTYPES[q.dtype], 0 if q_offset is None else T_q, 0 if q_offset is None else int(q_offset))
 
 
 def _ptrs(tensors) -> ctypes.Array:
@@ -147,21 +150,24 @@ def htree_forward(
     compression_rate: int = 16, max_top_nodes: int = 8192, top_k_per_layer: int = 512,
     scale: Optional[float] = None, rope_base: float = 10000.0,
     _save_for_backward: bool = False, _save_parents: bool = True,
-    return_trace: bool = False, _force_generic: bool = False,
+    return_trace: bool = False, _force_generic: bool = False, _q_offset: Optional[int] = None, _layers=None,
 ):
     """htree forward.  q [B,T,H,K], k [B,T,H_kv,K], v [B,T,H_kv,V] -> out [B,T,H,V] in q's dtype.
 
     Returns `out`, or `(out, bwd_ctx)` with `_save_for_backward` (the reference's contract, src/parallel.py:1139-1159),
     with a third element — {"num_layers", "num_groups", "layers": {l: LayerTrace}} — when `return_trace` is set
-    (the shape of htree_forward_naive's trace, src/naive.py:225-234)."""
-    shape = _validate(q, k, v, compression_rate, max_top_nodes, top_k_per_layer)
+    (the shape of htree_forward_naive's trace, src/naive.py:225-234).
+
+    Sequence sharding: with `_q_offset` = t0, q holds only the query positions t0 .. t0+q.shape[1]-1 while k, v (or the
+    prebuilt tree `_layers` = (layers_k, layers_v)) cover the whole sequence; outputs have q's length."""
+    shape = _validate(q, k, v, compression_rate, max_top_nodes, top_k_per_layer, _q_offset)
     B, T, H, K = q.shape
     H_kv, V = k.shape[2], v.shape[-1]
     if scale is None:
         scale = K ** -0.5
     q = q.contiguous(); k = k.contiguous(); v = v.contiguous()
     dev = q.device
-    layers_k, layers_v = build_tree(k, v, compression_rate, max_top_nodes)
+    layers_k, layers_v = _layers if _layers is not None else build_tree(k, v, compression_rate, max_top_nodes)
     L = len(layers_k)
     cos_cache, sin_cache = rope_cache(K, top_k_per_layer * compression_rate + 1024, rope_base, dev)
     out = torch.empty(B, T, H, V, dtype=q.dtype, device=dev)

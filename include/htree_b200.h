@@ -40,6 +40,7 @@ extern "C" {
 #define HTREE_E_ALIGN (-7)       /* a pointer or row size breaks the 16-byte alignment the kernels need */
 #define HTREE_E_UNSUPPORTED (-8) /* shape outside what the kernels were built for (e.g. shared memory need) */
 #define HTREE_E_NODEVICE (-9)    /* no CUDA device / wrong architecture */
+#define HTREE_E_WINDOW (-10)     /* query window outside the sequence, or a window given to the backward */
 
 /* forward flags */
 #define HTREE_FWD_SELECT_ONLY 1u /* rebuild the selections only: no V reads, no accumulation, out/gmax/gsum untouched */
@@ -53,6 +54,12 @@ typedef struct HtreeShape {
     int32_t top_k;          /* top_k_per_layer */
     int32_t max_top_nodes;  /* may be smaller than top_k*compression_rate; the reference asserts equality */
     int32_t dtype;          /* HTREE_F32 / HTREE_BF16 / HTREE_F16 */
+    /* Query window for sequence-sharded forward calls: the call computes query positions
+     * t_offset .. t_offset + T_q - 1 of the sequence, q/out are [B,T_q,H,*], gmax/gsum [B,T_q,H] and parents
+     * [B,T_q,H_kv,top_k], while the tree levels still cover all T positions.  T_q = 0 means the whole sequence
+     * (T_q = T, t_offset = 0).  The reference has no counterpart (it always runs every position). */
+    int32_t T_q;
+    int32_t t_offset;
 } HtreeShape;
 
 /* Optional per-level accumulator dump, the reference's LayerTrace (src/naive.py:13-19; filled by the harness in
@@ -66,6 +73,10 @@ typedef struct HtreeTrace {
 
 int htree_b200_version(void);
 const char* htree_b200_error_string(int code);
+
+/* Diagnostic: number of kernels this library has launched in the calling process so far (all threads, all devices).
+ * No counterpart in the reference. */
+uint64_t htree_b200_launch_count(void);
 
 /* Number of tree levels for a sequence length, and their lengths N_l (level loop of src/parallel.py:941-945).
  * htree_b200_level_sizes writes at most `cap` entries and returns the level count (or HTREE_E_LEVELS). */

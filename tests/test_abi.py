@@ -43,7 +43,7 @@ def test_level_sizes_follow_the_reference_loop():
 def _shape(**kw):
     d = dict(B=1, T=256, H=4, H_kv=2, K=16, V=16, compression_rate=4, top_k=8, max_top_nodes=32, dtype=0)
     d.update(kw)
-    return _lib.HtreeShape(*[d[n] for n, _ in _lib.HtreeShape._fields_])
+    return _lib.HtreeShape(*[d.get(n, 0) for n, _ in _lib.HtreeShape._fields_])
 
 
 def _fwd(shape, q=16, lk=None, n_pos=2048):
@@ -63,7 +63,8 @@ def test_argument_errors_are_reported_before_any_launch():
     assert _fwd(_shape(), q=None) == -1
     assert _fwd(_shape(), n_pos=8) == -6
     assert _fwd(_shape(), q=4100) == -7                 # misaligned pointer
-    for code in (-1, -2, -3, -4, -5, -6, -7, -8, -9):
+    assert _fwd(_shape(T_q=100, t_offset=200)) == -10   # window runs past the sequence
+    for code in (-1, -2, -3, -4, -5, -6, -7, -8, -9, -10):
         assert "unknown htree_b200 error" not in _lib.error_string(code)
 
 
