@@ -23,6 +23,7 @@ SYMBOLS = (
     "htree_b200_num_levels",
     "htree_b200_level_sizes",
     "htree_b200_build_tree",
+    "htree_b200_rotate_keys",
     "htree_b200_forward",
     "htree_b200_backward",
 )
@@ -66,9 +67,11 @@ def lib() -> ctypes.CDLL:
         L.htree_b200_level_sizes.restype = ctypes.c_int
         L.htree_b200_level_sizes.argtypes = [i32, i32, i32, ctypes.POINTER(i32), i32]
         L.htree_b200_build_tree.restype = ctypes.c_int
-        L.htree_b200_build_tree.argtypes = [ctypes.POINTER(HtreeShape), vp, vp, vp]
+        L.htree_b200_build_tree.argtypes = [ctypes.POINTER(HtreeShape), vp, vp, vp, vp, vp, vp]
+        L.htree_b200_rotate_keys.restype = ctypes.c_int
+        L.htree_b200_rotate_keys.argtypes = [ctypes.POINTER(HtreeShape), vp, vp, vp, vp, vp]
         L.htree_b200_forward.restype = ctypes.c_int
-        L.htree_b200_forward.argtypes = [ctypes.POINTER(HtreeShape), vp, vp, vp, vp, vp, i32, f32, vp, vp, vp, vp,
+        L.htree_b200_forward.argtypes = [ctypes.POINTER(HtreeShape), vp, vp, vp, vp, vp, vp, i32, f32, vp, vp, vp, vp,
                                          ctypes.POINTER(HtreeTrace), vp, u32, vp]
         L.htree_b200_backward.restype = ctypes.c_int
         L.htree_b200_backward.argtypes = [ctypes.POINTER(HtreeShape), vp, vp, vp, vp, vp, i32, f32, vp, vp, vp, vp, vp,

@@ -105,7 +105,8 @@ int htree_b200_level_sizes(int32_t T, int32_t CR, int32_t MTN, int32_t* sizes, i
     return L;
 }
 
-int htree_b200_build_tree(const HtreeShape* shape, void* const* layers_k, void* const* layers_v, void* stream) {
+int htree_b200_build_tree(const HtreeShape* shape, void* const* layers_k, void* const* layers_v,
+                          void* const* layers_k_rot, const float* cos_cache, const float* sin_cache, void* stream) {
     int32_t ln[HTREE_MAX_LEVELS];
     const int L = check_shape(shape, ln, false);   // top_k plays no role in the tree
     if (L < 0) return L;
@@ -116,11 +117,36 @@ int htree_b200_build_tree(const HtreeShape* shape, void* const* layers_k, void* 
     }
     const int es = esize(shape->dtype);
     if ((shape->H_kv * shape->K * es) % 16 || (shape->H_kv * shape->V * es) % 16) return HTREE_E_ALIGN;
-    return launch_tree_build(*shape, L, ln, layers_k, layers_v, (cudaStream_t)stream);
+    if (layers_k_rot) {
+        if (!cos_cache || !sin_cache) return HTREE_E_NULL;
+        if (!aligned16(cos_cache) || !aligned16(sin_cache)) return HTREE_E_ALIGN;
+        for (int l = 0; l < L; ++l) {
+            if (!layers_k_rot[l]) return HTREE_E_NULL;
+            if (!aligned16(layers_k_rot[l])) return HTREE_E_ALIGN;
+        }
+    }
+    int rc = launch_tree_build(*shape, L, ln, layers_k, layers_v, (cudaStream_t)stream);
+    if (rc == 0 && layers_k_rot)
+        rc = launch_rotate_keys(*shape, L, ln, layers_k, layers_k_rot, cos_cache, sin_cache, (cudaStream_t)stream);
+    return rc;
+}
+
+int htree_b200_rotate_keys(const HtreeShape* shape, void* const* layers_k, void* const* layers_k_rot,
+                           const float* cos_cache, const float* sin_cache, void* stream) {
+    int32_t ln[HTREE_MAX_LEVELS];
+    const int L = check_shape(shape, ln, false);
+    if (L < 0) return L;
+    if (!layers_k || !layers_k_rot || !cos_cache || !sin_cache) return HTREE_E_NULL;
+    if (!aligned16(cos_cache) || !aligned16(sin_cache)) return HTREE_E_ALIGN;
+    for (int l = 0; l < L; ++l) {
+        if (!layers_k[l] || !layers_k_rot[l]) return HTREE_E_NULL;
+        if (!aligned16(layers_k[l]) || !aligned16(layers_k_rot[l])) return HTREE_E_ALIGN;
+    }
+    return launch_rotate_keys(*shape, L, ln, layers_k, layers_k_rot, cos_cache, sin_cache, (cudaStream_t)stream);
 }
 
 int htree_b200_forward(const HtreeShape* shape, const void* q, void* const* layers_k, void* const* layers_v,
-                       const float* cos_cache, const float* sin_cache, int32_t n_pos, float scale, void* out,
+                       void* const* layers_k_rot, const float* cos_cache, const float* sin_cache, int32_t n_pos, float scale, void* out,
                        float* gmax, float* gsum, int32_t* const* parents, const HtreeTrace* trace, int32_t* status,
                        uint32_t flags, void* stream) {
     int32_t ln[HTREE_MAX_LEVELS];
@@ -138,6 +164,14 @@ int htree_b200_forward(const HtreeShape* shape, const void* q, void* const* laye
     }
     p.out = out; p.gmax = gmax; p.gsum = gsum;
     if (trace) { p.tr_max = trace->layer_max; p.tr_sum = trace->layer_sum; p.tr_out = trace->layer_out; }
+    if (layers_k_rot && !trace && !(flags & HTREE_FWD_GENERIC)) {
+        bool all = true;
+        for (int l = 0; l < L; ++l) {
+            if (!layers_k_rot[l] || !aligned16(layers_k_rot[l])) all = false;
+            p.lkr[l] = layers_k_rot[l];
+        }
+        if (all && fwd_mma_supported(p, shape->dtype)) return launch_fwd_mma(p, shape->dtype, (cudaStream_t)stream);
+    }
     return launch_fwd_generic(p, shape->dtype, (cudaStream_t)stream);
 }
 

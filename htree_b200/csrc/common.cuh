@@ -18,6 +18,7 @@ struct AttnParams {
     const void* q;
     const void* lk[HTREE_MAX_LEVELS];
     const void* lv[HTREE_MAX_LEVELS];
+    const void* lkr[HTREE_MAX_LEVELS];   // keys pre-rotated by their child index (16-bit storage types only), or NULL
     int32_t ln[HTREE_MAX_LEVELS];   // N_l
     int64_t lpow[HTREE_MAX_LEVELS]; // CR^l
     const float* cosc;
@@ -106,7 +107,11 @@ void note_launch(int n = 1);   // diagnostic launch counter (api.cu)
 // launchers implemented in the .cu files (return cudaError_t as int)
 int launch_tree_build(const HtreeShape& s, int L, const int32_t* ln, void* const* lk, void* const* lv, cudaStream_t st);
 int launch_tree_backward(const HtreeShape& s, int L, const int32_t* ln, float* const* dk, float* const* dv, cudaStream_t st);
+int launch_rotate_keys(const HtreeShape& s, int L, const int32_t* ln, void* const* lk, void* const* lkr, const float* cosc,
+                       const float* sinc, cudaStream_t st);
 int launch_fwd_generic(const AttnParams& p, int dtype, cudaStream_t st);
+bool fwd_mma_supported(const AttnParams& p, int dtype);
+int launch_fwd_mma(const AttnParams& p, int dtype, cudaStream_t st);
 int launch_bwd_generic(const AttnParams& p, int dtype, cudaStream_t st);
 
 }  // namespace htree

@@ -1,0 +1,413 @@
+// Tensor-core forward for 16-bit storage types: one WARP per (batch, query position, KV head) group, all tree levels
+// in one launch, every operand moved global/L2 -> registers -> mma.sync (no shared-memory staging, no block barriers).
+//
+// Replaces the same reference kernels as the generic forward (htree_select_accumulate_gqa_kernel,
+// htree_bottom_accumulate_gqa_kernel, htree_merge_to_global_kernel, htree_final_normalize_kernel;
+// src/parallel.py:248-867) for bf16/fp16, head_dim 64 or 128, K == V, group size <= 16, compression_rate 16.
+//
+// Design notes
+//  * M = the GQA group (<= 16 query heads) maps exactly onto the M = 16 rows of mma.sync.m16n8k16; candidates are the
+//    N dimension of the score product and the K dimension of the P.V product, so a chunk of 16 candidates (= the
+//    children of one parent) is two n8 score tiles and one k16 accumulation step.
+//  * RoPE.  The reference rotates every gathered key by its position j in the query's candidate list
+//    (src/parallel.py:687-692).  With j = 16*a + c (parent slot a, child index c) and rotations composing additively,
+//        (R(p) q)^T (R(j) k) = (R(p - 16a) q)^T (R(c) k),
+//    and c = node % 16 does not depend on the query.  The tree build therefore also stores K' = R(node % 16) K once
+//    per level, and this kernel rotates the QUERY once per parent (by p - 16a) while keys go from memory straight
+//    into B fragments.  Both operands see exactly one rounding, as in a direct evaluation; that rounding is to IEEE
+//    half for every storage type (K' is stored as half, the rotated query is packed as half), because half's 11-bit
+//    significand keeps the score noise 8x below bf16's and with it the rate of Top-K near-tie swaps.
+//  * Fragments are loaded so that no data movement is needed: the contraction index of the score product is
+//    permuted (thread r of a quad owns rotation pairs [P*r, P*(r+1)) of both halves), applied consistently to A and
+//    B; the value rows are loaded as 16-byte chunks and byte-permuted into k-major B fragments.
+//  * Upper levels run two passes over the candidates: pass 1 scores and stores only the shared importance
+//    (4 bytes per candidate in shared memory), an exact Top-K (bitwise search for the K-th largest key, ties to the
+//    smaller position, right-most forced) picks the kept set, pass 2 re-scores and accumulates the others.
+//    The leaf level is a single pass.  One running (max, sum, out) state spans all levels, which is the same
+//    softmax as the reference's per-level states merged afterwards (src/naive.py:215-223).
+#include "common.cuh"
+
+namespace htree {
+
+constexpr int MW = 4;   // warps (= queries) per block
+
+template <typename T> struct Frag;
+template <> struct Frag<__nv_bfloat16> {
+    static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+        return *reinterpret_cast<uint32_t*>(&h);
+    }
+    static __device__ __forceinline__ float2 unpack(uint32_t u) {
+        return make_float2(__uint_as_float(u << 16), __uint_as_float(u & 0xffff0000u));
+    }
+    static __device__ __forceinline__ void mma(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                     : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                     : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    }
+};
+template <> struct Frag<__half> {
+    static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
+        __half2 h = __floats2half2_rn(lo, hi);
+        return *reinterpret_cast<uint32_t*>(&h);
+    }
+    static __device__ __forceinline__ float2 unpack(uint32_t u) {
+        return __half22float2(*reinterpret_cast<__half2*>(&u));
+    }
+    static __device__ __forceinline__ void mma(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                     : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                     : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    }
+};
+
+__device__ __forceinline__ uint4 ldg16(const void* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
+__device__ __forceinline__ uint32_t word(const uint4& v, int i) { return i == 0 ? v.x : (i == 1 ? v.y : (i == 2 ? v.z : v.w)); }
+
+struct MmaSmem {   // per warp
+    float* imp;      // [maxc]   shared importance / its bit pattern
+    float* cmax;     // [TK]     per-chunk score maximum
+    uint32_t* selw;  // [maxc/32] kept-candidate bit mask
+    int32_t* par;    // [2][TK]
+};
+
+__host__ __device__ inline size_t mma_smem_per_warp(int TK, int CR) {
+    const size_t maxc = (size_t)TK * CR;
+    size_t b = sizeof(float) * maxc + sizeof(float) * TK + sizeof(uint32_t) * ((maxc + 31) / 32) + sizeof(int32_t) * 2 * TK;
+    return (b + 15) & ~size_t(15);
+}
+
+template <typename T, int D>
+__global__ void __launch_bounds__(MW * 32, 2) fwd_mma_kernel(const __grid_constant__ AttnParams p) {
+    constexpr int CR = 16;
+    constexpr int HALF = D / 2;
+    constexpr int KS = D / 16;        // k-steps of the score product
+    constexpr int PPT = HALF / 4;     // rotation pairs owned by one thread of a quad
+    constexpr int NV = PPT / 8;       // 16-byte loads per (row, half): 2 for D=128, 1 for D=64
+    constexpr int NHH = D / 64;       // 64-wide value column groups
+    constexpr int NOT = D / 8;        // n8 output tiles
+    using F = Frag<T>;          // P.V product: values stay in their storage type
+    using FS = Frag<__half>;    // score product: rotated queries and K' are IEEE half for every storage type
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, r = lane & 3;
+    const int tl = blockIdx.x * MW + warp;
+    if (tl >= p.Tq) return;                        // warps are independent: only __syncwarp below
+    const int t = p.t0 + tl;
+    const int b = blockIdx.y / p.Hkv, hk = blockIdx.y % p.Hkv;
+    const int G = p.G, TK = p.TK, L = p.L;
+    const int maxc = TK * CR;
+    unsigned char* wbase = smem_raw + (size_t)warp * mma_smem_per_warp(TK, CR);
+    float* imp = reinterpret_cast<float*>(wbase);
+    float* cmax = imp + maxc;
+    uint32_t* selw = reinterpret_cast<uint32_t*>(cmax + TK);
+    int32_t* par = reinterpret_cast<int32_t*>(selw + (maxc + 31) / 32);
+    int32_t* nxt = par + TK;
+
+    const bool select_only = (p.flags & HTREE_FWD_SELECT_ONLY) != 0;
+    const int64_t hbase = ((int64_t)b * p.Tq + tl) * p.H + (int64_t)hk * G;
+    const int64_t qidx = ((int64_t)b * p.Tq + tl) * p.Hkv + hk;
+    const bool row_ok[2] = {g < G, g + 8 < G};
+
+    // raw queries of rows g and g+8: pairs [PPT*r, PPT*(r+1)) of the low and of the high half
+    uint32_t qraw[2][2][KS];
+#pragma unroll
+    for (int rr = 0; rr < 2; ++rr) {
+        const T* qrow = reinterpret_cast<const T*>(p.q) + (hbase + g + 8 * rr) * D;
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf)
+#pragma unroll
+            for (int v = 0; v < NV; ++v) {
+                uint4 x = make_uint4(0, 0, 0, 0);
+                if (row_ok[rr]) x = ldg16(qrow + hf * HALF + PPT * r + 8 * v);
+                qraw[rr][hf][4 * v + 0] = x.x; qraw[rr][hf][4 * v + 1] = x.y;
+                qraw[rr][hf][4 * v + 2] = x.z; qraw[rr][hf][4 * v + 3] = x.w;
+            }
+    }
+
+    float O[NOT][4];
+#pragma unroll
+    for (int i = 0; i < NOT; ++i) { O[i][0] = O[i][1] = O[i][2] = O[i][3] = 0.f; }
+    float m_run[2] = {-1.0e30f, -1.0e30f}, s_run[2] = {0.f, 0.f};
+
+    {   // virtual parents of the top level (src/parallel.py:1026-1038)
+        int np0 = (int)(((int64_t)t / p.lpow[L - 1]) / CR) + 1;
+        if (np0 > TK) np0 = TK;
+        for (int i = lane; i < TK; i += 32) par[i] = i < np0 ? i : -1;
+    }
+    __syncwarp();
+
+    for (int l = L - 1; l >= 0; --l) {
+        const int Nl = p.ln[l];
+        const __half* lkr = reinterpret_cast<const __half*>(p.lkr[l]);
+        const T* lv = reinterpret_cast<const T*>(p.lv[l]);
+        if (p.parents[l]) for (int i = lane; i < TK; i += 32) p.parents[l][qidx * TK + i] = par[i];
+        if (select_only && l == 0) break;
+        int np = 0;
+        for (int i = lane; i < TK; i += 32) np += par[i] >= 0;
+        np = __reduce_add_sync(0xffffffffu, np);
+        const int rc = (int)(((int64_t)t / p.lpow[l]) % CR);
+        const int nc = (np - 1) * CR + rc + 1, rp = nc - 1;
+
+        // S0/S1 = scores of the 16 children of parent slot `a` against the 16 query rows
+        auto score_chunk = [&](int a, float (&S0)[4], float (&S1)[4]) {
+            const int delta = rp - CR * a;                         // query rotation for this parent slot
+            const float* cp = p.cosc + (size_t)delta * HALF + PPT * r;
+            const float* sp = p.sinc + (size_t)delta * HALF + PPT * r;
+            int node0 = par[a] * CR;
+            if (node0 < 0 || node0 >= Nl) { if (p.status) atomicOr(p.status, 4); node0 = 0; }
+            const int n0 = node0 + g, n1 = node0 + 8 + g;
+            const __half* k0 = lkr + (((int64_t)b * Nl + n0) * p.Hkv + hk) * D + PPT * r;
+            const __half* k1 = lkr + (((int64_t)b * Nl + n1) * p.Hkv + hk) * D + PPT * r;
+            uint32_t kb[2][2][KS];                                  // [tile][half][k-step]
+#pragma unroll
+            for (int hf = 0; hf < 2; ++hf)
+#pragma unroll
+                for (int v = 0; v < NV; ++v) {
+                    uint4 x = make_uint4(0, 0, 0, 0), y = make_uint4(0, 0, 0, 0);
+                    if (n0 < Nl) x = ldg16(k0 + hf * HALF + 8 * v);
+                    if (n1 < Nl) y = ldg16(k1 + hf * HALF + 8 * v);
+                    kb[0][hf][4 * v + 0] = x.x; kb[0][hf][4 * v + 1] = x.y; kb[0][hf][4 * v + 2] = x.z; kb[0][hf][4 * v + 3] = x.w;
+                    kb[1][hf][4 * v + 0] = y.x; kb[1][hf][4 * v + 1] = y.y; kb[1][hf][4 * v + 2] = y.z; kb[1][hf][4 * v + 3] = y.w;
+                }
+            S0[0] = S0[1] = S0[2] = S0[3] = 0.f;
+            S1[0] = S1[1] = S1[2] = S1[3] = 0.f;
+#pragma unroll
+            for (int ks2 = 0; ks2 < KS; ks2 += 2) {
+                const float4 c4 = __ldg(reinterpret_cast<const float4*>(cp + 2 * ks2));
+                const float4 s4 = __ldg(reinterpret_cast<const float4*>(sp + 2 * ks2));
+                const float cs[4] = {c4.x * p.scale, c4.y * p.scale, c4.z * p.scale, c4.w * p.scale};
+                const float sn[4] = {s4.x * p.scale, s4.y * p.scale, s4.z * p.scale, s4.w * p.scale};
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    const int ks = ks2 + u;
+                    uint32_t a[4];
+#pragma unroll
+                    for (int rr = 0; rr < 2; ++rr) {
+                        const float2 lo = F::unpack(qraw[rr][0][ks]), hi = F::unpack(qraw[rr][1][ks]);
+                        const float c0 = cs[2 * u], c1 = cs[2 * u + 1], s0 = sn[2 * u], s1 = sn[2 * u + 1];
+                        a[rr] = FS::pack(lo.x * c0 - hi.x * s0, lo.y * c1 - hi.y * s1);         // rotated low half
+                        a[2 + rr] = FS::pack(lo.x * s0 + hi.x * c0, lo.y * s1 + hi.y * c1);     // rotated high half
+                    }
+                    FS::mma(S0, a[0], a[1], a[2], a[3], kb[0][0][ks], kb[0][1][ks]);
+                    FS::mma(S1, a[0], a[1], a[2], a[3], kb[1][0][ks], kb[1][1][ks]);
+                }
+            }
+        };
+
+        // online-softmax accumulation of the columns in `mask` (bit c = child c of the parent at slot a)
+        auto accumulate_chunk = [&](int a, float (&S0)[4], float (&S1)[4], uint32_t mask) {
+            int node0 = par[a] * CR;
+            if (node0 < 0 || node0 >= Nl) node0 = 0;
+            const int col[4] = {2 * r, 2 * r + 1, 8 + 2 * r, 9 + 2 * r};
+            const bool cv[4] = {(mask >> col[0] & 1) != 0, (mask >> col[1] & 1) != 0, (mask >> col[2] & 1) != 0, (mask >> col[3] & 1) != 0};
+            // value rows first (longest latency): 16-byte chunk g of every 64-wide column group
+            uint4 vr[4][NHH];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const T* vrow = lv + (((int64_t)b * Nl + node0 + col[c]) * p.Hkv + hk) * D + 8 * g;
+#pragma unroll
+                for (int hh = 0; hh < NHH; ++hh) {
+                    vr[c][hh] = make_uint4(0, 0, 0, 0);
+                    if (cv[c]) vr[c][hh] = ldg16(vrow + 64 * hh);
+                }
+            }
+            const float NINF = -INFINITY;
+            float s[2][4];   // [row][tile0 c0, tile0 c1, tile1 c0, tile1 c1]
+            s[0][0] = (cv[0] && row_ok[0]) ? S0[0] : NINF; s[0][1] = (cv[1] && row_ok[0]) ? S0[1] : NINF;
+            s[0][2] = (cv[2] && row_ok[0]) ? S1[0] : NINF; s[0][3] = (cv[3] && row_ok[0]) ? S1[1] : NINF;
+            s[1][0] = (cv[0] && row_ok[1]) ? S0[2] : NINF; s[1][1] = (cv[1] && row_ok[1]) ? S0[3] : NINF;
+            s[1][2] = (cv[2] && row_ok[1]) ? S1[2] : NINF; s[1][3] = (cv[3] && row_ok[1]) ? S1[3] : NINF;
+            float mr[2];
+#pragma unroll
+            for (int rr = 0; rr < 2; ++rr) {
+                float m = fmaxf(fmaxf(s[rr][0], s[rr][1]), fmaxf(s[rr][2], s[rr][3]));
+                m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+                m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+                mr[rr] = m;
+            }
+            if (__any_sync(0xffffffffu, mr[0] > m_run[0] || mr[1] > m_run[1])) {
+                const float n0 = fmaxf(m_run[0], mr[0]), n1 = fmaxf(m_run[1], mr[1]);
+                const float a0 = __expf(m_run[0] - n0), a1 = __expf(m_run[1] - n1);
+                m_run[0] = n0; m_run[1] = n1;
+                s_run[0] *= a0; s_run[1] *= a1;
+#pragma unroll
+                for (int i = 0; i < NOT; ++i) { O[i][0] *= a0; O[i][1] *= a0; O[i][2] *= a1; O[i][3] *= a1; }
+            }
+            float pr[2][4];
+#pragma unroll
+            for (int rr = 0; rr < 2; ++rr)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    pr[rr][c] = __expf(s[rr][c] - m_run[rr]);
+                    s_run[rr] += pr[rr][c];
+                }
+            const uint32_t pa0 = F::pack(pr[0][0], pr[0][1]), pa1 = F::pack(pr[1][0], pr[1][1]);
+            const uint32_t pa2 = F::pack(pr[0][2], pr[0][3]), pa3 = F::pack(pr[1][2], pr[1][3]);
+#pragma unroll
+            for (int hh = 0; hh < NHH; ++hh)
+#pragma unroll
+                for (int w = 0; w < 8; ++w) {
+                    const uint32_t sel = (w & 1) ? 0x7632u : 0x5410u;
+                    const uint32_t b0 = __byte_perm(word(vr[0][hh], w >> 1), word(vr[1][hh], w >> 1), sel);
+                    const uint32_t b1 = __byte_perm(word(vr[2][hh], w >> 1), word(vr[3][hh], w >> 1), sel);
+                    F::mma(O[hh * 8 + w], pa0, pa1, pa2, pa3, b0, b1);
+                }
+        };
+
+        if (l > 0) {
+            if (nc <= TK) {   // every candidate is kept, nothing to score or accumulate
+                __syncwarp();
+                for (int j = lane; j < TK; j += 32) nxt[j] = j < nc ? par[j / CR] * CR + j % CR : -1;
+            } else {
+                // ---- pass 1: shared importance of every candidate ----
+                for (int a = 0; a < np; ++a) {
+                    float S0[4], S1[4];
+                    score_chunk(a, S0, S1);
+                    const int jb = a * CR;
+                    const bool cv[4] = {jb + 2 * r < nc, jb + 2 * r + 1 < nc, jb + 8 + 2 * r < nc, jb + 9 + 2 * r < nc};
+                    const float NINF = -INFINITY;
+                    float s[2][4];
+                    s[0][0] = (cv[0] && row_ok[0]) ? S0[0] : NINF; s[0][1] = (cv[1] && row_ok[0]) ? S0[1] : NINF;
+                    s[0][2] = (cv[2] && row_ok[0]) ? S1[0] : NINF; s[0][3] = (cv[3] && row_ok[0]) ? S1[1] : NINF;
+                    s[1][0] = (cv[0] && row_ok[1]) ? S0[2] : NINF; s[1][1] = (cv[1] && row_ok[1]) ? S0[3] : NINF;
+                    s[1][2] = (cv[2] && row_ok[1]) ? S1[2] : NINF; s[1][3] = (cv[3] && row_ok[1]) ? S1[3] : NINF;
+                    float cm = fmaxf(fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[0][2], s[0][3])),
+                                     fmaxf(fmaxf(s[1][0], s[1][1]), fmaxf(s[1][2], s[1][3])));
+                    cm = warp_max(cm);
+                    float e[4];
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        e[c] = __expf(s[0][c] - cm) + __expf(s[1][c] - cm);
+                        e[c] += __shfl_xor_sync(0xffffffffu, e[c], 4);
+                        e[c] += __shfl_xor_sync(0xffffffffu, e[c], 8);
+                        e[c] += __shfl_xor_sync(0xffffffffu, e[c], 16);
+                    }
+                    if (g == 0) {
+                        imp[jb + 2 * r] = e[0]; imp[jb + 2 * r + 1] = e[1];
+                        imp[jb + 8 + 2 * r] = e[2]; imp[jb + 9 + 2 * r] = e[3];
+                    }
+                    if (lane == 0) cmax[a] = cm;
+                }
+                __syncwarp();
+                // common reference maximum (src/naive.py:204-205), right-most candidate forced (src/naive.py:93)
+                float M = -INFINITY;
+                for (int a = lane; a < np; a += 32) M = fmaxf(M, cmax[a]);
+                M = warp_max(M);
+                for (int j = lane; j < nc; j += 32) {
+                    float v = imp[j] * __expf(cmax[j / CR] - M);
+                    if (j == rp) v = kForcedImportance;
+                    imp[j] = v;
+                }
+                __syncwarp();
+                // ---- exact Top-K: bitwise search for the TK-th largest key (keys are non-negative floats) ----
+                const uint32_t* key = reinterpret_cast<const uint32_t*>(imp);
+                uint32_t tau = 0;
+                for (int bit = 30; bit >= 0; --bit) {
+                    const uint32_t cand = tau | (1u << bit);
+                    int c = 0;
+                    for (int j = lane; j < nc; j += 32) c += key[j] >= cand;
+                    c = __reduce_add_sync(0xffffffffu, c);
+                    if (c >= TK) tau = cand;
+                }
+                int c_gt = 0;
+                for (int j = lane; j < nc; j += 32) c_gt += key[j] > tau;
+                c_gt = __reduce_add_sync(0xffffffffu, c_gt);
+                const int need = TK - c_gt;     // keys equal to tau that are kept: the smallest positions
+                int base_eq = 0, base_out = 0;
+                for (int j0 = 0; j0 < nc; j0 += 32) {
+                    const int j = j0 + lane;
+                    const uint32_t kx = j < nc ? key[j] : 0u;
+                    const bool gt = j < nc && kx > tau, eq = j < nc && kx == tau;
+                    const uint32_t meq = __ballot_sync(0xffffffffu, eq);
+                    const int eq_rank = base_eq + __popc(meq & ((1u << lane) - 1u));
+                    const bool keep = gt || (eq && eq_rank < need);
+                    const uint32_t mk = __ballot_sync(0xffffffffu, keep);
+                    if (keep) nxt[base_out + __popc(mk & ((1u << lane) - 1u))] = par[j / CR] * CR + j % CR;
+                    if (lane == 0) selw[j0 >> 5] = mk;
+                    base_eq += __popc(meq); base_out += __popc(mk);
+                }
+                for (int i = base_out + lane; i < TK; i += 32) nxt[i] = -1;
+                __syncwarp();
+                // ---- pass 2: accumulate what was not kept ----
+                if (!select_only) {
+                    for (int a = 0; a < np; ++a) {
+                        const uint32_t kept = (selw[a >> 1] >> (16 * (a & 1))) & 0xffffu;
+                        const uint32_t valid = a == np - 1 ? ((2u << rc) - 1u) : 0xffffu;
+                        const uint32_t mask = ~kept & valid;
+                        if (mask == 0) continue;
+                        float S0[4], S1[4];
+                        score_chunk(a, S0, S1);
+                        accumulate_chunk(a, S0, S1, mask);
+                    }
+                }
+            }
+            __syncwarp();
+            int32_t* tmp = par; par = nxt; nxt = tmp;
+        } else {
+            for (int a = 0; a < np; ++a) {
+                const uint32_t valid = a == np - 1 ? ((2u << rc) - 1u) : 0xffffu;
+                float S0[4], S1[4];
+                score_chunk(a, S0, S1);
+                accumulate_chunk(a, S0, S1, valid);
+            }
+        }
+    }
+    if (select_only) return;
+
+    // ---- epilogue: out = O / sum in the storage type; (gmax, gsum) for the backward ----
+#pragma unroll
+    for (int rr = 0; rr < 2; ++rr) {
+        s_run[rr] += __shfl_xor_sync(0xffffffffu, s_run[rr], 1);
+        s_run[rr] += __shfl_xor_sync(0xffffffffu, s_run[rr], 2);
+    }
+#pragma unroll
+    for (int rr = 0; rr < 2; ++rr) {
+        if (!row_ok[rr]) continue;
+        const float inv = 1.f / s_run[rr];
+        T* orow = reinterpret_cast<T*>(p.out) + (hbase + g + 8 * rr) * D;
+#pragma unroll
+        for (int hh = 0; hh < NHH; ++hh) {
+            // this thread owns columns 64*hh + 16*r + [0,16): c0 of tiles w=0..7, then c1 of tiles w=0..7
+            uint32_t w0[4], w1[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                w0[i] = F::pack(O[hh * 8 + 2 * i][2 * rr] * inv, O[hh * 8 + 2 * i + 1][2 * rr] * inv);
+                w1[i] = F::pack(O[hh * 8 + 2 * i][2 * rr + 1] * inv, O[hh * 8 + 2 * i + 1][2 * rr + 1] * inv);
+            }
+            uint4* dst = reinterpret_cast<uint4*>(orow + 64 * hh + 16 * r);
+            dst[0] = make_uint4(w0[0], w0[1], w0[2], w0[3]);
+            dst[1] = make_uint4(w1[0], w1[1], w1[2], w1[3]);
+        }
+        if (r == 0) { p.gmax[hbase + g + 8 * rr] = m_run[rr]; p.gsum[hbase + g + 8 * rr] = s_run[rr]; }
+    }
+}
+
+template <typename T, int D>
+static int launch_mma_td(const AttnParams& p, cudaStream_t st) {
+    const size_t smem = mma_smem_per_warp(p.TK, 16) * MW;
+    if (smem > 200 * 1024) return HTREE_E_UNSUPPORTED;
+    cudaError_t e = cudaFuncSetAttribute(fwd_mma_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    dim3 grid((p.Tq + MW - 1) / MW, p.B * p.Hkv);
+    fwd_mma_kernel<T, D><<<grid, MW * 32, smem, st>>>(p);
+    note_launch();
+    return (int)cudaGetLastError();
+}
+
+bool fwd_mma_supported(const AttnParams& p, int dtype) {
+    if (dtype != HTREE_BF16 && dtype != HTREE_F16) return false;
+    if (p.K != p.V || (p.K != 64 && p.K != 128)) return false;
+    if (p.G > 16 || p.CR != 16) return false;
+    for (int l = 0; l < p.L; ++l) if (!p.lkr[l]) return false;
+    return mma_smem_per_warp(p.TK, 16) * MW <= 200 * 1024;
+}
+
+int launch_fwd_mma(const AttnParams& p, int dtype, cudaStream_t st) {
+    if (dtype == HTREE_BF16) return p.K == 128 ? launch_mma_td<__nv_bfloat16, 128>(p, st) : launch_mma_td<__nv_bfloat16, 64>(p, st);
+    return p.K == 128 ? launch_mma_td<__half, 128>(p, st) : launch_mma_td<__half, 64>(p, st);
+}
+
+}  // namespace htree

@@ -129,6 +129,68 @@ int launch_tree_build(const HtreeShape& s, int L, const int32_t* ln, void* const
     }
 }
 
+struct RotArgs {
+    const void* src;
+    void* dst;
+    const float* cosc;
+    const float* sinc;
+    int64_t total;     // rows * (K/16): one thread rotates 8 pairs
+    int32_t Hkv, K, N, CR;
+};
+
+// K'[b, node, h, :] = R(node % CR) K[b, node, h, :] (half-split rotation by the child index), 16-bit storage types.
+// The tensor-core attention kernels read K' so that the per-candidate rotation of the reference
+// (src/parallel.py:687-692) turns into one query rotation per parent.
+// K' is always written as IEEE half, also for bf16 inputs: the rotated value is not representable in either type, and
+// half's 11-bit significand makes the one rounding 8x smaller than bf16's would be, which is what decides how often
+// Top-K boundary nodes swap against an fp32 evaluation.  Values are clamped to the finite half range.
+template <typename T>
+__global__ void __launch_bounds__(256) rotate_keys_kernel(const __grid_constant__ RotArgs a) {
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= a.total) return;
+    const int half = a.K >> 1, cpr = half >> 3;          // 8-pair chunks per row
+    const int ch = (int)(idx % cpr);
+    const int64_t row = idx / cpr;                        // (b * N + node) * Hkv + h
+    const int node = (int)((row / a.Hkv) % a.N);
+    const int c = node % a.CR;
+    const T* src = reinterpret_cast<const T*>(a.src) + row * a.K + 8 * ch;
+    __half* dst = reinterpret_cast<__half*>(a.dst) + row * a.K + 8 * ch;
+    float lo[8], hi[8], cs[8], sn[8];
+    unpack16<T>(__ldg(reinterpret_cast<const uint4*>(src)), lo);
+    unpack16<T>(__ldg(reinterpret_cast<const uint4*>(src + half)), hi);
+    const float4* cp = reinterpret_cast<const float4*>(a.cosc + (int64_t)c * half + 8 * ch);
+    const float4* sp = reinterpret_cast<const float4*>(a.sinc + (int64_t)c * half + 8 * ch);
+    const float4 c0 = __ldg(cp), c1 = __ldg(cp + 1), s0 = __ldg(sp), s1 = __ldg(sp + 1);
+    cs[0] = c0.x; cs[1] = c0.y; cs[2] = c0.z; cs[3] = c0.w; cs[4] = c1.x; cs[5] = c1.y; cs[6] = c1.z; cs[7] = c1.w;
+    sn[0] = s0.x; sn[1] = s0.y; sn[2] = s0.z; sn[3] = s0.w; sn[4] = s1.x; sn[5] = s1.y; sn[6] = s1.z; sn[7] = s1.w;
+    float olo[8], ohi[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        olo[i] = fminf(fmaxf(lo[i] * cs[i] - hi[i] * sn[i], -65504.f), 65504.f);
+        ohi[i] = fminf(fmaxf(lo[i] * sn[i] + hi[i] * cs[i], -65504.f), 65504.f);
+    }
+    *reinterpret_cast<uint4*>(dst) = pack16<__half>(olo);
+    *reinterpret_cast<uint4*>(dst + half) = pack16<__half>(ohi);
+}
+
+int launch_rotate_keys(const HtreeShape& s, int L, const int32_t* ln, void* const* lk, void* const* lkr, const float* cosc,
+                       const float* sinc, cudaStream_t st) {
+    if (s.dtype == HTREE_F32 || (s.K % 16) != 0) return HTREE_E_UNSUPPORTED;
+    for (int l = 0; l < L; ++l) {
+        RotArgs a;
+        a.src = lk[l]; a.dst = lkr[l]; a.cosc = cosc; a.sinc = sinc;
+        a.Hkv = s.H_kv; a.K = s.K; a.N = ln[l]; a.CR = s.compression_rate;
+        a.total = (int64_t)s.B * ln[l] * s.H_kv * (s.K / 16);
+        const unsigned grid = (unsigned)((a.total + 255) / 256);
+        if (s.dtype == HTREE_BF16) rotate_keys_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(a);
+        else rotate_keys_kernel<__half><<<grid, 256, 0, st>>>(a);
+        note_launch();
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return (int)e;
+    }
+    return 0;
+}
+
 struct TreeBwdArgs {
     const float* dparent[2];
     float* dchild[2];

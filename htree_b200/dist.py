@@ -121,6 +121,8 @@ def htree_forward_sequence_parallel(q_local: torch.Tensor, k: torch.Tensor, v: t
     L = len(configs.level_sizes(T, compression_rate, max_top_nodes))
     t0, t1 = query_range(T, world, rank, compression_rate, L) if world > 1 else (0, T)
     assert q_local.shape[1] == t1 - t0
-    layers = build_tree_sequence_parallel(k, v, compression_rate, max_top_nodes, group)
+    from .ops import rotate_keys
+    layers_k, layers_v = build_tree_sequence_parallel(k, v, compression_rate, max_top_nodes, group)
+    layers_kr = rotate_keys(layers_k, compression_rate, max_top_nodes, rope_base)   # local work on the gathered levels
     return htree_forward(q_local, k, v, compression_rate, max_top_nodes, top_k_per_layer, scale, rope_base,
-                         _q_offset=t0, _layers=layers)
+                         _q_offset=t0, _layers=(layers_k, layers_v, layers_kr))

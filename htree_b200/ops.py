@@ -115,8 +115,13 @@ def _ptrs(tensors) -> ctypes.Array:
     return _lib.ptr_array([t.data_ptr() if t is not None else None for t in tensors])
 
 
-def build_tree(k: torch.Tensor, v: torch.Tensor, compression_rate: int, max_top_nodes: int):
-    """Mean-pool tree (src/parallel.py:941-976).  Returns (layers_k, layers_v); level 0 are k and v themselves."""
+def build_tree(k: torch.Tensor, v: torch.Tensor, compression_rate: int, max_top_nodes: int,
+               rope_base: Optional[float] = None):
+    """Mean-pool tree (src/parallel.py:941-976).  Returns (layers_k, layers_v); level 0 are k and v themselves.
+
+    With `rope_base` given and a 16-bit storage type, a third list is returned: the keys of every level rotated by
+    their child index (node % compression_rate), which the tensor-core forward reads instead of layers_k.  These
+    are float16 tensors for bf16 inputs too (one rounding of the rotated value, with half's finer significand)."""
     k = k.contiguous(); v = v.contiguous()
     B, T, H_kv, K = k.shape
     V = v.shape[-1]
@@ -125,19 +130,45 @@ def build_tree(k: torch.Tensor, v: torch.Tensor, compression_rate: int, max_top_
     for n in sizes[1:]:
         layers_k.append(torch.empty(B, n, H_kv, K, dtype=k.dtype, device=k.device))
         layers_v.append(torch.empty(B, n, H_kv, V, dtype=v.dtype, device=v.device))
-    if len(sizes) > 1:
+    want_rot = rope_base is not None and k.dtype != torch.float32 and K % 16 == 0
+    layers_kr = [torch.empty(x.shape, dtype=torch.float16, device=x.device) for x in layers_k] if want_rot else None
+    if len(sizes) > 1 or want_rot:
         shape = _lib.HtreeShape(B, T, H_kv, H_kv, K, V, int(compression_rate), 1, int(max_top_nodes),
                                 _DTYPES[k.dtype])   # H and top_k play no role in the tree
+        cos_c = sin_c = None
+        if want_rot:
+            cos_c, sin_c = rope_cache(K, max(int(compression_rate), 16), rope_base, k.device)
         with torch.cuda.device(k.device):
-            _lib.check(_lib.lib().htree_b200_build_tree(ctypes.byref(shape), _ptrs(layers_k), _ptrs(layers_v),
-                                                        _stream()), "build_tree")
+            _lib.check(_lib.lib().htree_b200_build_tree(
+                ctypes.byref(shape), _ptrs(layers_k), _ptrs(layers_v), _ptrs(layers_kr) if want_rot else None,
+                cos_c.data_ptr() if want_rot else None, sin_c.data_ptr() if want_rot else None, _stream()),
+                "build_tree")
+    if rope_base is not None:
+        return layers_k, layers_v, layers_kr
     return layers_k, layers_v
 
 
-def _run_forward(shape, q, layers_k, layers_v, cos_cache, sin_cache, scale, out, gmax, gsum, parents, trace, flags):
+def rotate_keys(layers_k, compression_rate: int, max_top_nodes: int, rope_base: float):
+    """K' levels (keys rotated by their child index) for existing tree levels; None for fp32 or K % 16 != 0."""
+    k = layers_k[0]
+    B, T, H_kv, K = k.shape
+    if k.dtype == torch.float32 or K % 16:
+        return None
+    out = [torch.empty(x.shape, dtype=torch.float16, device=x.device) for x in layers_k]
+    shape = _lib.HtreeShape(B, T, H_kv, H_kv, K, K, int(compression_rate), 1, int(max_top_nodes), _DTYPES[k.dtype])
+    cos_c, sin_c = rope_cache(K, max(int(compression_rate), 16), rope_base, k.device)
+    with torch.cuda.device(k.device):
+        _lib.check(_lib.lib().htree_b200_rotate_keys(ctypes.byref(shape), _ptrs(layers_k), _ptrs(out),
+                                                     cos_c.data_ptr(), sin_c.data_ptr(), _stream()), "rotate_keys")
+    return out
+
+
+def _run_forward(shape, q, layers_k, layers_v, cos_cache, sin_cache, scale, out, gmax, gsum, parents, trace, flags,
+                 layers_kr=None):
     with torch.cuda.device(q.device):
         rc = _lib.lib().htree_b200_forward(
-            ctypes.byref(shape), q.data_ptr(), _ptrs(layers_k), _ptrs(layers_v), cos_cache.data_ptr(),
+            ctypes.byref(shape), q.data_ptr(), _ptrs(layers_k), _ptrs(layers_v),
+            _ptrs(layers_kr) if layers_kr is not None else None, cos_cache.data_ptr(),
             sin_cache.data_ptr(), cos_cache.shape[0], float(scale),
             out.data_ptr() if out is not None else None, gmax.data_ptr() if gmax is not None else None,
             gsum.data_ptr() if gsum is not None else None, _ptrs(parents) if parents is not None else None,
@@ -167,7 +198,11 @@ def htree_forward(
         scale = K ** -0.5
     q = q.contiguous(); k = k.contiguous(); v = v.contiguous()
     dev = q.device
-    layers_k, layers_v = _layers if _layers is not None else build_tree(k, v, compression_rate, max_top_nodes)
+    if _layers is not None:
+        layers_k, layers_v = _layers[0], _layers[1]
+        layers_kr = _layers[2] if len(_layers) > 2 else None
+    else:
+        layers_k, layers_v, layers_kr = build_tree(k, v, compression_rate, max_top_nodes, rope_base)
     L = len(layers_k)
     cos_cache, sin_cache = rope_cache(K, top_k_per_layer * compression_rate + 1024, rope_base, dev)
     out = torch.empty(B, T, H, V, dtype=q.dtype, device=dev)
@@ -183,7 +218,8 @@ def htree_forward(
               torch.empty(L, B, T, H, V, dtype=torch.float32, device=dev))
         trace = _lib.HtreeTrace(tr[0].data_ptr(), tr[1].data_ptr(), tr[2].data_ptr())
     flags = _lib.FWD_GENERIC if (_force_generic or return_trace) else 0
-    _run_forward(shape, q, layers_k, layers_v, cos_cache, sin_cache, scale, out, gmax, gsum, parents, trace, flags)
+    _run_forward(shape, q, layers_k, layers_v, cos_cache, sin_cache, scale, out, gmax, gsum, parents, trace, flags,
+                 layers_kr)
     if not (_save_for_backward or return_trace):
         return out
     result = [out]
@@ -192,7 +228,8 @@ def htree_forward(
         result.append(dict(
             global_max=gmax, global_sum=gsum,
             per_layer_parents={l: parents[l] for l in range(L)} if (_save_parents and parents is not None) else None,
-            layers_k=layers_k, layers_v=layers_v, cos_cache=cos_cache, sin_cache=sin_cache, num_layers=L,
+            layers_k=layers_k, layers_v=layers_v, layers_k_rot=layers_kr, cos_cache=cos_cache, sin_cache=sin_cache,
+            num_layers=L, rope_base=rope_base,
             compression_rate=compression_rate, top_k_per_layer=top_k_per_layer, max_top_nodes=max_top_nodes,
             scale=scale, NUM_GROUPS=G,
             # tuning constants of the reference's Triton kernels; kept so that code reading them keeps working
@@ -207,7 +244,7 @@ def htree_forward(
 
 
 def recompute_parents(q, layers_k, layers_v, cos_cache, sin_cache, compression_rate, top_k_per_layer,
-                      max_top_nodes, scale) -> Dict[int, torch.Tensor]:
+                      max_top_nodes, scale, layers_k_rot=None, _force_generic=False) -> Dict[int, torch.Tensor]:
     """Selection-only replay of the forward (the reference's _recompute_parents, src/backward.py:881-934)."""
     B, T, H, K = q.shape
     H_kv, V = layers_k[0].shape[2], layers_v[0].shape[-1]
@@ -216,7 +253,7 @@ def recompute_parents(q, layers_k, layers_v, cos_cache, sin_cache, compression_r
     L = len(layers_k)
     parents = [torch.empty(B, T, H_kv, top_k_per_layer, dtype=torch.int32, device=q.device) for _ in range(L)]
     _run_forward(shape, q.contiguous(), layers_k, layers_v, cos_cache, sin_cache, scale, None, None, None, parents,
-                 None, _lib.FWD_SELECT_ONLY)
+                 None, _lib.FWD_SELECT_ONLY | (_lib.FWD_GENERIC if _force_generic else 0), layers_k_rot)
     return {l: parents[l] for l in range(L)}
 
 
@@ -236,7 +273,8 @@ def htree_backward(dO: torch.Tensor, q: torch.Tensor, output: torch.Tensor, bwd_
     output = output.contiguous()
     parents = bwd_ctx.get("per_layer_parents")
     if parents is None:
-        parents = recompute_parents(q, layers_k, layers_v, cos_cache, sin_cache, CR, TK, MTN, scale)
+        parents = recompute_parents(q, layers_k, layers_v, cos_cache, sin_cache, CR, TK, MTN, scale,
+                                    bwd_ctx.get("layers_k_rot"))
     shape = _lib.HtreeShape(B, T, H, H_kv, K, V, int(CR), int(TK), int(MTN), _DTYPES[q.dtype])
     dq = torch.empty(B, T, H, K, dtype=torch.float32, device=dev)
     dk_levels = [torch.empty(x.shape, dtype=torch.float32, device=dev) for x in layers_k]
@@ -264,7 +302,7 @@ class HTreeFunction(torch.autograd.Function):
         ctx.save_for_backward(q, k, v, output, bwd_ctx["global_max"], bwd_ctx["global_sum"])
         ctx.bwd_ctx = bwd_ctx
         if not save:   # like the reference: drop the pooled levels and rebuild them in backward
-            bwd_ctx["layers_k"] = bwd_ctx["layers_v"] = None
+            bwd_ctx["layers_k"] = bwd_ctx["layers_v"] = bwd_ctx["layers_k_rot"] = None
         return output
 
     @staticmethod
@@ -272,7 +310,8 @@ class HTreeFunction(torch.autograd.Function):
         q, k, v, output, gmax, gsum = ctx.saved_tensors
         c = dict(ctx.bwd_ctx)
         if c["layers_k"] is None:
-            c["layers_k"], c["layers_v"] = build_tree(k, v, c["compression_rate"], c["max_top_nodes"])
+            c["layers_k"], c["layers_v"], c["layers_k_rot"] = build_tree(k, v, c["compression_rate"],
+                                                                         c["max_top_nodes"], c["rope_base"])
         dq, dk, dv = htree_backward(dO, q, output, c)
         return dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype), None, None, None, None, None
 

@@ -85,14 +85,30 @@ int htree_b200_level_sizes(int32_t T, int32_t compression_rate, int32_t max_top_
 
 /* Mean-pool tree build: replaces htree_build_kernel and its per-level launch loop (src/parallel.py:87-181, 955-976)
  * and _recompute_tree_build (src/backward.py:848-878).  layers_k[0]/layers_v[0] are the inputs k, v; levels
- * 1..L-1 are written (tail parents average only their valid children; fp32 accumulation, one rounding). */
-int htree_b200_build_tree(const HtreeShape* shape, void* const* layers_k, void* const* layers_v, void* stream);
+ * 1..L-1 are written (tail parents average only their valid children; fp32 accumulation, one rounding).
+ *   layers_k_rot  NULL, or L pointers to buffers shaped like layers_k (level 0 included) that receive
+ *                 K'[node] = R(node % compression_rate) K[node], the keys rotated by their child index with the
+ *                 half-split RoPE of src/parallel.py:687-692, stored as IEEE half for bf16 and fp16 inputs alike
+ *                 (clamped to the finite half range).  The tensor-core forward reads K' (16-bit storage
+ *                 types only; needs cos_cache/sin_cache with at least compression_rate rows, and K % 16 == 0).
+ *                 Pass NULL for fp32 or when only the generic kernels are wanted. */
+int htree_b200_build_tree(const HtreeShape* shape, void* const* layers_k, void* const* layers_v,
+                          void* const* layers_k_rot, const float* cos_cache, const float* sin_cache, void* stream);
+
+/* K' levels alone, from tree levels that already exist (e.g. levels assembled by an all-gather in sequence-sharded
+ * runs): layers_k_rot[l][node] = R(node % compression_rate) layers_k[l][node] for every level.  16-bit storage types
+ * only.  Same arithmetic as the rotation inside htree_b200_build_tree; no counterpart in the reference. */
+int htree_b200_rotate_keys(const HtreeShape* shape, void* const* layers_k, void* const* layers_k_rot,
+                           const float* cos_cache, const float* sin_cache, void* stream);
 
 /* Fused forward over all levels: replaces the per-level launches of htree_select_accumulate_gqa_kernel,
  * htree_bottom_accumulate_gqa_kernel, htree_merge_to_global_kernel and htree_final_normalize_kernel together with
  * the host-side state and virtual-parent initialisation (src/parallel.py:995-1134), and — with
  * HTREE_FWD_SELECT_ONLY — htree_recompute_selection_kernel / _recompute_parents (src/parallel.py:1167-1399,
  * src/backward.py:881-934).
+ *   layers_k_rot  NULL or the K' levels written by htree_b200_build_tree; when present (and the shape qualifies:
+ *                 bf16/fp16, K == V in {64,128}, H/H_kv <= 16, compression_rate 16) the tensor-core kernel runs,
+ *                 otherwise the generic fp32-arithmetic kernel
  *   cos_cache, sin_cache  [n_pos, K/2] fp32 RoPE tables (src/parallel.py:983-988); n_pos >= top_k*compression_rate
  *   out [B,T,H,V] in `dtype`; gmax, gsum [B,T,H] fp32 (global_max / global_sum of bwd_ctx)
  *   parents  NULL, or L pointers: parents[l] [B,T,H_kv,top_k] int32 receives the parent list CONSUMED at level l,
@@ -101,7 +117,7 @@ int htree_b200_build_tree(const HtreeShape* shape, void* const* layers_k, void* 
  *   status   NULL or one int32 on the device, OR-ed with a non-zero code if a kernel met an out-of-range node index
  */
 int htree_b200_forward(const HtreeShape* shape, const void* q, void* const* layers_k, void* const* layers_v,
-                       const float* cos_cache, const float* sin_cache, int32_t n_pos, float scale, void* out,
+                       void* const* layers_k_rot, const float* cos_cache, const float* sin_cache, int32_t n_pos, float scale, void* out,
                        float* gmax, float* gsum, int32_t* const* parents, const HtreeTrace* trace, int32_t* status,
                        uint32_t flags, void* stream);
 

@@ -225,3 +225,79 @@ def test_headline_cpu_case_full(dtype):
         r = gref[nm + "_f32"]
         tol = 1e-4 if dtype == "float32" else 2e-3      # bf16: gmax/gsum/out differ by storage rounding of out
         assert float(np.abs(parity.f32(t) - r).max()) <= tol * max(1.0, float(np.abs(r).max())), nm
+
+
+# ----------------------------------------------------------------------------------------------------------------
+# Tensor-core path (bf16/fp16, head_dim 64/128, compression_rate 16): scores are products of operands rounded to IEEE
+# half, so importances carry ~1e-4 relative noise and Top-K boundary nodes whose importances are closer than that may
+# swap (documented near-ties).  Measured on B200 with these cases: 98.9 % - 99.9 % of the groups select identical
+# node sets at every level, and every differing node lies within 8.1e-5 (relative) of the boundary importance; the
+# window below is 6x that.
+EPS_SEL_MMA = 5e-4
+
+MMA_CASES = {
+    "bf16_D64_G8_T3000": dict(B=1, T=3000, H=16, H_kv=2, K=64, V=64, CR=16, TK=8, MTN=100, dtype="bfloat16", seed=21),
+    "bf16_D128_G16_T2048": dict(B=2, T=2048, H=32, H_kv=2, K=128, V=128, CR=16, TK=16, MTN=256, dtype="bfloat16", seed=22),
+    "f16_D128_G4_T1500": dict(B=1, T=1500, H=4, H_kv=1, K=128, V=128, CR=16, TK=32, MTN=64, dtype="float16", seed=23),
+    "bf16_D128_G16_T6000_tk64": dict(B=1, T=6000, H=16, H_kv=1, K=128, V=128, CR=16, TK=64, MTN=128, dtype="bfloat16", seed=24),
+}
+
+
+@pytest.mark.parametrize("name", sorted(MMA_CASES))
+def test_tensor_core_forward_against_oracle(name):
+    ops = _ops()
+    c = MMA_CASES[name]
+    q, k, v, dO = parity.case_inputs(c)
+    out, ctx = ops.htree_forward(q.to(DEV), k.to(DEV), v.to(DEV), c["CR"], c["MTN"], c["TK"], _save_for_backward=True)
+    torch.cuda.synchronize(); ops.check_status()
+    assert ctx["layers_k_rot"] is not None
+    ref = oracle.forward(parity.f32(q), parity.f32(k), parity.f32(v), c["CR"], c["MTN"], c["TK"], dtype=c["dtype"],
+                         return_importance=True)
+    L = ctx["num_layers"]
+    assert L == ref["num_layers"]
+    ours_parents = [ctx["per_layer_parents"][l].cpu().numpy() for l in range(L)]
+    same, near = compare_with_oracle(c, q, k, v, ours_parents, ref, EPS_SEL_MMA)
+    G = c["H"] // c["H_kv"]
+    rows = np.repeat(same, G).reshape(c["B"], c["T"], c["H"])
+    frac_same = float(same.mean())
+    print(f"\n[{name}] groups with identical selections at every level: {frac_same:.4f}; near-tie rows: {near}")
+    assert frac_same > 0.97
+    o = parity.f32(out)
+    assert float(np.abs(o[rows] - ref["out_rounded"][rows]).max()) <= 2e-2       # bf16/fp16 bar: 2e-2 absolute
+    # groups whose selections differ by near-ties stay close too (reference protocol: p99 hard, max soft)
+    st = parity.err_stats(o, ref["out_rounded"])
+    assert st["p99"] <= 5e-3, st                      # hard criterion of correctness_test_bwd.py:257-264 for `out`
+    gm = parity.f32(ctx["global_max"]); gs = parity.f32(ctx["global_sum"])
+    assert np.allclose(gm[rows], ref["gmax"][rows], rtol=2e-2, atol=2e-2)
+    assert np.allclose(gs[rows], ref["gsum"][rows], rtol=3e-2, atol=1e-3)
+    # the generic kernel on the same inputs must agree with the tensor-core kernel to the same tolerance
+    out_g = ops.htree_forward(q.to(DEV), k.to(DEV), v.to(DEV), c["CR"], c["MTN"], c["TK"], _force_generic=True)
+    st2 = parity.err_stats(o, parity.f32(out_g))
+    assert st2["p99"] <= 2e-2, st2
+
+
+def test_tensor_core_selection_only_matches_full_forward():
+    ops = _ops()
+    c = MMA_CASES["bf16_D128_G16_T2048"]
+    q, k, v, _ = (x.to(DEV) for x in parity.case_inputs(c))
+    out, ctx = ops.htree_forward(q, k, v, c["CR"], c["MTN"], c["TK"], _save_for_backward=True)
+    again = ops.recompute_parents(q, ctx["layers_k"], ctx["layers_v"], ctx["cos_cache"], ctx["sin_cache"], c["CR"],
+                                  c["TK"], c["MTN"], ctx["scale"], ctx["layers_k_rot"])
+    for l in range(ctx["num_layers"]):
+        assert torch.equal(again[l], ctx["per_layer_parents"][l])
+
+
+def test_prerotated_keys_match_direct_rotation():
+    ops = _ops()
+    _, k, v, _ = parity.make_inputs(1, 700, 2, 2, 64, 64, "bfloat16", 31)
+    lk, lv, lkr = ops.build_tree(k.to(DEV), v.to(DEV), 16, 16, 10000.0)
+    cs, sn = oracle.rope_cache(64, 16)
+    for a, b in zip(lk, lkr):
+        x = parity.f32(a)
+        c = np.arange(x.shape[1]) % 16
+        lo, hi = x[..., :32], x[..., 32:]
+        co, si = cs[c][None, :, None, :], sn[c][None, :, None, :]
+        want = oracle.round_storage(np.concatenate([lo * co - hi * si, lo * si + hi * co], -1), "float16")
+        assert b.dtype == torch.float16
+        assert np.abs(parity.f32(b) - want).max() <= 4e-3      # at most one half ulp from contraction differences
+        assert (parity.f32(b) != want).mean() < 0.02
