@@ -74,7 +74,7 @@ def lib() -> ctypes.CDLL:
         L.htree_b200_forward.argtypes = [ctypes.POINTER(HtreeShape), vp, vp, vp, vp, vp, vp, i32, f32, vp, vp, vp, vp,
                                          ctypes.POINTER(HtreeTrace), vp, u32, vp]
         L.htree_b200_backward.restype = ctypes.c_int
-        L.htree_b200_backward.argtypes = [ctypes.POINTER(HtreeShape), vp, vp, vp, vp, vp, i32, f32, vp, vp, vp, vp, vp,
+        L.htree_b200_backward.argtypes = [ctypes.POINTER(HtreeShape), vp, vp, vp, vp, vp, vp, i32, f32, vp, vp, vp, vp, vp,
                                           vp, vp, vp, vp, u32, vp]
         _lib = L
     return _lib

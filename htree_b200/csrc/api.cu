@@ -176,7 +176,7 @@ int htree_b200_forward(const HtreeShape* shape, const void* q, void* const* laye
 }
 
 int htree_b200_backward(const HtreeShape* shape, const void* q, void* const* layers_k, void* const* layers_v,
-                        const float* cos_cache, const float* sin_cache, int32_t n_pos, float scale, const void* out,
+                        void* const* layers_k_rot, const float* cos_cache, const float* sin_cache, int32_t n_pos, float scale, const void* out,
                         const void* dO, const float* gmax, const float* gsum, int32_t* const* parents, float* dq,
                         float* const* dk_levels, float* const* dv_levels, int32_t* status, uint32_t flags,
                         void* stream) {
@@ -202,7 +202,15 @@ int htree_b200_backward(const HtreeShape* shape, const void* q, void* const* lay
     }
     p.out = const_cast<void*>(out); p.dO = dO; p.gmax = const_cast<float*>(gmax); p.gsum = const_cast<float*>(gsum);
     p.dq = dq;
-    rc = launch_bwd_generic(p, shape->dtype, st);
+    bool fast = layers_k_rot != nullptr && !(flags & HTREE_FWD_GENERIC);
+    if (fast) {
+        for (int l = 0; l < L; ++l) {
+            if (!layers_k_rot[l] || !aligned16(layers_k_rot[l])) fast = false;
+            p.lkr[l] = layers_k_rot[l];
+        }
+        fast = fast && aligned16(dO) && aligned16(out) && aligned16(dq) && bwd_mma_supported(p, shape->dtype);
+    }
+    rc = fast ? launch_bwd_mma(p, shape->dtype, st) : launch_bwd_generic(p, shape->dtype, st);
     if (rc) return rc;
     return launch_tree_backward(*shape, L, ln, dk_levels, dv_levels, st);
 }

@@ -1,0 +1,289 @@
+// Tensor-core backward for 16-bit storage types, head_dim 128: one WARP per (batch, query position, KV head) group,
+// all tree levels in one launch, operands gathered global/L2 -> registers -> mma.sync.
+//
+// Replaces htree_bwd_preprocess_delta_kernel, htree_bwd_dq_bottom/upper_kernel, htree_bwd_build_parent_mask_kernel and
+// htree_bwd_dkv_bottom/upper_kernel (src/backward.py:45-780) for bf16/fp16, K == V == 128, group <= 16,
+// compression_rate 16.  Arithmetic follows src/naive.py:376-386 with the forward's decomposition
+// S = (scale R(p-16a) q)^T K',  K' = R(node % 16) K  (see fwd_mma.cu).  For every accumulated chunk (the 16 children
+// of one parent, minus the children the next level kept):
+//   S   = q^_a K'^T                                    (score product, as in the forward)
+//   P   = exp(S - gmax) / gsum,  dP = dO V^T,  dS = P * (dP - D),  D = sum_v dO * out
+//   dq += scale * dS (R(16a-p) K')                     keys re-gathered row-wise, rotated back into q's frame
+//   dK[node] += R(c)^T (dS^T q^_a)                     one k16 product per 8 columns; fragments transposed with movmatrix
+//   dV[node] += P^T dO
+// dK/dV go to the fp32 level buffers with 16-byte vector reductions (red.global.add.v4.f32); dq stays in registers
+// across all levels and is written once.
+#include "mma_common.cuh"
+
+namespace htree {
+
+constexpr int MWB = 4;   // warps (= queries) per block
+
+__host__ __device__ inline size_t bwd_mma_smem_per_warp(int TK) { return sizeof(int32_t) * 3 * (size_t)TK; }
+
+template <typename T>
+__global__ void __launch_bounds__(MWB * 32, 2) bwd_mma_kernel(const __grid_constant__ AttnParams p) {
+    constexpr int D = 128, CR = 16, HALF = 64, KS = 8, PPT = 16, NOT = 16;
+    using F = Frag<T>;
+    using FS = Frag<__half>;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, r = lane & 3;
+    const int tl = blockIdx.x * MWB + warp;
+    if (tl >= p.T) return;                          // warps are independent (no block barrier anywhere)
+    const int t = tl;
+    const int b = blockIdx.y / p.Hkv, hk = blockIdx.y % p.Hkv;
+    const int G = p.G, TK = p.TK, L = p.L;
+    int32_t* par = reinterpret_cast<int32_t*>(smem_raw + (size_t)warp * bwd_mma_smem_per_warp(TK));
+    int32_t* nsel = par + TK;
+    uint32_t* keptw = reinterpret_cast<uint32_t*>(nsel + TK);
+
+    const int64_t hbase = ((int64_t)b * p.T + t) * p.H + (int64_t)hk * G;
+    const int64_t qidx = ((int64_t)b * p.T + t) * p.Hkv + hk;
+    const bool row_ok[2] = {g < G, g + 8 < G};
+
+    uint32_t qraw[2][2][KS], dOraw[2][2][KS];
+    load_rows<T, D>(reinterpret_cast<const T*>(p.q) + hbase * D, g, r, row_ok, qraw);
+    load_rows<T, D>(reinterpret_cast<const T*>(p.dO) + hbase * D, g, r, row_ok, dOraw);
+    float Drow[2], gmx[2], ginv[2];
+    {   // D = sum_v dO * out over the whole row (src/naive.py:333); this thread holds 32 of the 128 columns
+        uint32_t oraw[2][2][KS];
+        load_rows<T, D>(reinterpret_cast<const T*>(p.out) + hbase * D, g, r, row_ok, oraw);
+#pragma unroll
+        for (int rr = 0; rr < 2; ++rr) {
+            float s = 0.f;
+#pragma unroll
+            for (int hf = 0; hf < 2; ++hf)
+#pragma unroll
+                for (int ks = 0; ks < KS; ++ks) {
+                    const float2 a = F::unpack(dOraw[rr][hf][ks]), o = F::unpack(oraw[rr][hf][ks]);
+                    s += a.x * o.x + a.y * o.y;
+                }
+            s += __shfl_xor_sync(0xffffffffu, s, 1);
+            s += __shfl_xor_sync(0xffffffffu, s, 2);
+            Drow[rr] = s;
+            gmx[rr] = row_ok[rr] ? p.gmax[hbase + g + 8 * rr] : 0.f;
+            ginv[rr] = row_ok[rr] ? 1.f / p.gsum[hbase + g + 8 * rr] : 0.f;
+        }
+    }
+
+    float dqa[NOT][4];   // dq of rows g, g+8; tile (hh, w) column n <-> dim 64*hh + 8*n + w
+#pragma unroll
+    for (int i = 0; i < NOT; ++i) { dqa[i][0] = dqa[i][1] = dqa[i][2] = dqa[i][3] = 0.f; }
+
+    for (int l = L - 1; l >= 0; --l) {
+        const int Nl = p.ln[l];
+        const __half* lkr = reinterpret_cast<const __half*>(p.lkr[l]);
+        const T* lv = reinterpret_cast<const T*>(p.lv[l]);
+        float* dkl = p.dk[l];
+        float* dvl = p.dv[l];
+        __syncwarp();
+        for (int i = lane; i < TK; i += 32) {
+            par[i] = p.parents[l][qidx * TK + i];
+            nsel[i] = l > 0 ? p.parents[l - 1][qidx * TK + i] : -1;
+            keptw[i] = 0u;
+        }
+        __syncwarp();
+        int np = 0;
+        for (int i = lane; i < TK; i += 32) np += par[i] >= 0;
+        np = __reduce_add_sync(0xffffffffu, np);
+        if (np <= 0) continue;
+        // children the next level kept: bit c of keptw[a] for node = par[a]*16 + c (both lists ascending)
+        for (int i = lane; i < TK; i += 32) {
+            const int node = nsel[i];
+            if (node < 0) continue;
+            const int parent = node / CR;
+            int lo = 0, hi = np;
+            while (lo < hi) { const int mid = (lo + hi) >> 1; if (par[mid] < parent) lo = mid + 1; else hi = mid; }
+            if (lo < np && par[lo] == parent) atomicOr(&keptw[lo], 1u << (node % CR));
+        }
+        __syncwarp();
+        const int rc = (int)(((int64_t)t / p.lpow[l]) % CR);
+        const int rp = (np - 1) * CR + rc;
+
+        for (int a = 0; a < np; ++a) {
+            const uint32_t valid = a == np - 1 ? ((2u << rc) - 1u) : 0xffffu;
+            const uint32_t mask = ~keptw[a] & valid;
+            if (mask == 0) continue;
+            int node0 = par[a] * CR;
+            if (node0 < 0 || node0 >= Nl) { if (p.status) atomicOr(p.status, 8); node0 = 0; }
+            const int delta = rp - CR * a;
+            const int col[4] = {2 * r, 2 * r + 1, 8 + 2 * r, 9 + 2 * r};
+            const bool cv[4] = {(mask >> col[0] & 1) != 0, (mask >> col[1] & 1) != 0, (mask >> col[2] & 1) != 0, (mask >> col[3] & 1) != 0};
+
+            // ---- S and the rotated-query fragments ----
+            float S0[4], S1[4];
+            uint32_t qa[KS][4];
+            score_chunk<T, D, true>(p, lkr, Nl, b, hk, node0, delta, g, r, qraw, S0, S1, qa);
+
+            // ---- dP = dO V^T: value rows in the same (column n = child, permuted contraction) fragment order ----
+            float dP0[4] = {0.f, 0.f, 0.f, 0.f}, dP1[4] = {0.f, 0.f, 0.f, 0.f};
+            {
+                const int n0 = node0 + g, n1 = node0 + 8 + g;
+                const T* v0 = lv + (((int64_t)b * Nl + n0) * p.Hkv + hk) * D + PPT * r;
+                const T* v1 = lv + (((int64_t)b * Nl + n1) * p.Hkv + hk) * D + PPT * r;
+                uint32_t vb[2][2][KS];
+#pragma unroll
+                for (int hf = 0; hf < 2; ++hf)
+#pragma unroll
+                    for (int v = 0; v < 2; ++v) {
+                        uint4 x = make_uint4(0, 0, 0, 0), y = make_uint4(0, 0, 0, 0);
+                        if (n0 < Nl) x = ldg16(v0 + hf * HALF + 8 * v);
+                        if (n1 < Nl) y = ldg16(v1 + hf * HALF + 8 * v);
+                        vb[0][hf][4 * v + 0] = x.x; vb[0][hf][4 * v + 1] = x.y; vb[0][hf][4 * v + 2] = x.z; vb[0][hf][4 * v + 3] = x.w;
+                        vb[1][hf][4 * v + 0] = y.x; vb[1][hf][4 * v + 1] = y.y; vb[1][hf][4 * v + 2] = y.z; vb[1][hf][4 * v + 3] = y.w;
+                    }
+#pragma unroll
+                for (int ks = 0; ks < KS; ++ks) {
+                    F::mma(dP0, dOraw[0][0][ks], dOraw[1][0][ks], dOraw[0][1][ks], dOraw[1][1][ks], vb[0][0][ks], vb[0][1][ks]);
+                    F::mma(dP1, dOraw[0][0][ks], dOraw[1][0][ks], dOraw[0][1][ks], dOraw[1][1][ks], vb[1][0][ks], vb[1][1][ks]);
+                }
+            }
+
+            // ---- P and dS (src/naive.py:379-382), zero outside the accumulated set ----
+            float P[2][4], dS[2][4];   // [row][tile0 c0, tile0 c1, tile1 c0, tile1 c1]
+            {
+                const float s[2][4] = {{S0[0], S0[1], S1[0], S1[1]}, {S0[2], S0[3], S1[2], S1[3]}};
+                const float dp[2][4] = {{dP0[0], dP0[1], dP1[0], dP1[1]}, {dP0[2], dP0[3], dP1[2], dP1[3]}};
+#pragma unroll
+                for (int rr = 0; rr < 2; ++rr)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        const bool on = cv[c] && row_ok[rr];
+                        P[rr][c] = on ? __expf(s[rr][c] - gmx[rr]) * ginv[rr] : 0.f;
+                        dS[rr][c] = on ? P[rr][c] * (dp[rr][c] - Drow[rr]) : 0.f;
+                    }
+            }
+            // A fragments of dS (heads x children) and, transposed with movmatrix, of dS^T and P^T (children x heads)
+            const uint32_t ds0 = FS::pack(dS[0][0], dS[0][1]), ds1 = FS::pack(dS[1][0], dS[1][1]);
+            const uint32_t ds2 = FS::pack(dS[0][2], dS[0][3]), ds3 = FS::pack(dS[1][2], dS[1][3]);
+            const uint32_t dst0 = movmatrix_trans(ds0), dst1 = movmatrix_trans(ds2);
+            const uint32_t dst2 = movmatrix_trans(ds1), dst3 = movmatrix_trans(ds3);
+            const uint32_t pt0 = movmatrix_trans(F::pack(P[0][0], P[0][1])), pt1 = movmatrix_trans(F::pack(P[0][2], P[0][3]));
+            const uint32_t pt2 = movmatrix_trans(F::pack(P[1][0], P[1][1])), pt3 = movmatrix_trans(F::pack(P[1][2], P[1][3]));
+
+            // ---- dq += scale * dS (R(-delta) K'): keys row-wise (16-byte chunk g of both halves), rotated back ----
+            {
+                const float* cp = p.cosc + (size_t)delta * HALF + 8 * g;
+                const float* sp = p.sinc + (size_t)delta * HALF + 8 * g;
+                const float4 c0 = __ldg(reinterpret_cast<const float4*>(cp)), c1 = __ldg(reinterpret_cast<const float4*>(cp + 4));
+                const float4 s0 = __ldg(reinterpret_cast<const float4*>(sp)), s1 = __ldg(reinterpret_cast<const float4*>(sp + 4));
+                const float cs[8] = {c0.x * p.scale, c0.y * p.scale, c0.z * p.scale, c0.w * p.scale,
+                                     c1.x * p.scale, c1.y * p.scale, c1.z * p.scale, c1.w * p.scale};
+                const float sn[8] = {s0.x * p.scale, s0.y * p.scale, s0.z * p.scale, s0.w * p.scale,
+                                     s1.x * p.scale, s1.y * p.scale, s1.z * p.scale, s1.w * p.scale};
+                uint32_t klo[4][4], khi[4][4];   // [child of this thread][packed pairs] after the rotation
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const __half* krow = lkr + (((int64_t)b * Nl + node0 + col[c]) * p.Hkv + hk) * D + 8 * g;
+                    uint4 x = make_uint4(0, 0, 0, 0), y = make_uint4(0, 0, 0, 0);
+                    if (cv[c]) { x = ldg16(krow); y = ldg16(krow + HALF); }
+                    const uint32_t xw[4] = {x.x, x.y, x.z, x.w}, yw[4] = {y.x, y.y, y.z, y.w};
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float2 lo = FS::unpack(xw[i]), hi = FS::unpack(yw[i]);
+                        klo[c][i] = FS::pack(lo.x * cs[2 * i] + hi.x * sn[2 * i], lo.y * cs[2 * i + 1] + hi.y * sn[2 * i + 1]);
+                        khi[c][i] = FS::pack(hi.x * cs[2 * i] - lo.x * sn[2 * i], hi.y * cs[2 * i + 1] - lo.y * sn[2 * i + 1]);
+                    }
+                }
+#pragma unroll
+                for (int w = 0; w < 8; ++w) {
+                    const uint32_t sel = (w & 1) ? 0x7632u : 0x5410u;
+                    FS::mma(dqa[w], ds0, ds1, ds2, ds3, __byte_perm(klo[0][w >> 1], klo[1][w >> 1], sel),
+                            __byte_perm(klo[2][w >> 1], klo[3][w >> 1], sel));
+                    FS::mma(dqa[8 + w], ds0, ds1, ds2, ds3, __byte_perm(khi[0][w >> 1], khi[1][w >> 1], sel),
+                            __byte_perm(khi[2][w >> 1], khi[3][w >> 1], sel));
+                }
+            }
+
+            // ---- dK[node0 + c] += R(c)^T (dS^T q^_a) and dV[node0 + c] += P^T dO, rows c = g and g + 8 ----
+            const bool rowc[2] = {(mask >> g & 1) != 0, (mask >> (g + 8) & 1) != 0};
+            float* dkrow[2];
+            float* dvrow[2];
+#pragma unroll
+            for (int rr = 0; rr < 2; ++rr) {
+                const int64_t off = (((int64_t)b * Nl + node0 + g + 8 * rr) * p.Hkv + hk) * D + PPT * r;
+                dkrow[rr] = dkl + off;
+                dvrow[rr] = dvl + off;
+            }
+            const float* ccp[2] = {p.cosc + (size_t)g * HALF + PPT * r, p.cosc + (size_t)(g + 8) * HALF + PPT * r};
+            const float* csp[2] = {p.sinc + (size_t)g * HALF + PPT * r, p.sinc + (size_t)(g + 8) * HALF + PPT * r};
+#pragma unroll
+            for (int ks2 = 0; ks2 < KS; ks2 += 2) {
+                float klo_[2][4], khi_[2][4], vlo_[2][4], vhi_[2][4];   // [row][4 consecutive columns 2*ks2 .. 2*ks2+3]
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    const int ks = ks2 + u;
+                    float tl_[4] = {0.f, 0.f, 0.f, 0.f}, th_[4] = {0.f, 0.f, 0.f, 0.f};
+                    FS::mma(tl_, dst0, dst1, dst2, dst3, movmatrix_trans(qa[ks][0]), movmatrix_trans(qa[ks][1]));
+                    FS::mma(th_, dst0, dst1, dst2, dst3, movmatrix_trans(qa[ks][2]), movmatrix_trans(qa[ks][3]));
+                    klo_[0][2 * u] = tl_[0]; klo_[0][2 * u + 1] = tl_[1]; klo_[1][2 * u] = tl_[2]; klo_[1][2 * u + 1] = tl_[3];
+                    khi_[0][2 * u] = th_[0]; khi_[0][2 * u + 1] = th_[1]; khi_[1][2 * u] = th_[2]; khi_[1][2 * u + 1] = th_[3];
+                    float ul_[4] = {0.f, 0.f, 0.f, 0.f}, uh_[4] = {0.f, 0.f, 0.f, 0.f};
+                    F::mma(ul_, pt0, pt1, pt2, pt3, movmatrix_trans(dOraw[0][0][ks]), movmatrix_trans(dOraw[1][0][ks]));
+                    F::mma(uh_, pt0, pt1, pt2, pt3, movmatrix_trans(dOraw[0][1][ks]), movmatrix_trans(dOraw[1][1][ks]));
+                    vlo_[0][2 * u] = ul_[0]; vlo_[0][2 * u + 1] = ul_[1]; vlo_[1][2 * u] = ul_[2]; vlo_[1][2 * u + 1] = ul_[3];
+                    vhi_[0][2 * u] = uh_[0]; vhi_[0][2 * u + 1] = uh_[1]; vhi_[1][2 * u] = uh_[2]; vhi_[1][2 * u + 1] = uh_[3];
+                }
+#pragma unroll
+                for (int rr = 0; rr < 2; ++rr) {
+                    if (!rowc[rr]) continue;
+                    const float4 c4 = __ldg(reinterpret_cast<const float4*>(ccp[rr] + 2 * ks2));
+                    const float4 s4 = __ldg(reinterpret_cast<const float4*>(csp[rr] + 2 * ks2));
+                    const float cs[4] = {c4.x, c4.y, c4.z, c4.w}, sn[4] = {s4.x, s4.y, s4.z, s4.w};
+                    float lo[4], hi[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {   // inverse rotation by the child index (src/naive.py:31-38)
+                        lo[i] = klo_[rr][i] * cs[i] + khi_[rr][i] * sn[i];
+                        hi[i] = khi_[rr][i] * cs[i] - klo_[rr][i] * sn[i];
+                    }
+                    red_add_v4(dkrow[rr] + 2 * ks2, lo[0], lo[1], lo[2], lo[3]);
+                    red_add_v4(dkrow[rr] + HALF + 2 * ks2, hi[0], hi[1], hi[2], hi[3]);
+                    red_add_v4(dvrow[rr] + 2 * ks2, vlo_[rr][0], vlo_[rr][1], vlo_[rr][2], vlo_[rr][3]);
+                    red_add_v4(dvrow[rr] + HALF + 2 * ks2, vhi_[rr][0], vhi_[rr][1], vhi_[rr][2], vhi_[rr][3]);
+                }
+            }
+        }
+    }
+
+    // ---- dq: this thread owns columns 64*hh + 16*r + [0,16) of rows g and g+8 ----
+#pragma unroll
+    for (int rr = 0; rr < 2; ++rr) {
+        if (!row_ok[rr]) continue;
+        float* dqrow = p.dq + (hbase + g + 8 * rr) * D;
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+            float4* dst = reinterpret_cast<float4*>(dqrow + 64 * hh + 16 * r);
+            dst[0] = make_float4(dqa[hh * 8 + 0][2 * rr], dqa[hh * 8 + 1][2 * rr], dqa[hh * 8 + 2][2 * rr], dqa[hh * 8 + 3][2 * rr]);
+            dst[1] = make_float4(dqa[hh * 8 + 4][2 * rr], dqa[hh * 8 + 5][2 * rr], dqa[hh * 8 + 6][2 * rr], dqa[hh * 8 + 7][2 * rr]);
+            dst[2] = make_float4(dqa[hh * 8 + 0][2 * rr + 1], dqa[hh * 8 + 1][2 * rr + 1], dqa[hh * 8 + 2][2 * rr + 1], dqa[hh * 8 + 3][2 * rr + 1]);
+            dst[3] = make_float4(dqa[hh * 8 + 4][2 * rr + 1], dqa[hh * 8 + 5][2 * rr + 1], dqa[hh * 8 + 6][2 * rr + 1], dqa[hh * 8 + 7][2 * rr + 1]);
+        }
+    }
+}
+
+bool bwd_mma_supported(const AttnParams& p, int dtype) {
+    if (dtype != HTREE_BF16 && dtype != HTREE_F16) return false;
+    if (p.K != 128 || p.V != 128 || p.G > 16 || p.CR != 16) return false;
+    for (int l = 0; l < p.L; ++l) if (!p.lkr[l]) return false;
+    return bwd_mma_smem_per_warp(p.TK) * MWB <= 200 * 1024;
+}
+
+int launch_bwd_mma(const AttnParams& p, int dtype, cudaStream_t st) {
+    const size_t smem = bwd_mma_smem_per_warp(p.TK) * MWB;
+    dim3 grid((p.T + MWB - 1) / MWB, p.B * p.Hkv);
+    cudaError_t e;
+    if (dtype == HTREE_BF16) {
+        e = cudaFuncSetAttribute(bwd_mma_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        bwd_mma_kernel<__nv_bfloat16><<<grid, MWB * 32, smem, st>>>(p);
+    } else {
+        e = cudaFuncSetAttribute(bwd_mma_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        bwd_mma_kernel<__half><<<grid, MWB * 32, smem, st>>>(p);
+    }
+    note_launch();
+    return (int)cudaGetLastError();
+}
+
+}  // namespace htree

@@ -112,6 +112,8 @@ int launch_rotate_keys(const HtreeShape& s, int L, const int32_t* ln, void* cons
 int launch_fwd_generic(const AttnParams& p, int dtype, cudaStream_t st);
 bool fwd_mma_supported(const AttnParams& p, int dtype);
 int launch_fwd_mma(const AttnParams& p, int dtype, cudaStream_t st);
+bool bwd_mma_supported(const AttnParams& p, int dtype);
+int launch_bwd_mma(const AttnParams& p, int dtype, cudaStream_t st);
 int launch_bwd_generic(const AttnParams& p, int dtype, cudaStream_t st);
 
 }  // namespace htree

@@ -25,46 +25,11 @@
 //    smaller position, right-most forced) picks the kept set, pass 2 re-scores and accumulates the others.
 //    The leaf level is a single pass.  One running (max, sum, out) state spans all levels, which is the same
 //    softmax as the reference's per-level states merged afterwards (src/naive.py:215-223).
-#include "common.cuh"
+#include "mma_common.cuh"
 
 namespace htree {
 
 constexpr int MW = 4;   // warps (= queries) per block
-
-template <typename T> struct Frag;
-template <> struct Frag<__nv_bfloat16> {
-    static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
-        __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
-        return *reinterpret_cast<uint32_t*>(&h);
-    }
-    static __device__ __forceinline__ float2 unpack(uint32_t u) {
-        return make_float2(__uint_as_float(u << 16), __uint_as_float(u & 0xffff0000u));
-    }
-    static __device__ __forceinline__ void mma(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                               uint32_t b0, uint32_t b1) {
-        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-                     : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                     : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-    }
-};
-template <> struct Frag<__half> {
-    static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
-        __half2 h = __floats2half2_rn(lo, hi);
-        return *reinterpret_cast<uint32_t*>(&h);
-    }
-    static __device__ __forceinline__ float2 unpack(uint32_t u) {
-        return __half22float2(*reinterpret_cast<__half2*>(&u));
-    }
-    static __device__ __forceinline__ void mma(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                               uint32_t b0, uint32_t b1) {
-        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-                     : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                     : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-    }
-};
-
-__device__ __forceinline__ uint4 ldg16(const void* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
-__device__ __forceinline__ uint32_t word(const uint4& v, int i) { return i == 0 ? v.x : (i == 1 ? v.y : (i == 2 ? v.z : v.w)); }
 
 struct MmaSmem {   // per warp
     float* imp;      // [maxc]   shared importance / its bit pattern
@@ -113,19 +78,7 @@ __global__ void __launch_bounds__(MW * 32, 2) fwd_mma_kernel(const __grid_consta
 
     // raw queries of rows g and g+8: pairs [PPT*r, PPT*(r+1)) of the low and of the high half
     uint32_t qraw[2][2][KS];
-#pragma unroll
-    for (int rr = 0; rr < 2; ++rr) {
-        const T* qrow = reinterpret_cast<const T*>(p.q) + (hbase + g + 8 * rr) * D;
-#pragma unroll
-        for (int hf = 0; hf < 2; ++hf)
-#pragma unroll
-            for (int v = 0; v < NV; ++v) {
-                uint4 x = make_uint4(0, 0, 0, 0);
-                if (row_ok[rr]) x = ldg16(qrow + hf * HALF + PPT * r + 8 * v);
-                qraw[rr][hf][4 * v + 0] = x.x; qraw[rr][hf][4 * v + 1] = x.y;
-                qraw[rr][hf][4 * v + 2] = x.z; qraw[rr][hf][4 * v + 3] = x.w;
-            }
-    }
+    load_rows<T, D>(reinterpret_cast<const T*>(p.q) + hbase * D, g, r, row_ok, qraw);
 
     float O[NOT][4];
 #pragma unroll
@@ -152,49 +105,11 @@ __global__ void __launch_bounds__(MW * 32, 2) fwd_mma_kernel(const __grid_consta
         const int nc = (np - 1) * CR + rc + 1, rp = nc - 1;
 
         // S0/S1 = scores of the 16 children of parent slot `a` against the 16 query rows
-        auto score_chunk = [&](int a, float (&S0)[4], float (&S1)[4]) {
-            const int delta = rp - CR * a;                         // query rotation for this parent slot
-            const float* cp = p.cosc + (size_t)delta * HALF + PPT * r;
-            const float* sp = p.sinc + (size_t)delta * HALF + PPT * r;
+        auto score = [&](int a, float (&S0)[4], float (&S1)[4]) {
             int node0 = par[a] * CR;
             if (node0 < 0 || node0 >= Nl) { if (p.status) atomicOr(p.status, 4); node0 = 0; }
-            const int n0 = node0 + g, n1 = node0 + 8 + g;
-            const __half* k0 = lkr + (((int64_t)b * Nl + n0) * p.Hkv + hk) * D + PPT * r;
-            const __half* k1 = lkr + (((int64_t)b * Nl + n1) * p.Hkv + hk) * D + PPT * r;
-            uint32_t kb[2][2][KS];                                  // [tile][half][k-step]
-#pragma unroll
-            for (int hf = 0; hf < 2; ++hf)
-#pragma unroll
-                for (int v = 0; v < NV; ++v) {
-                    uint4 x = make_uint4(0, 0, 0, 0), y = make_uint4(0, 0, 0, 0);
-                    if (n0 < Nl) x = ldg16(k0 + hf * HALF + 8 * v);
-                    if (n1 < Nl) y = ldg16(k1 + hf * HALF + 8 * v);
-                    kb[0][hf][4 * v + 0] = x.x; kb[0][hf][4 * v + 1] = x.y; kb[0][hf][4 * v + 2] = x.z; kb[0][hf][4 * v + 3] = x.w;
-                    kb[1][hf][4 * v + 0] = y.x; kb[1][hf][4 * v + 1] = y.y; kb[1][hf][4 * v + 2] = y.z; kb[1][hf][4 * v + 3] = y.w;
-                }
-            S0[0] = S0[1] = S0[2] = S0[3] = 0.f;
-            S1[0] = S1[1] = S1[2] = S1[3] = 0.f;
-#pragma unroll
-            for (int ks2 = 0; ks2 < KS; ks2 += 2) {
-                const float4 c4 = __ldg(reinterpret_cast<const float4*>(cp + 2 * ks2));
-                const float4 s4 = __ldg(reinterpret_cast<const float4*>(sp + 2 * ks2));
-                const float cs[4] = {c4.x * p.scale, c4.y * p.scale, c4.z * p.scale, c4.w * p.scale};
-                const float sn[4] = {s4.x * p.scale, s4.y * p.scale, s4.z * p.scale, s4.w * p.scale};
-#pragma unroll
-                for (int u = 0; u < 2; ++u) {
-                    const int ks = ks2 + u;
-                    uint32_t a[4];
-#pragma unroll
-                    for (int rr = 0; rr < 2; ++rr) {
-                        const float2 lo = F::unpack(qraw[rr][0][ks]), hi = F::unpack(qraw[rr][1][ks]);
-                        const float c0 = cs[2 * u], c1 = cs[2 * u + 1], s0 = sn[2 * u], s1 = sn[2 * u + 1];
-                        a[rr] = FS::pack(lo.x * c0 - hi.x * s0, lo.y * c1 - hi.y * s1);         // rotated low half
-                        a[2 + rr] = FS::pack(lo.x * s0 + hi.x * c0, lo.y * s1 + hi.y * c1);     // rotated high half
-                    }
-                    FS::mma(S0, a[0], a[1], a[2], a[3], kb[0][0][ks], kb[0][1][ks]);
-                    FS::mma(S1, a[0], a[1], a[2], a[3], kb[1][0][ks], kb[1][1][ks]);
-                }
-            }
+            uint32_t unused[1][4];
+            score_chunk<T, D, false>(p, lkr, Nl, b, hk, node0, rp - CR * a, g, r, qraw, S0, S1, unused);
         };
 
         // online-softmax accumulation of the columns in `mask` (bit c = child c of the parent at slot a)
@@ -265,7 +180,7 @@ __global__ void __launch_bounds__(MW * 32, 2) fwd_mma_kernel(const __grid_consta
                 // ---- pass 1: shared importance of every candidate ----
                 for (int a = 0; a < np; ++a) {
                     float S0[4], S1[4];
-                    score_chunk(a, S0, S1);
+                    score(a, S0, S1);
                     const int jb = a * CR;
                     const bool cv[4] = {jb + 2 * r < nc, jb + 2 * r + 1 < nc, jb + 8 + 2 * r < nc, jb + 9 + 2 * r < nc};
                     const float NINF = -INFINITY;
@@ -339,7 +254,7 @@ __global__ void __launch_bounds__(MW * 32, 2) fwd_mma_kernel(const __grid_consta
                         const uint32_t mask = ~kept & valid;
                         if (mask == 0) continue;
                         float S0[4], S1[4];
-                        score_chunk(a, S0, S1);
+                        score(a, S0, S1);
                         accumulate_chunk(a, S0, S1, mask);
                     }
                 }
@@ -350,7 +265,7 @@ __global__ void __launch_bounds__(MW * 32, 2) fwd_mma_kernel(const __grid_consta
             for (int a = 0; a < np; ++a) {
                 const uint32_t valid = a == np - 1 ? ((2u << rc) - 1u) : 0xffffu;
                 float S0[4], S1[4];
-                score_chunk(a, S0, S1);
+                score(a, S0, S1);
                 accumulate_chunk(a, S0, S1, valid);
             }
         }

@@ -1,0 +1,127 @@
+// Pieces shared by the tensor-core forward and backward kernels: mma.sync fragments for both 16-bit storage types,
+// 16-byte gathers, and the score product of one parent's 16 children against the (<= 16) query heads of a group.
+#pragma once
+#include "common.cuh"
+
+namespace htree {
+
+template <typename T> struct Frag;
+template <> struct Frag<__nv_bfloat16> {
+    static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+        return *reinterpret_cast<uint32_t*>(&h);
+    }
+    static __device__ __forceinline__ float2 unpack(uint32_t u) {
+        return make_float2(__uint_as_float(u << 16), __uint_as_float(u & 0xffff0000u));
+    }
+    static __device__ __forceinline__ void mma(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                     : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                     : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    }
+};
+template <> struct Frag<__half> {
+    static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
+        __half2 h = __floats2half2_rn(lo, hi);
+        return *reinterpret_cast<uint32_t*>(&h);
+    }
+    static __device__ __forceinline__ float2 unpack(uint32_t u) {
+        return __half22float2(*reinterpret_cast<__half2*>(&u));
+    }
+    static __device__ __forceinline__ void mma(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                     : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                     : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    }
+};
+
+__device__ __forceinline__ uint4 ldg16(const void* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
+__device__ __forceinline__ uint32_t word(const uint4& v, int i) { return i == 0 ? v.x : (i == 1 ? v.y : (i == 2 ? v.z : v.w)); }
+
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+    uint32_t d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(d) : "r"(a));
+    return d;
+}
+
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};\n" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+// Scores of the 16 children of one parent (two n8 tiles: children 0-7 and 8-15) against query rows g and g+8 of the
+// group, S = (scale * R(delta) q)^T K'.  Thread (g = lane/4, r = lane%4) owns rotation pairs [PPT*r, PPT*(r+1)) of
+// both halves for the contraction (a permutation applied to A and B alike), so keys go from memory to B fragments
+// untouched and the query is rotated in registers.  With KEEP_A the rotated-query A fragments of every k-step are
+// returned as well (the backward reuses them, transposed, for dK).
+//   S0/S1: accumulators of tile 0 / tile 1: [0],[1] = row g, children 2r, 2r+1; [2],[3] = row g+8.
+template <typename T, int D, bool KEEP_A>
+__device__ __forceinline__ void score_chunk(const AttnParams& p, const __half* lkr, int Nl, int b, int hk, int node0, int delta,
+                                            int g, int r, const uint32_t (&qraw)[2][2][D / 16], float (&S0)[4], float (&S1)[4],
+                                            uint32_t (&qa)[KEEP_A ? D / 16 : 1][4]) {
+    constexpr int HALF = D / 2, KS = D / 16, PPT = HALF / 4, NV = PPT / 8;
+    using F = Frag<T>;
+    using FS = Frag<__half>;
+    const float* cp = p.cosc + (size_t)delta * HALF + PPT * r;
+    const float* sp = p.sinc + (size_t)delta * HALF + PPT * r;
+    const int n0 = node0 + g, n1 = node0 + 8 + g;
+    const __half* k0 = lkr + (((int64_t)b * Nl + n0) * p.Hkv + hk) * D + PPT * r;
+    const __half* k1 = lkr + (((int64_t)b * Nl + n1) * p.Hkv + hk) * D + PPT * r;
+    uint32_t kb[2][2][KS];   // [tile][half][k-step]
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf)
+#pragma unroll
+        for (int v = 0; v < NV; ++v) {
+            uint4 x = make_uint4(0, 0, 0, 0), y = make_uint4(0, 0, 0, 0);
+            if (n0 < Nl) x = ldg16(k0 + hf * HALF + 8 * v);
+            if (n1 < Nl) y = ldg16(k1 + hf * HALF + 8 * v);
+            kb[0][hf][4 * v + 0] = x.x; kb[0][hf][4 * v + 1] = x.y; kb[0][hf][4 * v + 2] = x.z; kb[0][hf][4 * v + 3] = x.w;
+            kb[1][hf][4 * v + 0] = y.x; kb[1][hf][4 * v + 1] = y.y; kb[1][hf][4 * v + 2] = y.z; kb[1][hf][4 * v + 3] = y.w;
+        }
+    S0[0] = S0[1] = S0[2] = S0[3] = 0.f;
+    S1[0] = S1[1] = S1[2] = S1[3] = 0.f;
+#pragma unroll
+    for (int ks2 = 0; ks2 < KS; ks2 += 2) {
+        const float4 c4 = __ldg(reinterpret_cast<const float4*>(cp + 2 * ks2));
+        const float4 s4 = __ldg(reinterpret_cast<const float4*>(sp + 2 * ks2));
+        const float cs[4] = {c4.x * p.scale, c4.y * p.scale, c4.z * p.scale, c4.w * p.scale};
+        const float sn[4] = {s4.x * p.scale, s4.y * p.scale, s4.z * p.scale, s4.w * p.scale};
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int ks = ks2 + u;
+            uint32_t a[4];
+#pragma unroll
+            for (int rr = 0; rr < 2; ++rr) {
+                const float2 lo = F::unpack(qraw[rr][0][ks]), hi = F::unpack(qraw[rr][1][ks]);
+                const float c0 = cs[2 * u], c1 = cs[2 * u + 1], s0 = sn[2 * u], s1 = sn[2 * u + 1];
+                a[rr] = FS::pack(lo.x * c0 - hi.x * s0, lo.y * c1 - hi.y * s1);         // rotated low half
+                a[2 + rr] = FS::pack(lo.x * s0 + hi.x * c0, lo.y * s1 + hi.y * c1);     // rotated high half
+            }
+            if (KEEP_A) { qa[KEEP_A ? ks : 0][0] = a[0]; qa[KEEP_A ? ks : 0][1] = a[1]; qa[KEEP_A ? ks : 0][2] = a[2]; qa[KEEP_A ? ks : 0][3] = a[3]; }
+            FS::mma(S0, a[0], a[1], a[2], a[3], kb[0][0][ks], kb[0][1][ks]);
+            FS::mma(S1, a[0], a[1], a[2], a[3], kb[1][0][ks], kb[1][1][ks]);
+        }
+    }
+}
+
+// Raw rows g and g+8 of a [heads, D] block in the fragment order used above (zero for rows beyond the group).
+template <typename T, int D>
+__device__ __forceinline__ void load_rows(const T* base, int g, int r, const bool (&row_ok)[2], uint32_t (&raw)[2][2][D / 16]) {
+    constexpr int HALF = D / 2, PPT = HALF / 4, NV = PPT / 8;
+#pragma unroll
+    for (int rr = 0; rr < 2; ++rr) {
+        const T* row = base + (int64_t)(g + 8 * rr) * D;
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf)
+#pragma unroll
+            for (int v = 0; v < NV; ++v) {
+                uint4 x = make_uint4(0, 0, 0, 0);
+                if (row_ok[rr]) x = ldg16(row + hf * HALF + PPT * r + 8 * v);
+                raw[rr][hf][4 * v + 0] = x.x; raw[rr][hf][4 * v + 1] = x.y;
+                raw[rr][hf][4 * v + 2] = x.z; raw[rr][hf][4 * v + 3] = x.w;
+            }
+    }
+}
+
+}  // namespace htree

@@ -257,7 +257,7 @@ def recompute_parents(q, layers_k, layers_v, cos_cache, sin_cache, compression_r
     return {l: parents[l] for l in range(L)}
 
 
-def htree_backward(dO: torch.Tensor, q: torch.Tensor, output: torch.Tensor, bwd_ctx: dict):
+def htree_backward(dO: torch.Tensor, q: torch.Tensor, output: torch.Tensor, bwd_ctx: dict, _force_generic: bool = False):
     """Backward given the forward context; returns fp32 (dq, dk, dv) with the shapes of q, k, v
     (src/backward.py:941-1119).  If bwd_ctx['per_layer_parents'] is None the selections are rebuilt first."""
     B, T, H, K = q.shape
@@ -267,6 +267,7 @@ def htree_backward(dO: torch.Tensor, q: torch.Tensor, output: torch.Tensor, bwd_
     CR, TK, MTN = bwd_ctx["compression_rate"], bwd_ctx["top_k_per_layer"], bwd_ctx["max_top_nodes"]
     scale = bwd_ctx["scale"]
     cos_cache, sin_cache = bwd_ctx["cos_cache"], bwd_ctx["sin_cache"]
+    layers_kr = bwd_ctx.get("layers_k_rot")
     dev = q.device
     q = q.contiguous()
     dO = dO.contiguous().to(q.dtype)
@@ -281,11 +282,12 @@ def htree_backward(dO: torch.Tensor, q: torch.Tensor, output: torch.Tensor, bwd_
     dv_levels = [torch.empty(x.shape, dtype=torch.float32, device=dev) for x in layers_v]
     with torch.cuda.device(dev):
         rc = _lib.lib().htree_b200_backward(
-            ctypes.byref(shape), q.data_ptr(), _ptrs(layers_k), _ptrs(layers_v), cos_cache.data_ptr(),
+            ctypes.byref(shape), q.data_ptr(), _ptrs(layers_k), _ptrs(layers_v),
+            _ptrs(layers_kr) if layers_kr is not None else None, cos_cache.data_ptr(),
             sin_cache.data_ptr(), cos_cache.shape[0], float(scale), output.data_ptr(), dO.data_ptr(),
             bwd_ctx["global_max"].data_ptr(), bwd_ctx["global_sum"].data_ptr(),
             _ptrs([parents[l] for l in range(L)]), dq.data_ptr(), _ptrs(dk_levels), _ptrs(dv_levels),
-            _status(dev).data_ptr(), 0, _stream())
+            _status(dev).data_ptr(), _lib.FWD_GENERIC if _force_generic else 0, _stream())
     _lib.check(rc, "backward")
     return dq, dk_levels[0], dv_levels[0]
 

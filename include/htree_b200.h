@@ -44,7 +44,8 @@ extern "C" {
 
 /* forward flags */
 #define HTREE_FWD_SELECT_ONLY 1u /* rebuild the selections only: no V reads, no accumulation, out/gmax/gsum untouched */
-#define HTREE_FWD_GENERIC 2u     /* force the dtype-generic fp32-arithmetic kernel even where a tensor-core kernel exists */
+#define HTREE_FWD_GENERIC 2u     /* force the dtype-generic fp32-arithmetic kernel even where a tensor-core kernel exists
+                                    (also honoured by the backward) */
 
 /* Problem description shared by all entry points (mirrors the keyword arguments of htree_forward,
  * src/parallel.py:874-885). */
@@ -123,6 +124,8 @@ int htree_b200_forward(const HtreeShape* shape, const void* q, void* const* laye
 
 /* Backward: replaces htree_backward and every kernel it launches (preprocess_delta, dq_bottom/upper,
  * build_parent_mask, dkv_bottom/upper, tree_backward; src/backward.py:45-841, 941-1119).
+ *   layers_k_rot  NULL or the K' levels of htree_b200_build_tree: selects the tensor-core kernel where the shape
+ *                 qualifies (bf16/fp16, K == V == 128, H/H_kv <= 16, compression_rate 16), else the generic kernel
  *   out, dO [B,T,H,V] in `dtype`; gmax, gsum from the forward; parents[l] as written by the forward (required)
  *   dq [B,T,H,K] fp32 (written)
  *   dk_levels[l] [B,N_l,H_kv,K] fp32, dv_levels[l] [B,N_l,H_kv,V] fp32 for every level: zero-filled by this call,
@@ -130,7 +133,7 @@ int htree_b200_forward(const HtreeShape* shape, const void* q, void* const* laye
  *   scratch (the reference's dk_layers / dv_layers, src/backward.py:979-981).
  */
 int htree_b200_backward(const HtreeShape* shape, const void* q, void* const* layers_k, void* const* layers_v,
-                        const float* cos_cache, const float* sin_cache, int32_t n_pos, float scale, const void* out,
+                        void* const* layers_k_rot, const float* cos_cache, const float* sin_cache, int32_t n_pos, float scale, const void* out,
                         const void* dO, const float* gmax, const float* gsum, int32_t* const* parents, float* dq,
                         float* const* dk_levels, float* const* dv_levels, int32_t* status, uint32_t flags,
                         void* stream);
