@@ -93,16 +93,18 @@ def build_tree_sequence_parallel(k: torch.Tensor, v: torch.Tensor, compression_r
     if world == 1 or L == 1:
         return build_tree(k, v, compression_rate, max_top_nodes)
     t0, t1 = query_range(T, world, rank, compression_rate, L)
-    # pool the local slice down to exactly L levels: a limit of 1 node keeps pooling, then cut at L
-    lk, lv = build_tree(k[:, t0:t1].contiguous(), v[:, t0:t1].contiguous(), compression_rate, 1)
+    # pool the local slice to the same depth: its top level is this rank's share of the global top level
+    lk, lv = build_tree(k[:, t0:t1].contiguous(), v[:, t0:t1].contiguous(), compression_rate, sizes[-1] // world)
+    assert len(lk) == L
     layers_k, layers_v = [k], [v]
     for l in range(1, L):
         for src, dst in ((lk[l], layers_k), (lv[l], layers_v)):
             n_loc = src.shape[1]
             assert n_loc * world == sizes[l]
-            gathered = torch.empty((world,) + tuple(src.shape), dtype=src.dtype, device=src.device)
-            dist.all_gather_into_tensor(gathered, src.contiguous(), group=group)
+            gathered = torch.empty((world * B,) + tuple(src.shape[1:]), dtype=src.dtype, device=src.device)
+            dist.all_gather_into_tensor(gathered, src.contiguous(), group=group)   # rank-major along dim 0
             # [world, B, n_loc, H_kv, D] -> [B, world*n_loc, H_kv, D]
+            gathered = gathered.view(world, B, n_loc, H_kv, src.shape[-1])
             dst.append(gathered.permute(1, 0, 2, 3, 4).reshape(B, sizes[l], H_kv, src.shape[-1]).contiguous())
     return layers_k, layers_v
 
