@@ -26,6 +26,8 @@ SYMBOLS = (
     "htree_b200_rotate_keys",
     "htree_b200_forward",
     "htree_b200_backward",
+    "htree_b200_static_scratch_bytes",
+    "htree_b200_backward_static_scratch",
 )
 
 
@@ -76,6 +78,10 @@ def lib() -> ctypes.CDLL:
         L.htree_b200_backward.restype = ctypes.c_int
         L.htree_b200_backward.argtypes = [ctypes.POINTER(HtreeShape), vp, vp, vp, vp, vp, vp, i32, f32, vp, vp, vp, vp, vp,
                                           vp, vp, vp, vp, u32, vp]
+        L.htree_b200_static_scratch_bytes.restype = ctypes.c_size_t
+        L.htree_b200_backward_static_scratch.restype = ctypes.c_int
+        L.htree_b200_backward_static_scratch.argtypes = [ctypes.POINTER(HtreeShape), vp, vp, vp, vp, vp, vp, i32, f32, vp,
+                                                         vp, vp, vp, vp, vp, vp, vp, vp, u32, vp]
         _lib = L
     return _lib
 

@@ -87,6 +87,7 @@ const char* htree_b200_error_string(int code) {
         case HTREE_E_UNSUPPORTED: return "shape not supported by the compiled kernels";
         case HTREE_E_NODEVICE: return "no usable CUDA device";
         case HTREE_E_WINDOW: return "query window outside the sequence, or a window passed to the backward";
+        case HTREE_E_SCRATCH: return "pooled tree levels do not fit the built-in scratch array (see htree_b200_static_scratch_bytes)";
         default: return code > 0 ? cudaGetErrorString((cudaError_t)code) : "unknown htree_b200 error";
     }
 }

@@ -41,6 +41,7 @@ extern "C" {
 #define HTREE_E_UNSUPPORTED (-8) /* shape outside what the kernels were built for (e.g. shared memory need) */
 #define HTREE_E_NODEVICE (-9)    /* no CUDA device / wrong architecture */
 #define HTREE_E_WINDOW (-10)     /* query window outside the sequence, or a window given to the backward */
+#define HTREE_E_SCRATCH (-11)    /* pooled-level accumulators exceed the library's built-in scratch array */
 
 /* forward flags */
 #define HTREE_FWD_SELECT_ONLY 1u /* rebuild the selections only: no V reads, no accumulation, out/gmax/gsum untouched */
@@ -137,6 +138,30 @@ int htree_b200_backward(const HtreeShape* shape, const void* q, void* const* lay
                         const void* dO, const float* gmax, const float* gsum, int32_t* const* parents, float* dq,
                         float* const* dk_levels, float* const* dv_levels, int32_t* status, uint32_t flags,
                         void* stream);
+
+/* Backward without caller-provided scratch.  No counterpart in the reference (its backward allocates its level
+ * buffers with torch, src/backward.py:979-981); it exists for callers that cannot allocate device memory around
+ * the call: a host program that reaches this library through a plain FFI and holds only the tensors its framework
+ * passed in, or a process whose device memory is fully reserved by a framework pool, or one that must not take the
+ * device-wide synchronisation of an allocation while other streams run.
+ *
+ * Same arguments and results as htree_b200_backward, except that only the outputs dk [B,T,H_kv,K] and
+ * dv [B,T,H_kv,V] (fp32) are passed: the accumulators of the pooled levels live in an array built into the library
+ * (htree_b200_static_scratch_bytes() bytes, 16 MiB, present in the memory of every GPU that loads the library until
+ * the process exits).  The call allocates nothing and frees nothing.
+ *   - Shapes whose pooled levels need more than that, sum over l >= 1 of B*N_l*H_kv*(K+V) floats (each level slice
+ *     rounded up to 64 floats), are rejected with HTREE_E_SCRATCH before anything is launched.
+ *   - The first call on a device looks up the array's device address (once per device, with that device current);
+ *     make that first call outside of any stream capture.
+ *   - All calls on one device share the array.  It keeps the previous call's contents; each call clears the part it
+ *     uses on its own stream before use.  Two calls that overlap on the GPU (different streams, or threads without
+ *     ordering between them) race on it: serialise them. */
+size_t htree_b200_static_scratch_bytes(void);
+int htree_b200_backward_static_scratch(const HtreeShape* shape, const void* q, void* const* layers_k,
+                                       void* const* layers_v, void* const* layers_k_rot, const float* cos_cache,
+                                       const float* sin_cache, int32_t n_pos, float scale, const void* out,
+                                       const void* dO, const float* gmax, const float* gsum, int32_t* const* parents,
+                                       float* dq, float* dk, float* dv, int32_t* status, uint32_t flags, void* stream);
 
 #ifdef __cplusplus
 }
