@@ -102,6 +102,7 @@ def cpu_oracle_leg(c: dict, seconds: float, steps: int = 1, warmup: int = 0):
     groups (t, kv head 0, batch 0) with t uniform over the sequence, all host threads.  Returns (tokens/s, info)."""
     from oracle import oracle
     oracle.build()
+    oracle.use_all_threads()
     T, D, G = c["T"], c["D"], c["H"] // c["H_kv"]
     rng = np.random.default_rng(42)
 
@@ -259,6 +260,10 @@ def main():
     barrier()
     clocks = sampler.stop() if sampler else None
     launches = _lib.launch_count() - launches0
+    if world > 1:
+        lt = torch.tensor([launches], device=dev, dtype=torch.float64)
+        tdist.all_reduce(lt)
+        launches = int(lt.item())
     ms_total = max_over_ranks(t_begin.elapsed_time(t_end))
     ms_step = ms_total / args.steps
     fwd_ms = max_over_ranks(statistics.mean(e[0].elapsed_time(e[1]) for e in ev))
@@ -328,7 +333,7 @@ def main():
             "data": "synthetic", "config": cfg_desc,
             "fwd_tokens_per_s": B * T / (fwd_ms * 1e-3), "roofline": roofline, "e2e": e2e,
             "gpu_launches": int(launches), "clocks": clocks}
-    if not args.no_cpu_baseline and world >= 1:
+    if not args.no_cpu_baseline and world == 1:
         tps, info = cpu_oracle_leg(c, args.cpu_seconds)
         line["cpu_baseline"] = {"value": tps, "unit": "tokens/s", "cores": info["cores"], "kind": info["kind"],
                                 "sample": info["sample"]}

@@ -8,7 +8,7 @@ import ctypes
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libhtree_b200.so")
+LIB_PATH = os.environ.get("HTREE_B200_LIB") or os.path.join(_HERE, "libhtree_b200.so")   # override: another build of the same ABI
 
 MAX_LEVELS = 12
 F32, BF16, F16 = 0, 1, 2
@@ -73,14 +73,14 @@ def lib() -> ctypes.CDLL:
         L.htree_b200_rotate_keys.restype = ctypes.c_int
         L.htree_b200_rotate_keys.argtypes = [ctypes.POINTER(HtreeShape), vp, vp, vp, vp, vp]
         L.htree_b200_forward.restype = ctypes.c_int
-        L.htree_b200_forward.argtypes = [ctypes.POINTER(HtreeShape), vp, vp, vp, vp, vp, vp, i32, f32, vp, vp, vp, vp,
+        L.htree_b200_forward.argtypes = [ctypes.POINTER(HtreeShape), vp, vp, vp, vp, vp, vp, vp, vp, i32, f32, vp, vp, vp, vp,
                                          ctypes.POINTER(HtreeTrace), vp, u32, vp]
         L.htree_b200_backward.restype = ctypes.c_int
-        L.htree_b200_backward.argtypes = [ctypes.POINTER(HtreeShape), vp, vp, vp, vp, vp, vp, i32, f32, vp, vp, vp, vp, vp,
+        L.htree_b200_backward.argtypes = [ctypes.POINTER(HtreeShape), vp, vp, vp, vp, vp, vp, vp, vp, i32, f32, vp, vp, vp, vp, vp,
                                           vp, vp, vp, vp, u32, vp]
         L.htree_b200_static_scratch_bytes.restype = ctypes.c_size_t
         L.htree_b200_backward_static_scratch.restype = ctypes.c_int
-        L.htree_b200_backward_static_scratch.argtypes = [ctypes.POINTER(HtreeShape), vp, vp, vp, vp, vp, vp, i32, f32, vp,
+        L.htree_b200_backward_static_scratch.argtypes = [ctypes.POINTER(HtreeShape), vp, vp, vp, vp, vp, vp, vp, vp, i32, f32, vp,
                                                          vp, vp, vp, vp, vp, vp, vp, vp, u32, vp]
         _lib = L
     return _lib

@@ -38,20 +38,23 @@ def _stale(target: str, deps) -> bool:
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
-    """Compile every .cu under csrc/ and link the shared library.  Returns its path."""
+def build(force: bool = False, verbose: bool = False, defines=(), out: str = LIB, obj_dir: str = OBJ_DIR) -> str:
+    """Compile every .cu under csrc/ and link the shared library.  Returns its path.
+    `defines` (e.g. ["HTREE_FWD_MIN_BLOCKS=3"]) with a separate `out`/`obj_dir` builds a tuning variant of the same ABI."""
     nvcc = _nvcc()
-    os.makedirs(OBJ_DIR, exist_ok=True)
+    LIB_, OBJ_DIR_ = out, obj_dir
+    os.makedirs(OBJ_DIR_, exist_ok=True)
     headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))]
     headers.append(os.path.join(HERE, "..", "include", "htree_b200.h"))
     srcs = sources()
-    objs = [os.path.join(OBJ_DIR, os.path.basename(s)[:-3] + ".o") for s in srcs]
+    objs = [os.path.join(OBJ_DIR_, os.path.basename(s)[:-3] + ".o") for s in srcs]
+    dflags = [f"-D{d}" for d in defines]
 
     def compile_one(pair):
         src, obj = pair
         if not (force or _stale(obj, [src] + headers)):
             return ""
-        r = subprocess.run([nvcc, *ARCH, *FLAGS, "-c", src, "-o", obj], capture_output=True, text=True)
+        r = subprocess.run([nvcc, *ARCH, *FLAGS, *dflags, "-c", src, "-o", obj], capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"nvcc failed on {src}:\n{r.stdout}\n{r.stderr}")
         return r.stderr
@@ -62,11 +65,11 @@ def build(force: bool = False, verbose: bool = False) -> str:
         for log in logs:
             if log:
                 print(log)
-    if force or _stale(LIB, objs):
-        r = subprocess.run([nvcc, *ARCH, "-shared", "-o", LIB, *objs, "-lcudart"], capture_output=True, text=True)
+    if force or _stale(LIB_, objs):
+        r = subprocess.run([nvcc, *ARCH, "-shared", "-o", LIB_, *objs, "-lcudart"], capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
-    return LIB
+    return LIB_
 
 
 if __name__ == "__main__":

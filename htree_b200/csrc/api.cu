@@ -147,7 +147,8 @@ int htree_b200_rotate_keys(const HtreeShape* shape, void* const* layers_k, void*
 }
 
 int htree_b200_forward(const HtreeShape* shape, const void* q, void* const* layers_k, void* const* layers_v,
-                       void* const* layers_k_rot, const float* cos_cache, const float* sin_cache, int32_t n_pos, float scale, void* out,
+                       void* const* layers_k_rot, const float* cos_cache, const float* sin_cache, const void* cos_half,
+                       const void* sin_half, int32_t n_pos, float scale, void* out,
                        float* gmax, float* gsum, int32_t* const* parents, const HtreeTrace* trace, int32_t* status,
                        uint32_t flags, void* stream) {
     int32_t ln[HTREE_MAX_LEVELS];
@@ -164,6 +165,9 @@ int htree_b200_forward(const HtreeShape* shape, const void* q, void* const* laye
         if (!aligned16(out)) return HTREE_E_ALIGN;
     }
     p.out = out; p.gmax = gmax; p.gsum = gsum;
+    if (cos_half && sin_half && aligned16(cos_half) && aligned16(sin_half)) {
+        p.cosh = static_cast<const __half*>(cos_half); p.sinh = static_cast<const __half*>(sin_half);
+    }
     if (trace) { p.tr_max = trace->layer_max; p.tr_sum = trace->layer_sum; p.tr_out = trace->layer_out; }
     if (layers_k_rot && !trace && !(flags & HTREE_FWD_GENERIC)) {
         bool all = true;
@@ -177,7 +181,8 @@ int htree_b200_forward(const HtreeShape* shape, const void* q, void* const* laye
 }
 
 int htree_b200_backward(const HtreeShape* shape, const void* q, void* const* layers_k, void* const* layers_v,
-                        void* const* layers_k_rot, const float* cos_cache, const float* sin_cache, int32_t n_pos, float scale, const void* out,
+                        void* const* layers_k_rot, const float* cos_cache, const float* sin_cache, const void* cos_half,
+                        const void* sin_half, int32_t n_pos, float scale, const void* out,
                         const void* dO, const float* gmax, const float* gsum, int32_t* const* parents, float* dq,
                         float* const* dk_levels, float* const* dv_levels, int32_t* status, uint32_t flags,
                         void* stream) {
@@ -203,6 +208,9 @@ int htree_b200_backward(const HtreeShape* shape, const void* q, void* const* lay
     }
     p.out = const_cast<void*>(out); p.dO = dO; p.gmax = const_cast<float*>(gmax); p.gsum = const_cast<float*>(gsum);
     p.dq = dq;
+    if (cos_half && sin_half && aligned16(cos_half) && aligned16(sin_half)) {
+        p.cosh = static_cast<const __half*>(cos_half); p.sinh = static_cast<const __half*>(sin_half);
+    }
     bool fast = layers_k_rot != nullptr && !(flags & HTREE_FWD_GENERIC);
     if (fast) {
         for (int l = 0; l < L; ++l) {

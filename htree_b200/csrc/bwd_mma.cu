@@ -18,11 +18,14 @@
 namespace htree {
 
 constexpr int MWB = 4;   // warps (= queries) per block
+#ifndef HTREE_BWD_MIN_BLOCKS
+#define HTREE_BWD_MIN_BLOCKS 2   // register budget: 2 blocks of 128 threads per SM (255 registers)
+#endif
 
 __host__ __device__ inline size_t bwd_mma_smem_per_warp(int TK) { return sizeof(int32_t) * 3 * (size_t)TK; }
 
-template <typename T>
-__global__ void __launch_bounds__(MWB * 32, 2) bwd_mma_kernel(const __grid_constant__ AttnParams p) {
+template <typename T, bool ROT16>
+__global__ void __launch_bounds__(MWB * 32, HTREE_BWD_MIN_BLOCKS) bwd_mma_kernel(const __grid_constant__ AttnParams p) {
     constexpr int D = 128, CR = 16, HALF = 64, KS = 8, PPT = 16, NOT = 16;
     using F = Frag<T>;
     using FS = Frag<__half>;
@@ -43,7 +46,8 @@ __global__ void __launch_bounds__(MWB * 32, 2) bwd_mma_kernel(const __grid_const
     const bool row_ok[2] = {g < G, g + 8 < G};
 
     uint32_t qraw[2][2][KS], dOraw[2][2][KS];
-    load_rows<T, D>(reinterpret_cast<const T*>(p.q) + hbase * D, g, r, row_ok, qraw);
+    load_rows_half<T, D>(reinterpret_cast<const T*>(p.q) + hbase * D, g, r, row_ok, qraw);
+    constexpr bool rot16 = ROT16;   // packed-half rotations (needs the pre-scaled half tables)
     load_rows<T, D>(reinterpret_cast<const T*>(p.dO) + hbase * D, g, r, row_ok, dOraw);
     float Drow[2], gmx[2], ginv[2];
     {   // D = sum_v dO * out over the whole row (src/naive.py:333); this thread holds 32 of the 128 columns
@@ -114,7 +118,8 @@ __global__ void __launch_bounds__(MWB * 32, 2) bwd_mma_kernel(const __grid_const
             // ---- S and the rotated-query fragments ----
             float S0[4], S1[4];
             uint32_t qa[KS][4];
-            score_chunk<T, D, true>(p, lkr, Nl, b, hk, node0, delta, g, r, qraw, S0, S1, qa);
+            if (rot16) score_chunk<D, true, true>(p, lkr, Nl, b, hk, node0, delta, g, r, qraw, S0, S1, qa);
+            else score_chunk<D, true, false>(p, lkr, Nl, b, hk, node0, delta, g, r, qraw, S0, S1, qa);
 
             // ---- dP = dO V^T: value rows in the same (column n = child, permuted contraction) fragment order ----
             float dP0[4] = {0.f, 0.f, 0.f, 0.f}, dP1[4] = {0.f, 0.f, 0.f, 0.f};
@@ -164,26 +169,47 @@ __global__ void __launch_bounds__(MWB * 32, 2) bwd_mma_kernel(const __grid_const
 
             // ---- dq += scale * dS (R(-delta) K'): keys row-wise (16-byte chunk g of both halves), rotated back ----
             {
-                const float* cp = p.cosc + (size_t)delta * HALF + 8 * g;
-                const float* sp = p.sinc + (size_t)delta * HALF + 8 * g;
-                const float4 c0 = __ldg(reinterpret_cast<const float4*>(cp)), c1 = __ldg(reinterpret_cast<const float4*>(cp + 4));
-                const float4 s0 = __ldg(reinterpret_cast<const float4*>(sp)), s1 = __ldg(reinterpret_cast<const float4*>(sp + 4));
-                const float cs[8] = {c0.x * p.scale, c0.y * p.scale, c0.z * p.scale, c0.w * p.scale,
-                                     c1.x * p.scale, c1.y * p.scale, c1.z * p.scale, c1.w * p.scale};
-                const float sn[8] = {s0.x * p.scale, s0.y * p.scale, s0.z * p.scale, s0.w * p.scale,
-                                     s1.x * p.scale, s1.y * p.scale, s1.z * p.scale, s1.w * p.scale};
                 uint32_t klo[4][4], khi[4][4];   // [child of this thread][packed pairs] after the rotation
+                if (rot16) {
+                    const uint4 cw = ldg16(p.cosh + (size_t)delta * HALF + 8 * g), sw = ldg16(p.sinh + (size_t)delta * HALF + 8 * g);
+                    const uint32_t cs[4] = {cw.x, cw.y, cw.z, cw.w}, sn[4] = {sw.x, sw.y, sw.z, sw.w};
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    const __half* krow = lkr + (((int64_t)b * Nl + node0 + col[c]) * p.Hkv + hk) * D + 8 * g;
-                    uint4 x = make_uint4(0, 0, 0, 0), y = make_uint4(0, 0, 0, 0);
-                    if (cv[c]) { x = ldg16(krow); y = ldg16(krow + HALF); }
-                    const uint32_t xw[4] = {x.x, x.y, x.z, x.w}, yw[4] = {y.x, y.y, y.z, y.w};
+                    for (int c = 0; c < 4; ++c) {
+                        const __half* krow = lkr + (((int64_t)b * Nl + node0 + col[c]) * p.Hkv + hk) * D + 8 * g;
+                        uint4 x = make_uint4(0, 0, 0, 0), y = make_uint4(0, 0, 0, 0);
+                        if (cv[c]) { x = ldg16(krow); y = ldg16(krow + HALF); }
+                        const uint32_t xw[4] = {x.x, x.y, x.z, x.w}, yw[4] = {y.x, y.y, y.z, y.w};
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const float2 lo = FS::unpack(xw[i]), hi = FS::unpack(yw[i]);
-                        klo[c][i] = FS::pack(lo.x * cs[2 * i] + hi.x * sn[2 * i], lo.y * cs[2 * i + 1] + hi.y * sn[2 * i + 1]);
-                        khi[c][i] = FS::pack(hi.x * cs[2 * i] - lo.x * sn[2 * i], hi.y * cs[2 * i + 1] - lo.y * sn[2 * i + 1]);
+                        for (int i = 0; i < 4; ++i) {
+                            const __half2 lo = *reinterpret_cast<const __half2*>(&xw[i]), hi = *reinterpret_cast<const __half2*>(&yw[i]);
+                            const __half2 c2 = *reinterpret_cast<const __half2*>(&cs[i]), s2 = *reinterpret_cast<const __half2*>(&sn[i]);
+                            const __half2 u = __hfma2(lo, c2, __hmul2(hi, s2));                 // lo*cos + hi*sin
+                            const __half2 w2 = __hfma2(hi, c2, __hneg2(__hmul2(lo, s2)));       // hi*cos - lo*sin
+                            klo[c][i] = *reinterpret_cast<const uint32_t*>(&u);
+                            khi[c][i] = *reinterpret_cast<const uint32_t*>(&w2);
+                        }
+                    }
+                } else {
+                    const float* cp = p.cosc + (size_t)delta * HALF + 8 * g;
+                    const float* sp = p.sinc + (size_t)delta * HALF + 8 * g;
+                    const float4 c0 = __ldg(reinterpret_cast<const float4*>(cp)), c1 = __ldg(reinterpret_cast<const float4*>(cp + 4));
+                    const float4 s0 = __ldg(reinterpret_cast<const float4*>(sp)), s1 = __ldg(reinterpret_cast<const float4*>(sp + 4));
+                    const float cs[8] = {c0.x * p.scale, c0.y * p.scale, c0.z * p.scale, c0.w * p.scale,
+                                         c1.x * p.scale, c1.y * p.scale, c1.z * p.scale, c1.w * p.scale};
+                    const float sn[8] = {s0.x * p.scale, s0.y * p.scale, s0.z * p.scale, s0.w * p.scale,
+                                         s1.x * p.scale, s1.y * p.scale, s1.z * p.scale, s1.w * p.scale};
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        const __half* krow = lkr + (((int64_t)b * Nl + node0 + col[c]) * p.Hkv + hk) * D + 8 * g;
+                        uint4 x = make_uint4(0, 0, 0, 0), y = make_uint4(0, 0, 0, 0);
+                        if (cv[c]) { x = ldg16(krow); y = ldg16(krow + HALF); }
+                        const uint32_t xw[4] = {x.x, x.y, x.z, x.w}, yw[4] = {y.x, y.y, y.z, y.w};
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const float2 lo = FS::unpack(xw[i]), hi = FS::unpack(yw[i]);
+                            klo[c][i] = FS::pack(lo.x * cs[2 * i] + hi.x * sn[2 * i], lo.y * cs[2 * i + 1] + hi.y * sn[2 * i + 1]);
+                            khi[c][i] = FS::pack(hi.x * cs[2 * i] - lo.x * sn[2 * i], hi.y * cs[2 * i + 1] - lo.y * sn[2 * i + 1]);
+                        }
                     }
                 }
 #pragma unroll
@@ -269,21 +295,21 @@ bool bwd_mma_supported(const AttnParams& p, int dtype) {
     return bwd_mma_smem_per_warp(p.TK) * MWB <= 200 * 1024;
 }
 
-int launch_bwd_mma(const AttnParams& p, int dtype, cudaStream_t st) {
+template <typename T, bool ROT16>
+static int launch_bwd_mma_t(const AttnParams& p, cudaStream_t st) {
     const size_t smem = bwd_mma_smem_per_warp(p.TK) * MWB;
     dim3 grid((p.T + MWB - 1) / MWB, p.B * p.Hkv);
-    cudaError_t e;
-    if (dtype == HTREE_BF16) {
-        e = cudaFuncSetAttribute(bwd_mma_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
-        bwd_mma_kernel<__nv_bfloat16><<<grid, MWB * 32, smem, st>>>(p);
-    } else {
-        e = cudaFuncSetAttribute(bwd_mma_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
-        bwd_mma_kernel<__half><<<grid, MWB * 32, smem, st>>>(p);
-    }
+    cudaError_t e = cudaFuncSetAttribute(bwd_mma_kernel<T, ROT16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    bwd_mma_kernel<T, ROT16><<<grid, MWB * 32, smem, st>>>(p);
     note_launch();
     return (int)cudaGetLastError();
+}
+
+int launch_bwd_mma(const AttnParams& p, int dtype, cudaStream_t st) {
+    const bool rot16 = p.cosh != nullptr && p.sinh != nullptr;
+    if (dtype == HTREE_BF16) return rot16 ? launch_bwd_mma_t<__nv_bfloat16, true>(p, st) : launch_bwd_mma_t<__nv_bfloat16, false>(p, st);
+    return rot16 ? launch_bwd_mma_t<__half, true>(p, st) : launch_bwd_mma_t<__half, false>(p, st);
 }
 
 }  // namespace htree

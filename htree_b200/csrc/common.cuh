@@ -23,6 +23,8 @@ struct AttnParams {
     int64_t lpow[HTREE_MAX_LEVELS]; // CR^l
     const float* cosc;
     const float* sinc;
+    const __half* cosh;   // optional: cos * scale and sin * scale as IEEE half, same shape as cosc/sinc
+    const __half* sinh;
     int32_t* parents[HTREE_MAX_LEVELS];  // may be all NULL in the forward
     int32_t* status;
     // forward outputs

@@ -30,6 +30,9 @@
 namespace htree {
 
 constexpr int MW = 4;   // warps (= queries) per block
+#ifndef HTREE_FWD_MIN_BLOCKS
+#define HTREE_FWD_MIN_BLOCKS 2   // register budget: 2 blocks of 128 threads per SM (255 registers)
+#endif
 
 struct MmaSmem {   // per warp
     float* imp;      // [maxc]   shared importance / its bit pattern
@@ -44,8 +47,8 @@ __host__ __device__ inline size_t mma_smem_per_warp(int TK, int CR) {
     return (b + 15) & ~size_t(15);
 }
 
-template <typename T, int D>
-__global__ void __launch_bounds__(MW * 32, 2) fwd_mma_kernel(const __grid_constant__ AttnParams p) {
+template <typename T, int D, bool ROT16>
+__global__ void __launch_bounds__(MW * 32, HTREE_FWD_MIN_BLOCKS) fwd_mma_kernel(const __grid_constant__ AttnParams p) {
     constexpr int CR = 16;
     constexpr int HALF = D / 2;
     constexpr int KS = D / 16;        // k-steps of the score product
@@ -78,7 +81,8 @@ __global__ void __launch_bounds__(MW * 32, 2) fwd_mma_kernel(const __grid_consta
 
     // raw queries of rows g and g+8: pairs [PPT*r, PPT*(r+1)) of the low and of the high half
     uint32_t qraw[2][2][KS];
-    load_rows<T, D>(reinterpret_cast<const T*>(p.q) + hbase * D, g, r, row_ok, qraw);
+    load_rows_half<T, D>(reinterpret_cast<const T*>(p.q) + hbase * D, g, r, row_ok, qraw);
+    constexpr bool rot16 = ROT16;   // packed-half rotation where the Top-K is not being decided
 
     float O[NOT][4];
 #pragma unroll
@@ -104,12 +108,14 @@ __global__ void __launch_bounds__(MW * 32, 2) fwd_mma_kernel(const __grid_consta
         const int rc = (int)(((int64_t)t / p.lpow[l]) % CR);
         const int nc = (np - 1) * CR + rc + 1, rp = nc - 1;
 
-        // S0/S1 = scores of the 16 children of parent slot `a` against the 16 query rows
-        auto score = [&](int a, float (&S0)[4], float (&S1)[4]) {
+        // S0/S1 = scores of the 16 children of parent slot `a` against the 16 query rows.  `select` = this pass
+        // decides the Top-K: the query is then always rotated in fp32.
+        auto score = [&](int a, float (&S0)[4], float (&S1)[4], bool select) {
             int node0 = par[a] * CR;
             if (node0 < 0 || node0 >= Nl) { if (p.status) atomicOr(p.status, 4); node0 = 0; }
             uint32_t unused[1][4];
-            score_chunk<T, D, false>(p, lkr, Nl, b, hk, node0, rp - CR * a, g, r, qraw, S0, S1, unused);
+            if (rot16 && !select) score_chunk<D, false, true>(p, lkr, Nl, b, hk, node0, rp - CR * a, g, r, qraw, S0, S1, unused);
+            else score_chunk<D, false, false>(p, lkr, Nl, b, hk, node0, rp - CR * a, g, r, qraw, S0, S1, unused);
         };
 
         // online-softmax accumulation of the columns in `mask` (bit c = child c of the parent at slot a)
@@ -180,7 +186,7 @@ __global__ void __launch_bounds__(MW * 32, 2) fwd_mma_kernel(const __grid_consta
                 // ---- pass 1: shared importance of every candidate ----
                 for (int a = 0; a < np; ++a) {
                     float S0[4], S1[4];
-                    score(a, S0, S1);
+                    score(a, S0, S1, true);
                     const int jb = a * CR;
                     const bool cv[4] = {jb + 2 * r < nc, jb + 2 * r + 1 < nc, jb + 8 + 2 * r < nc, jb + 9 + 2 * r < nc};
                     const float NINF = -INFINITY;
@@ -254,7 +260,7 @@ __global__ void __launch_bounds__(MW * 32, 2) fwd_mma_kernel(const __grid_consta
                         const uint32_t mask = ~kept & valid;
                         if (mask == 0) continue;
                         float S0[4], S1[4];
-                        score(a, S0, S1);
+                        score(a, S0, S1, false);
                         accumulate_chunk(a, S0, S1, mask);
                     }
                 }
@@ -265,7 +271,7 @@ __global__ void __launch_bounds__(MW * 32, 2) fwd_mma_kernel(const __grid_consta
             for (int a = 0; a < np; ++a) {
                 const uint32_t valid = a == np - 1 ? ((2u << rc) - 1u) : 0xffffu;
                 float S0[4], S1[4];
-                score(a, S0, S1);
+                score(a, S0, S1, false);
                 accumulate_chunk(a, S0, S1, valid);
             }
         }
@@ -300,16 +306,21 @@ __global__ void __launch_bounds__(MW * 32, 2) fwd_mma_kernel(const __grid_consta
     }
 }
 
-template <typename T, int D>
-static int launch_mma_td(const AttnParams& p, cudaStream_t st) {
+template <typename T, int D, bool ROT16>
+static int launch_mma_tdr(const AttnParams& p, cudaStream_t st) {
     const size_t smem = mma_smem_per_warp(p.TK, 16) * MW;
     if (smem > 200 * 1024) return HTREE_E_UNSUPPORTED;
-    cudaError_t e = cudaFuncSetAttribute(fwd_mma_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(fwd_mma_kernel<T, D, ROT16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     dim3 grid((p.Tq + MW - 1) / MW, p.B * p.Hkv);
-    fwd_mma_kernel<T, D><<<grid, MW * 32, smem, st>>>(p);
+    fwd_mma_kernel<T, D, ROT16><<<grid, MW * 32, smem, st>>>(p);
     note_launch();
     return (int)cudaGetLastError();
+}
+
+template <typename T, int D>
+static int launch_mma_td(const AttnParams& p, cudaStream_t st) {
+    return (p.cosh != nullptr && p.sinh != nullptr) ? launch_mma_tdr<T, D, true>(p, st) : launch_mma_tdr<T, D, false>(p, st);
 }
 
 bool fwd_mma_supported(const AttnParams& p, int dtype) {

@@ -1,6 +1,8 @@
 // Pieces shared by the tensor-core forward and backward kernels: mma.sync fragments for both 16-bit storage types,
 // 16-byte gathers, and the score product of one parent's 16 children against the (<= 16) query heads of a group.
 #pragma once
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace htree {
@@ -56,12 +58,14 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
 // untouched and the query is rotated in registers.  With KEEP_A the rotated-query A fragments of every k-step are
 // returned as well (the backward reuses them, transposed, for dK).
 //   S0/S1: accumulators of tile 0 / tile 1: [0],[1] = row g, children 2r, 2r+1; [2],[3] = row g+8.
-template <typename T, int D, bool KEEP_A>
+//   qraw holds the query rows as IEEE half pairs (load_rows_half).  ROT16 selects how the query is rotated: false =
+//   fp32 arithmetic with the fp32 tables, one rounding to half at the end; true = packed half2 arithmetic with the
+//   pre-scaled half tables (4 instead of 14 instructions per pair of pairs, about twice the rounding noise).
+template <int D, bool KEEP_A, bool ROT16>
 __device__ __forceinline__ void score_chunk(const AttnParams& p, const __half* lkr, int Nl, int b, int hk, int node0, int delta,
                                             int g, int r, const uint32_t (&qraw)[2][2][D / 16], float (&S0)[4], float (&S1)[4],
                                             uint32_t (&qa)[KEEP_A ? D / 16 : 1][4]) {
     constexpr int HALF = D / 2, KS = D / 16, PPT = HALF / 4, NV = PPT / 8;
-    using F = Frag<T>;
     using FS = Frag<__half>;
     const float* cp = p.cosc + (size_t)delta * HALF + PPT * r;
     const float* sp = p.sinc + (size_t)delta * HALF + PPT * r;
@@ -81,6 +85,35 @@ __device__ __forceinline__ void score_chunk(const AttnParams& p, const __half* l
         }
     S0[0] = S0[1] = S0[2] = S0[3] = 0.f;
     S1[0] = S1[1] = S1[2] = S1[3] = 0.f;
+    if (ROT16) {
+        const __half* chp = p.cosh + (size_t)delta * HALF + PPT * r;
+        const __half* shp = p.sinh + (size_t)delta * HALF + PPT * r;
+        uint32_t ch[KS], sh[KS];   // (cos, sin) * scale of pairs (2ks, 2ks+1), packed half2
+#pragma unroll
+        for (int v = 0; v < NV; ++v) {
+            const uint4 x = ldg16(chp + 8 * v), y = ldg16(shp + 8 * v);
+            ch[4 * v + 0] = x.x; ch[4 * v + 1] = x.y; ch[4 * v + 2] = x.z; ch[4 * v + 3] = x.w;
+            sh[4 * v + 0] = y.x; sh[4 * v + 1] = y.y; sh[4 * v + 2] = y.z; sh[4 * v + 3] = y.w;
+        }
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+            uint32_t a[4];
+            const __half2 c2 = *reinterpret_cast<const __half2*>(&ch[ks]), s2 = *reinterpret_cast<const __half2*>(&sh[ks]);
+#pragma unroll
+            for (int rr = 0; rr < 2; ++rr) {
+                const __half2 lo = *reinterpret_cast<const __half2*>(&qraw[rr][0][ks]);
+                const __half2 hi = *reinterpret_cast<const __half2*>(&qraw[rr][1][ks]);
+                const __half2 x = __hfma2(lo, c2, __hneg2(__hmul2(hi, s2)));     // lo*cos - hi*sin
+                const __half2 y = __hfma2(hi, c2, __hmul2(lo, s2));              // lo*sin + hi*cos
+                a[rr] = *reinterpret_cast<const uint32_t*>(&x);
+                a[2 + rr] = *reinterpret_cast<const uint32_t*>(&y);
+            }
+            if (KEEP_A) { qa[KEEP_A ? ks : 0][0] = a[0]; qa[KEEP_A ? ks : 0][1] = a[1]; qa[KEEP_A ? ks : 0][2] = a[2]; qa[KEEP_A ? ks : 0][3] = a[3]; }
+            FS::mma(S0, a[0], a[1], a[2], a[3], kb[0][0][ks], kb[0][1][ks]);
+            FS::mma(S1, a[0], a[1], a[2], a[3], kb[1][0][ks], kb[1][1][ks]);
+        }
+        return;
+    }
 #pragma unroll
     for (int ks2 = 0; ks2 < KS; ks2 += 2) {
         const float4 c4 = __ldg(reinterpret_cast<const float4*>(cp + 2 * ks2));
@@ -93,7 +126,7 @@ __device__ __forceinline__ void score_chunk(const AttnParams& p, const __half* l
             uint32_t a[4];
 #pragma unroll
             for (int rr = 0; rr < 2; ++rr) {
-                const float2 lo = F::unpack(qraw[rr][0][ks]), hi = F::unpack(qraw[rr][1][ks]);
+                const float2 lo = FS::unpack(qraw[rr][0][ks]), hi = FS::unpack(qraw[rr][1][ks]);
                 const float c0 = cs[2 * u], c1 = cs[2 * u + 1], s0 = sn[2 * u], s1 = sn[2 * u + 1];
                 a[rr] = FS::pack(lo.x * c0 - hi.x * s0, lo.y * c1 - hi.y * s1);         // rotated low half
                 a[2 + rr] = FS::pack(lo.x * s0 + hi.x * c0, lo.y * s1 + hi.y * c1);     // rotated high half
@@ -121,6 +154,24 @@ __device__ __forceinline__ void load_rows(const T* base, int g, int r, const boo
                 raw[rr][hf][4 * v + 0] = x.x; raw[rr][hf][4 * v + 1] = x.y;
                 raw[rr][hf][4 * v + 2] = x.z; raw[rr][hf][4 * v + 3] = x.w;
             }
+    }
+}
+
+// Query rows for score_chunk: load_rows, then bf16 pairs are converted to IEEE half pairs (exact for magnitudes in
+// half's normal range; larger values saturate to the largest finite half).
+template <typename T, int D>
+__device__ __forceinline__ void load_rows_half(const T* base, int g, int r, const bool (&row_ok)[2], uint32_t (&raw)[2][2][D / 16]) {
+    load_rows<T, D>(base, g, r, row_ok, raw);
+    if (sizeof(T) == 2 && !std::is_same<T, __half>::value) {
+#pragma unroll
+        for (int rr = 0; rr < 2; ++rr)
+#pragma unroll
+            for (int hf = 0; hf < 2; ++hf)
+#pragma unroll
+                for (int i = 0; i < D / 16; ++i) {
+                    const float2 f = Frag<__nv_bfloat16>::unpack(raw[rr][hf][i]);
+                    raw[rr][hf][i] = Frag<__half>::pack(fminf(fmaxf(f.x, -65504.f), 65504.f), fminf(fmaxf(f.y, -65504.f), 65504.f));
+                }
     }
 }
 

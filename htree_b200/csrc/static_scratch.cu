@@ -46,7 +46,8 @@ size_t htree_b200_static_scratch_bytes(void) { return kScratchFloats * sizeof(fl
 
 int htree_b200_backward_static_scratch(const HtreeShape* shape, const void* q, void* const* layers_k,
                                        void* const* layers_v, void* const* layers_k_rot, const float* cos_cache,
-                                       const float* sin_cache, int32_t n_pos, float scale, const void* out,
+                                       const float* sin_cache, const void* cos_half, const void* sin_half,
+                                       int32_t n_pos, float scale, const void* out,
                                        const void* dO, const float* gmax, const float* gsum, int32_t* const* parents,
                                        float* dq, float* dk, float* dv, int32_t* status, uint32_t flags, void* stream) {
     if (!shape || !dk || !dv) return HTREE_E_NULL;
@@ -74,7 +75,7 @@ int htree_b200_backward_static_scratch(const HtreeShape* shape, const void* q, v
     for (int l = 1; l < L; ++l) { dk_levels[l] = base + off_k[l]; dv_levels[l] = base + off_v[l]; }
     // htree_b200_backward zero-fills every level it is given before accumulating, so whatever an earlier call left in
     // the array is cleared on the caller's stream before this call's kernels touch it.
-    return htree_b200_backward(shape, q, layers_k, layers_v, layers_k_rot, cos_cache, sin_cache, n_pos, scale, out, dO,
+    return htree_b200_backward(shape, q, layers_k, layers_v, layers_k_rot, cos_cache, sin_cache, cos_half, sin_half, n_pos, scale, out, dO,
                                gmax, gsum, parents, dq, dk_levels, dv_levels, status, flags, stream);
 }
 

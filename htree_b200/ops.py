@@ -64,6 +64,21 @@ def rope_cache(k_dim: int, cache_size: int, rope_base: float, device) -> Tuple[t
     return hit
 
 
+_rope_half: Dict[Tuple, Tuple[torch.Tensor, torch.Tensor]] = {}
+
+
+def rope_cache_half(k_dim: int, cache_size: int, rope_base: float, scale: float, device):
+    """cos*scale and sin*scale as float16 tables (same shape as rope_cache), for the packed-half query rotation of the
+    tensor-core kernels in the passes that do not decide the Top-K."""
+    key = (int(k_dim), int(cache_size), float(rope_base), float(scale), torch.device(device))
+    hit = _rope_half.get(key)
+    if hit is None:
+        c, s = rope_cache(k_dim, cache_size, rope_base, device)
+        hit = ((c * float(scale)).to(torch.float16).contiguous(), (s * float(scale)).to(torch.float16).contiguous())
+        _rope_half[key] = hit
+    return hit
+
+
 def _status(device) -> torch.Tensor:
     device = torch.device(device)
     w = _status_words.get(device)
@@ -164,12 +179,13 @@ def rotate_keys(layers_k, compression_rate: int, max_top_nodes: int, rope_base: 
 
 
 def _run_forward(shape, q, layers_k, layers_v, cos_cache, sin_cache, scale, out, gmax, gsum, parents, trace, flags,
-                 layers_kr=None):
+                 layers_kr=None, half_tables=None):
     with torch.cuda.device(q.device):
         rc = _lib.lib().htree_b200_forward(
             ctypes.byref(shape), q.data_ptr(), _ptrs(layers_k), _ptrs(layers_v),
-            _ptrs(layers_kr) if layers_kr is not None else None, cos_cache.data_ptr(),
-            sin_cache.data_ptr(), cos_cache.shape[0], float(scale),
+            _ptrs(layers_kr) if layers_kr is not None else None, cos_cache.data_ptr(), sin_cache.data_ptr(),
+            half_tables[0].data_ptr() if half_tables else None, half_tables[1].data_ptr() if half_tables else None,
+            cos_cache.shape[0], float(scale),
             out.data_ptr() if out is not None else None, gmax.data_ptr() if gmax is not None else None,
             gsum.data_ptr() if gsum is not None else None, _ptrs(parents) if parents is not None else None,
             ctypes.byref(trace) if trace is not None else None, _status(q.device).data_ptr(), flags, _stream())
@@ -218,8 +234,9 @@ def htree_forward(
               torch.empty(L, B, T, H, V, dtype=torch.float32, device=dev))
         trace = _lib.HtreeTrace(tr[0].data_ptr(), tr[1].data_ptr(), tr[2].data_ptr())
     flags = _lib.FWD_GENERIC if (_force_generic or return_trace) else 0
+    half_tables = rope_cache_half(K, cos_cache.shape[0], rope_base, scale, dev) if layers_kr is not None else None
     _run_forward(shape, q, layers_k, layers_v, cos_cache, sin_cache, scale, out, gmax, gsum, parents, trace, flags,
-                 layers_kr)
+                 layers_kr, half_tables)
     if not (_save_for_backward or return_trace):
         return out
     result = [out]
@@ -229,6 +246,7 @@ def htree_forward(
             global_max=gmax, global_sum=gsum,
             per_layer_parents={l: parents[l] for l in range(L)} if (_save_parents and parents is not None) else None,
             layers_k=layers_k, layers_v=layers_v, layers_k_rot=layers_kr, cos_cache=cos_cache, sin_cache=sin_cache,
+            rope_half=half_tables,
             num_layers=L, rope_base=rope_base,
             compression_rate=compression_rate, top_k_per_layer=top_k_per_layer, max_top_nodes=max_top_nodes,
             scale=scale, NUM_GROUPS=G,
@@ -268,6 +286,7 @@ def htree_backward(dO: torch.Tensor, q: torch.Tensor, output: torch.Tensor, bwd_
     scale = bwd_ctx["scale"]
     cos_cache, sin_cache = bwd_ctx["cos_cache"], bwd_ctx["sin_cache"]
     layers_kr = bwd_ctx.get("layers_k_rot")
+    half_tables = bwd_ctx.get("rope_half")
     dev = q.device
     q = q.contiguous()
     dO = dO.contiguous().to(q.dtype)
@@ -283,8 +302,9 @@ def htree_backward(dO: torch.Tensor, q: torch.Tensor, output: torch.Tensor, bwd_
     with torch.cuda.device(dev):
         rc = _lib.lib().htree_b200_backward(
             ctypes.byref(shape), q.data_ptr(), _ptrs(layers_k), _ptrs(layers_v),
-            _ptrs(layers_kr) if layers_kr is not None else None, cos_cache.data_ptr(),
-            sin_cache.data_ptr(), cos_cache.shape[0], float(scale), output.data_ptr(), dO.data_ptr(),
+            _ptrs(layers_kr) if layers_kr is not None else None, cos_cache.data_ptr(), sin_cache.data_ptr(),
+            half_tables[0].data_ptr() if half_tables else None, half_tables[1].data_ptr() if half_tables else None,
+            cos_cache.shape[0], float(scale), output.data_ptr(), dO.data_ptr(),
             bwd_ctx["global_max"].data_ptr(), bwd_ctx["global_sum"].data_ptr(),
             _ptrs([parents[l] for l in range(L)]), dq.data_ptr(), _ptrs(dk_levels), _ptrs(dv_levels),
             _status(dev).data_ptr(), _lib.FWD_GENERIC if _force_generic else 0, _stream())

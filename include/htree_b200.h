@@ -112,6 +112,9 @@ int htree_b200_rotate_keys(const HtreeShape* shape, void* const* layers_k, void*
  *                 bf16/fp16, K == V in {64,128}, H/H_kv <= 16, compression_rate 16) the tensor-core kernel runs,
  *                 otherwise the generic fp32-arithmetic kernel
  *   cos_cache, sin_cache  [n_pos, K/2] fp32 RoPE tables (src/parallel.py:983-988); n_pos >= top_k*compression_rate
+ *   cos_half, sin_half    NULL, or [n_pos, K/2] IEEE half tables holding cos*scale and sin*scale: the tensor-core
+ *                         kernels then rotate queries with packed half arithmetic where that does not touch the
+ *                         Top-K decision (accumulation passes, backward); without them everything rotates in fp32
  *   out [B,T,H,V] in `dtype`; gmax, gsum [B,T,H] fp32 (global_max / global_sum of bwd_ctx)
  *   parents  NULL, or L pointers: parents[l] [B,T,H_kv,top_k] int32 receives the parent list CONSUMED at level l,
  *            ascending and -1 padded (per_layer_parents of bwd_ctx, src/parallel.py:1039-1044)
@@ -119,7 +122,8 @@ int htree_b200_rotate_keys(const HtreeShape* shape, void* const* layers_k, void*
  *   status   NULL or one int32 on the device, OR-ed with a non-zero code if a kernel met an out-of-range node index
  */
 int htree_b200_forward(const HtreeShape* shape, const void* q, void* const* layers_k, void* const* layers_v,
-                       void* const* layers_k_rot, const float* cos_cache, const float* sin_cache, int32_t n_pos, float scale, void* out,
+                       void* const* layers_k_rot, const float* cos_cache, const float* sin_cache, const void* cos_half,
+                       const void* sin_half, int32_t n_pos, float scale, void* out,
                        float* gmax, float* gsum, int32_t* const* parents, const HtreeTrace* trace, int32_t* status,
                        uint32_t flags, void* stream);
 
@@ -134,7 +138,8 @@ int htree_b200_forward(const HtreeShape* shape, const void* q, void* const* laye
  *   scratch (the reference's dk_layers / dv_layers, src/backward.py:979-981).
  */
 int htree_b200_backward(const HtreeShape* shape, const void* q, void* const* layers_k, void* const* layers_v,
-                        void* const* layers_k_rot, const float* cos_cache, const float* sin_cache, int32_t n_pos, float scale, const void* out,
+                        void* const* layers_k_rot, const float* cos_cache, const float* sin_cache, const void* cos_half,
+                        const void* sin_half, int32_t n_pos, float scale, const void* out,
                         const void* dO, const float* gmax, const float* gsum, int32_t* const* parents, float* dq,
                         float* const* dk_levels, float* const* dv_levels, int32_t* status, uint32_t flags,
                         void* stream);
@@ -159,7 +164,8 @@ int htree_b200_backward(const HtreeShape* shape, const void* q, void* const* lay
 size_t htree_b200_static_scratch_bytes(void);
 int htree_b200_backward_static_scratch(const HtreeShape* shape, const void* q, void* const* layers_k,
                                        void* const* layers_v, void* const* layers_k_rot, const float* cos_cache,
-                                       const float* sin_cache, int32_t n_pos, float scale, const void* out,
+                                       const float* sin_cache, const void* cos_half, const void* sin_half,
+                                       int32_t n_pos, float scale, const void* out,
                                        const void* dO, const float* gmax, const float* gsum, int32_t* const* parents,
                                        float* dq, float* dk, float* dv, int32_t* status, uint32_t flags, void* stream);
 

@@ -454,6 +454,16 @@ int ho_backward(const HoShape* sh, const float* q, const float* const* layers_k,
     return status;
 }
 
+/* Use n OpenMP threads from now on (launchers such as torchrun export OMP_NUM_THREADS=1). */
+void ho_set_threads(int n) {
+#ifdef _OPENMP
+    extern void omp_set_num_threads(int);
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 int ho_max_threads(void) {
 #ifdef _OPENMP
     extern int omp_get_max_threads(void);

@@ -60,6 +60,13 @@ def max_threads() -> int:
     return int(_load().ho_max_threads())
 
 
+def use_all_threads() -> int:
+    """Run with one OpenMP thread per CPU this process may use, whatever OMP_NUM_THREADS says."""
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    _load().ho_set_threads(int(n))
+    return max_threads()
+
+
 def num_levels(T: int, CR: int, MTN: int) -> int:
     return int(_load().ho_num_levels(int(T), int(CR), int(MTN)))
 

@@ -22,7 +22,8 @@ def _call(lib, shape, q, ctx, out, dO, dq, dk_arg, dv_arg, static):
     ptrs = lambda ts: _lib.ptr_array([t.data_ptr() for t in ts])
     common = [ctypes.byref(shape), q.data_ptr(), ptrs(ctx["layers_k"]), ptrs(ctx["layers_v"]),
               ptrs(ctx["layers_k_rot"]) if ctx["layers_k_rot"] is not None else None, ctx["cos_cache"].data_ptr(),
-              ctx["sin_cache"].data_ptr(), ctx["cos_cache"].shape[0], float(ctx["scale"]), out.data_ptr(), dO.data_ptr(),
+              ctx["sin_cache"].data_ptr(), None, None, ctx["cos_cache"].shape[0], float(ctx["scale"]), out.data_ptr(),
+              dO.data_ptr(),
               ctx["global_max"].data_ptr(), ctx["global_sum"].data_ptr(),
               ptrs([ctx["per_layer_parents"][l] for l in range(L)]), dq.data_ptr()]
     stream = torch.cuda.current_stream().cuda_stream
@@ -64,7 +65,7 @@ def test_static_scratch_rejects_oversized_levels():
     # pooled levels of 4 x 65536 tokens with 4 KV heads and K = V = 128 need 71 MB: more than the 16 MiB array
     shape = _lib.HtreeShape(4, 65536, 64, 4, 128, 128, 16, 64, 256, 1)
     one = ctypes.c_void_p(256)
-    rc = lib.htree_b200_backward_static_scratch(ctypes.byref(shape), 256, None, None, None, 256, 256, 2048, 0.1, 256, 256,
+    rc = lib.htree_b200_backward_static_scratch(ctypes.byref(shape), 256, None, None, None, 256, 256, None, None, 2048, 0.1, 256, 256,
                                                 256, 256, None, 256, one, one, None, 0, None)
     assert rc == -11
     assert "scratch" in _lib.error_string(rc)
