@@ -9,10 +9,11 @@
 //   S   = q^_a K'^T                                    (score product, as in the forward)
 //   P   = exp(S - gmax) / gsum,  dP = dO V^T,  dS = P * (dP - D),  D = sum_v dO * out
 //   dq += scale * dS (R(16a-p) K')                     keys re-gathered row-wise, rotated back into q's frame
-//   dK[node] += R(c)^T (dS^T q^_a)                     one k16 product per 8 columns; fragments transposed with movmatrix
-//   dV[node] += P^T dO
-// dK/dV go to the fp32 level buffers with 16-byte vector reductions (red.global.add.v4.f32); dq stays in registers
-// across all levels and is written once.
+//   dK'[node] += dS^T q^_a                             one k16 product per 8 columns; fragments transposed with movmatrix
+//   dV[node]  += P^T dO
+// dK'/dV go to the fp32 level buffers with 16-byte vector reductions (red.global.add.v4.f32) in a layout that lets a
+// quad fill whole 32-byte sectors; finalize_grads_kernel afterwards restores the column order and applies
+// dK = R(node % 16)^T dK' once per node.  dq stays in registers across all levels and is written once.
 #include "mma_common.cuh"
 
 namespace htree {
@@ -129,15 +130,10 @@ __global__ void __launch_bounds__(MWB * 32, HTREE_BWD_MIN_BLOCKS) bwd_mma_kernel
                 const T* v1 = lv + (((int64_t)b * Nl + n1) * p.Hkv + hk) * D + PPT * r;
                 uint32_t vb[2][2][KS];
 #pragma unroll
-                for (int hf = 0; hf < 2; ++hf)
-#pragma unroll
-                    for (int v = 0; v < 2; ++v) {
-                        uint4 x = make_uint4(0, 0, 0, 0), y = make_uint4(0, 0, 0, 0);
-                        if (n0 < Nl) x = ldg16(v0 + hf * HALF + 8 * v);
-                        if (n1 < Nl) y = ldg16(v1 + hf * HALF + 8 * v);
-                        vb[0][hf][4 * v + 0] = x.x; vb[0][hf][4 * v + 1] = x.y; vb[0][hf][4 * v + 2] = x.z; vb[0][hf][4 * v + 3] = x.w;
-                        vb[1][hf][4 * v + 0] = y.x; vb[1][hf][4 * v + 1] = y.y; vb[1][hf][4 * v + 2] = y.z; vb[1][hf][4 * v + 3] = y.w;
-                    }
+                for (int hf = 0; hf < 2; ++hf) {
+                    ldg_vec<2>(v0 + hf * HALF, n0 < Nl, vb[0][hf]);
+                    ldg_vec<2>(v1 + hf * HALF, n1 < Nl, vb[1][hf]);
+                }
 #pragma unroll
                 for (int ks = 0; ks < KS; ++ks) {
                     F::mma(dP0, dOraw[0][0][ks], dOraw[1][0][ks], dOraw[0][1][ks], dOraw[1][1][ks], vb[0][0][ks], vb[0][1][ks]);
@@ -222,24 +218,26 @@ __global__ void __launch_bounds__(MWB * 32, HTREE_BWD_MIN_BLOCKS) bwd_mma_kernel
                 }
             }
 
-            // ---- dK[node0 + c] += R(c)^T (dS^T q^_a) and dV[node0 + c] += P^T dO, rows c = g and g + 8 ----
+            // ---- dK'[node0 + c] += dS^T q^_a and dV[node0 + c] += P^T dO, rows c = g and g + 8 ----
+            // The level buffers are used in a private layout here: dK' is the gradient of the pre-rotated key (the
+            // rotation by the child index is undone once per node by finalize_grads_kernel, not once per visit), and
+            // within each 64-wide half position 16*m + 4*r + i holds column 16*r + 4*m + i, so that the four threads
+            // of a quad reduce into 64 contiguous bytes (two full sectors per row and instruction).
             const bool rowc[2] = {(mask >> g & 1) != 0, (mask >> (g + 8) & 1) != 0};
             float* dkrow[2];
             float* dvrow[2];
 #pragma unroll
             for (int rr = 0; rr < 2; ++rr) {
-                const int64_t off = (((int64_t)b * Nl + node0 + g + 8 * rr) * p.Hkv + hk) * D + PPT * r;
+                const int64_t off = (((int64_t)b * Nl + node0 + g + 8 * rr) * p.Hkv + hk) * D + 4 * r;
                 dkrow[rr] = dkl + off;
                 dvrow[rr] = dvl + off;
             }
-            const float* ccp[2] = {p.cosc + (size_t)g * HALF + PPT * r, p.cosc + (size_t)(g + 8) * HALF + PPT * r};
-            const float* csp[2] = {p.sinc + (size_t)g * HALF + PPT * r, p.sinc + (size_t)(g + 8) * HALF + PPT * r};
 #pragma unroll
-            for (int ks2 = 0; ks2 < KS; ks2 += 2) {
-                float klo_[2][4], khi_[2][4], vlo_[2][4], vhi_[2][4];   // [row][4 consecutive columns 2*ks2 .. 2*ks2+3]
+            for (int m = 0; m < KS / 2; ++m) {
+                float klo_[2][4], khi_[2][4], vlo_[2][4], vhi_[2][4];   // [row][4 consecutive columns 16r + 4m + i]
 #pragma unroll
                 for (int u = 0; u < 2; ++u) {
-                    const int ks = ks2 + u;
+                    const int ks = 2 * m + u;
                     float tl_[4] = {0.f, 0.f, 0.f, 0.f}, th_[4] = {0.f, 0.f, 0.f, 0.f};
                     FS::mma(tl_, dst0, dst1, dst2, dst3, movmatrix_trans(qa[ks][0]), movmatrix_trans(qa[ks][1]));
                     FS::mma(th_, dst0, dst1, dst2, dst3, movmatrix_trans(qa[ks][2]), movmatrix_trans(qa[ks][3]));
@@ -254,19 +252,10 @@ __global__ void __launch_bounds__(MWB * 32, HTREE_BWD_MIN_BLOCKS) bwd_mma_kernel
 #pragma unroll
                 for (int rr = 0; rr < 2; ++rr) {
                     if (!rowc[rr]) continue;
-                    const float4 c4 = __ldg(reinterpret_cast<const float4*>(ccp[rr] + 2 * ks2));
-                    const float4 s4 = __ldg(reinterpret_cast<const float4*>(csp[rr] + 2 * ks2));
-                    const float cs[4] = {c4.x, c4.y, c4.z, c4.w}, sn[4] = {s4.x, s4.y, s4.z, s4.w};
-                    float lo[4], hi[4];
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {   // inverse rotation by the child index (src/naive.py:31-38)
-                        lo[i] = klo_[rr][i] * cs[i] + khi_[rr][i] * sn[i];
-                        hi[i] = khi_[rr][i] * cs[i] - klo_[rr][i] * sn[i];
-                    }
-                    red_add_v4(dkrow[rr] + 2 * ks2, lo[0], lo[1], lo[2], lo[3]);
-                    red_add_v4(dkrow[rr] + HALF + 2 * ks2, hi[0], hi[1], hi[2], hi[3]);
-                    red_add_v4(dvrow[rr] + 2 * ks2, vlo_[rr][0], vlo_[rr][1], vlo_[rr][2], vlo_[rr][3]);
-                    red_add_v4(dvrow[rr] + HALF + 2 * ks2, vhi_[rr][0], vhi_[rr][1], vhi_[rr][2], vhi_[rr][3]);
+                    red_add_v4(dkrow[rr] + 16 * m, klo_[rr][0], klo_[rr][1], klo_[rr][2], klo_[rr][3]);
+                    red_add_v4(dkrow[rr] + HALF + 16 * m, khi_[rr][0], khi_[rr][1], khi_[rr][2], khi_[rr][3]);
+                    red_add_v4(dvrow[rr] + 16 * m, vlo_[rr][0], vlo_[rr][1], vlo_[rr][2], vlo_[rr][3]);
+                    red_add_v4(dvrow[rr] + HALF + 16 * m, vhi_[rr][0], vhi_[rr][1], vhi_[rr][2], vhi_[rr][3]);
                 }
             }
         }
@@ -288,6 +277,38 @@ __global__ void __launch_bounds__(MWB * 32, HTREE_BWD_MIN_BLOCKS) bwd_mma_kernel
     }
 }
 
+// Turns the private accumulator layout of bwd_mma_kernel into gradients, in place, one 16-lane group per row:
+// un-permute both buffers (position 16m + 4r + i of each half <-> column 16r + 4m + i) and rotate dK' back by the
+// node's child index, dK = R(node % CR)^T dK' (inverse of the rotation in rotate_keys_kernel; src/naive.py:31-38).
+__global__ void __launch_bounds__(256) finalize_grads_kernel(float* dk, float* dv, const float* cosc, const float* sinc,
+                                                             int64_t rows, int Hkv, int N, int CR) {
+    constexpr int D = 128, HALF = 64;
+    const int64_t row = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 4;
+    const int j = threadIdx.x & 15;                      // position group 4j .. 4j+3 of each half
+    const bool on = row < rows;
+    const int m = j >> 2, r = j & 3;
+    const int col = 16 * r + 4 * m;                      // first of the 4 columns stored at positions 4j .. 4j+3
+    float4 klo = make_float4(0, 0, 0, 0), khi = klo, vlo = klo, vhi = klo;
+    float* dkr = dk + row * D;
+    float* dvr = dv + row * D;
+    if (on) {
+        klo = *reinterpret_cast<const float4*>(dkr + 4 * j); khi = *reinterpret_cast<const float4*>(dkr + HALF + 4 * j);
+        vlo = *reinterpret_cast<const float4*>(dvr + 4 * j); vhi = *reinterpret_cast<const float4*>(dvr + HALF + 4 * j);
+    }
+    __syncwarp();                                        // every lane of the row has read before anyone writes
+    if (!on) return;
+    const int c = (int)((row / Hkv) % N) % CR;
+    const float4 cs = __ldg(reinterpret_cast<const float4*>(cosc + (size_t)c * HALF + col));
+    const float4 sn = __ldg(reinterpret_cast<const float4*>(sinc + (size_t)c * HALF + col));
+    float4 lo, hi;
+    lo.x = klo.x * cs.x + khi.x * sn.x; hi.x = khi.x * cs.x - klo.x * sn.x;
+    lo.y = klo.y * cs.y + khi.y * sn.y; hi.y = khi.y * cs.y - klo.y * sn.y;
+    lo.z = klo.z * cs.z + khi.z * sn.z; hi.z = khi.z * cs.z - klo.z * sn.z;
+    lo.w = klo.w * cs.w + khi.w * sn.w; hi.w = khi.w * cs.w - klo.w * sn.w;
+    *reinterpret_cast<float4*>(dkr + col) = lo; *reinterpret_cast<float4*>(dkr + HALF + col) = hi;
+    *reinterpret_cast<float4*>(dvr + col) = vlo; *reinterpret_cast<float4*>(dvr + HALF + col) = vhi;
+}
+
 bool bwd_mma_supported(const AttnParams& p, int dtype) {
     if (dtype != HTREE_BF16 && dtype != HTREE_F16) return false;
     if (p.K != 128 || p.V != 128 || p.G > 16 || p.CR != 16) return false;
@@ -303,7 +324,17 @@ static int launch_bwd_mma_t(const AttnParams& p, cudaStream_t st) {
     if (e != cudaSuccess) return (int)e;
     bwd_mma_kernel<T, ROT16><<<grid, MWB * 32, smem, st>>>(p);
     note_launch();
-    return (int)cudaGetLastError();
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return (int)e;
+    for (int l = 0; l < p.L; ++l) {
+        const int64_t rows = (int64_t)p.B * p.ln[l] * p.Hkv;
+        const unsigned blocks = (unsigned)((rows * 16 + 255) / 256);
+        finalize_grads_kernel<<<blocks, 256, 0, st>>>(p.dk[l], p.dv[l], p.cosc, p.sinc, rows, p.Hkv, p.ln[l], p.CR);
+        note_launch();
+        e = cudaGetLastError();
+        if (e != cudaSuccess) return (int)e;
+    }
+    return 0;
 }
 
 int launch_bwd_mma(const AttnParams& p, int dtype, cudaStream_t st) {

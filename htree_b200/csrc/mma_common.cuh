@@ -40,6 +40,26 @@ template <> struct Frag<__half> {
 };
 
 __device__ __forceinline__ uint4 ldg16(const void* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
+// 32 bytes with one 256-bit load (sm_100a); address must be 32-byte aligned.
+__device__ __forceinline__ void ldg32(const void* p, uint32_t (&o)[8]) {
+    asm volatile("ld.global.nc.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];\n"
+                 : "=r"(o[0]), "=r"(o[1]), "=r"(o[2]), "=r"(o[3]), "=r"(o[4]), "=r"(o[5]), "=r"(o[6]), "=r"(o[7])
+                 : "l"(p));
+}
+// n16 consecutive 16-byte pieces (n16 = 1 or 2) into o[0 .. 4*n16), using one 256-bit load when n16 == 2
+template <int N16>
+__device__ __forceinline__ void ldg_vec(const void* p, bool on, uint32_t* o) {
+    if (N16 == 2) {
+        uint32_t t[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        if (on) ldg32(p, t);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = t[i];
+    } else {
+        uint4 x = make_uint4(0, 0, 0, 0);
+        if (on) x = ldg16(p);
+        o[0] = x.x; o[1] = x.y; o[2] = x.z; o[3] = x.w;
+    }
+}
 __device__ __forceinline__ uint32_t word(const uint4& v, int i) { return i == 0 ? v.x : (i == 1 ? v.y : (i == 2 ? v.z : v.w)); }
 
 __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
@@ -74,27 +94,18 @@ __device__ __forceinline__ void score_chunk(const AttnParams& p, const __half* l
     const __half* k1 = lkr + (((int64_t)b * Nl + n1) * p.Hkv + hk) * D + PPT * r;
     uint32_t kb[2][2][KS];   // [tile][half][k-step]
 #pragma unroll
-    for (int hf = 0; hf < 2; ++hf)
-#pragma unroll
-        for (int v = 0; v < NV; ++v) {
-            uint4 x = make_uint4(0, 0, 0, 0), y = make_uint4(0, 0, 0, 0);
-            if (n0 < Nl) x = ldg16(k0 + hf * HALF + 8 * v);
-            if (n1 < Nl) y = ldg16(k1 + hf * HALF + 8 * v);
-            kb[0][hf][4 * v + 0] = x.x; kb[0][hf][4 * v + 1] = x.y; kb[0][hf][4 * v + 2] = x.z; kb[0][hf][4 * v + 3] = x.w;
-            kb[1][hf][4 * v + 0] = y.x; kb[1][hf][4 * v + 1] = y.y; kb[1][hf][4 * v + 2] = y.z; kb[1][hf][4 * v + 3] = y.w;
-        }
+    for (int hf = 0; hf < 2; ++hf) {
+        ldg_vec<NV>(k0 + hf * HALF, n0 < Nl, kb[0][hf]);
+        ldg_vec<NV>(k1 + hf * HALF, n1 < Nl, kb[1][hf]);
+    }
     S0[0] = S0[1] = S0[2] = S0[3] = 0.f;
     S1[0] = S1[1] = S1[2] = S1[3] = 0.f;
     if (ROT16) {
         const __half* chp = p.cosh + (size_t)delta * HALF + PPT * r;
         const __half* shp = p.sinh + (size_t)delta * HALF + PPT * r;
         uint32_t ch[KS], sh[KS];   // (cos, sin) * scale of pairs (2ks, 2ks+1), packed half2
-#pragma unroll
-        for (int v = 0; v < NV; ++v) {
-            const uint4 x = ldg16(chp + 8 * v), y = ldg16(shp + 8 * v);
-            ch[4 * v + 0] = x.x; ch[4 * v + 1] = x.y; ch[4 * v + 2] = x.z; ch[4 * v + 3] = x.w;
-            sh[4 * v + 0] = y.x; sh[4 * v + 1] = y.y; sh[4 * v + 2] = y.z; sh[4 * v + 3] = y.w;
-        }
+        ldg_vec<NV>(chp, true, ch);
+        ldg_vec<NV>(shp, true, sh);
 #pragma unroll
         for (int ks = 0; ks < KS; ++ks) {
             uint32_t a[4];
@@ -146,14 +157,7 @@ __device__ __forceinline__ void load_rows(const T* base, int g, int r, const boo
     for (int rr = 0; rr < 2; ++rr) {
         const T* row = base + (int64_t)(g + 8 * rr) * D;
 #pragma unroll
-        for (int hf = 0; hf < 2; ++hf)
-#pragma unroll
-            for (int v = 0; v < NV; ++v) {
-                uint4 x = make_uint4(0, 0, 0, 0);
-                if (row_ok[rr]) x = ldg16(row + hf * HALF + PPT * r + 8 * v);
-                raw[rr][hf][4 * v + 0] = x.x; raw[rr][hf][4 * v + 1] = x.y;
-                raw[rr][hf][4 * v + 2] = x.z; raw[rr][hf][4 * v + 3] = x.w;
-            }
+        for (int hf = 0; hf < 2; ++hf) ldg_vec<NV>(row + hf * HALF + PPT * r, row_ok[rr], raw[rr][hf]);
     }
 }
 
