@@ -1,0 +1,194 @@
+"""GPU parity at the BASELINE configuration sizes: sampled groups against the CPU oracle (the oracle evaluates single
+(batch, position, KV head) groups, so full-size sequences can be spot-checked), size-independent properties
+(causality, window consistency, finiteness), the near-tie stress workload, and the sequence-sharded forward."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle
+from tests import parity
+from tests.test_gpu_parity import EPS_SEL, EPS_SEL_MMA, _ops
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def sample_queries(B, T, Hkv, n, seed):
+    rng = np.random.default_rng(seed)
+    return np.stack([rng.integers(0, B, n), np.sort(rng.integers(0, T, n)), rng.integers(0, Hkv, n)], 1).astype(np.int32)
+
+
+def compare_sampled(c, q, k, v, out, ctx, queries, eps):
+    """Selections (near-tie rule, level by level) and outputs of the sampled groups.  Returns (fraction of sampled
+    groups identical at every level, max |out - oracle| over those groups)."""
+    ref = oracle.forward(parity.f32(q), parity.f32(k), parity.f32(v), c["CR"], c["MTN"], c["TK"], dtype=c["dtype"],
+                         queries=queries, return_importance=True)
+    L, TK, G = ctx["num_layers"], c["TK"], c["H"] // c["H_kv"]
+    assert L == ref["num_layers"]
+    bi, ti, hi = queries[:, 0], queries[:, 1], queries[:, 2]
+    ours_par = [ctx["per_layer_parents"][l][bi, ti, hi].cpu().numpy() for l in range(L)]
+    same = np.ones(len(queries), bool)
+    for l in range(L - 1, 0, -1):
+        rows = np.nonzero(same)[0]
+        ex, near, bad = parity.compare_selections(ours_par[l - 1][rows], ref["parents"][l - 1][rows],
+                                                  ref["importance"][l][rows], ref["parents"][l][rows], c["CR"], eps)
+        assert bad == 0, f"level {l}: {bad} mismatches that are not near-ties"
+        same &= (ours_par[l - 1] == ref["parents"][l - 1]).all(-1)
+    o = out.float().cpu().numpy().reshape(c["B"], c["T"], c["H_kv"], G, -1)[bi, ti, hi]     # [n,G,V]
+    err = np.abs(o - ref["out_rounded"])[same]
+    return float(same.mean()), float(err.max()), ref, same
+
+
+def test_config2_full_size_forward():
+    """BASELINE config 2 exactly: B=1, T=32768, H_q=32, H_kv=2, head_dim=128, bf16, CR=16, max_top_nodes=128, Top-K=64."""
+    ops = _ops()
+    c = dict(B=1, T=32768, H=32, H_kv=2, K=128, V=128, CR=16, TK=64, MTN=128, dtype="bfloat16", seed=0)
+    q, k, v, _ = parity.case_inputs(c)
+    qd, kd, vd = q.to(DEV), k.to(DEV), v.to(DEV)
+    out, ctx = ops.htree_forward(qd, kd, vd, c["CR"], c["MTN"], c["TK"], _save_for_backward=True)
+    torch.cuda.synchronize(); ops.check_status()
+    assert ctx["layers_k_rot"] is not None and ctx["num_layers"] == 3
+    assert bool(torch.isfinite(out.float()).all())
+    queries = sample_queries(1, c["T"], c["H_kv"], 384, 1)
+    frac, err, _, _ = compare_sampled(c, q, k, v, out, ctx, queries, EPS_SEL_MMA)
+    print(f"\n[cfg2] sampled groups identical at every level: {frac:.4f}; max|out-oracle| on them {err:.3e}")
+    assert frac > 0.95 and err <= 2e-2
+    # causality at full size: changing k, v after t0 must not change out[: t0 + 1]
+    t0 = 20000
+    k2, v2 = kd.clone(), vd.clone()
+    k2[:, t0 + 1:] += 1.0; v2[:, t0 + 1:] -= 1.0
+    out2 = ops.htree_forward(qd, k2, v2, c["CR"], c["MTN"], c["TK"])
+    assert torch.equal(out[:, : t0 + 1], out2[:, : t0 + 1])
+    # query-window consistency (what sequence sharding relies on)
+    t1, t2 = 16384, 24576
+    layers = (ctx["layers_k"], ctx["layers_v"], ctx["layers_k_rot"])
+    out_w = ops.htree_forward(qd[:, t1:t2].contiguous(), kd, vd, c["CR"], c["MTN"], c["TK"], _q_offset=t1, _layers=layers)
+    assert torch.equal(out_w, out[:, t1:t2])
+
+
+def test_config3_shapes_forward_backward():
+    """BASELINE config 3 shapes with one batch element: T=65536, H_q=64, H_kv=4, head_dim=128, bf16, CR=16,
+    max_top_nodes=256, Top-K=64; forward and backward."""
+    ops = _ops()
+    c = dict(B=1, T=65536, H=64, H_kv=4, K=128, V=128, CR=16, TK=64, MTN=256, dtype="bfloat16", seed=1)
+    q, k, v, dO = parity.case_inputs(c)
+    qd, kd, vd, dOd = (x.to(DEV) for x in (q, k, v, dO))
+    out, ctx = ops.htree_forward(qd, kd, vd, c["CR"], c["MTN"], c["TK"], _save_for_backward=True)
+    dq, dk, dv = ops.htree_backward(dOd, qd, out, ctx)
+    dq_g, dk_g, dv_g = ops.htree_backward(dOd, qd, out, ctx, _force_generic=True)
+    torch.cuda.synchronize(); ops.check_status()
+    queries = sample_queries(1, c["T"], c["H_kv"], 256, 2)
+    frac, err, ref, same = compare_sampled(c, q, k, v, out, ctx, queries, EPS_SEL_MMA)
+    print(f"\n[cfg3] sampled groups identical at every level: {frac:.4f}; max|out-oracle| on them {err:.3e}")
+    assert frac > 0.95 and err <= 2e-2
+    # dq of the sampled groups: oracle backward fed with OUR selections / gmax / gsum / stored out
+    G, L = 16, ctx["num_layers"]
+    bi, ti, hi = queries[:, 0], queries[:, 1], queries[:, 2]
+    fwd = dict(ref)
+    fwd["parents"] = np.stack([ctx["per_layer_parents"][l][bi, ti, hi].cpu().numpy() for l in range(L)])
+    pick = lambda x: x.float().cpu().numpy().reshape(1, c["T"], 4, G, -1)[bi, ti, hi]
+    fwd["gmax"] = pick(ctx["global_max"])[..., 0]; fwd["gsum"] = pick(ctx["global_sum"])[..., 0]
+    fwd["out_rounded"] = pick(out)
+    g = oracle.backward(parity.f32(q), fwd, pick(dOd), c["CR"], c["TK"], c["dtype"], queries=queries)
+    e = float(np.abs(pick(dq) - g["dq_f32"]).max())
+    print(f"[cfg3] dq of sampled groups: max|ref| {np.abs(g['dq_f32']).max():.3f} max err {e:.3e}")
+    assert e <= 2e-2 * max(1.0, float(np.abs(g["dq_f32"]).max()))
+    # dk / dv: the tensor-core backward against the fp32-arithmetic backward on the same saved forward
+    for nm, a, b in (("dq", dq, dq_g), ("dk", dk, dk_g), ("dv", dv, dv_g)):
+        st = parity.err_stats(parity.f32(a), parity.f32(b))
+        scale = max(1.0, float(b.abs().max()))
+        print(f"[cfg3] {nm}: max|generic| {float(b.abs().max()):.3f} {st}")
+        assert st["max"] <= 2e-2 * scale and st["p99"] <= 5e-3 * scale, (nm, st)
+
+
+def stress_inputs(B, T, H, Hkv, D, dtype, seed):
+    """Near-tie workload of BASELINE config 5: keys = N(0,1) plus a rank-4 shared component with N(0, std 3)
+    coefficients, which clusters scores; q, v, dO ~ N(0,1)."""
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randn(B, T, H, D, generator=g)
+    z = torch.randn(B, T, Hkv, D, generator=g)
+    v = torch.randn(B, T, Hkv, D, generator=g)
+    dO = torch.randn(B, T, H, D, generator=g)
+    U = torch.randn(4, D, generator=g)
+    coef = 3.0 * torch.randn(B, T, Hkv, 4, generator=g)
+    k = z + coef @ U
+    dt = parity.TDT[dtype]
+    return q.to(dt), k.to(dt), v.to(dt), dO.to(dt)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("tk", [16, 32, 64, 128])
+def test_config5_near_tie_stress(dtype, tk):
+    """BASELINE config 5: B=2, T=16384, H_q=16, H_kv=2, head_dim=64, CR=8, max_top_nodes=64, Top-K swept."""
+    ops = _ops()
+    c = dict(B=2, T=16384, H=16, H_kv=2, K=64, V=64, CR=8, TK=tk, MTN=64, dtype=dtype, seed=50 + tk)
+    q, k, v, dO = stress_inputs(c["B"], c["T"], c["H"], c["H_kv"], 64, dtype, c["seed"])
+    qd, kd, vd, dOd = (x.to(DEV) for x in (q, k, v, dO))
+    out, ctx = ops.htree_forward(qd, kd, vd, c["CR"], c["MTN"], c["TK"], _save_for_backward=True)
+    dq, dk, dv = ops.htree_backward(dOd, qd, out, ctx)
+    torch.cuda.synchronize(); ops.check_status()
+    for x in (out, dq, dk, dv):
+        assert bool(torch.isfinite(x.float()).all())
+    queries = sample_queries(c["B"], c["T"], c["H_kv"], 512, 3)
+    frac, err, ref, same = compare_sampled(c, q, k, v, out, ctx, queries, EPS_SEL[dtype])
+    print(f"\n[cfg5 {dtype} top_k={tk}] levels {ctx['num_layers']}; sampled groups identical: {frac:.4f}; max err {err:.3e}")
+    assert frac > 0.98
+    if dtype == "float32":
+        assert err <= 1e-4 * max(1.0, float(np.abs(ref["out_rounded"]).max()))
+    else:
+        assert err <= 2e-2
+    # dq of the sampled groups against the oracle (our selections substituted)
+    G, L = 8, ctx["num_layers"]
+    bi, ti, hi = queries[:, 0], queries[:, 1], queries[:, 2]
+    fwd = dict(ref)
+    fwd["parents"] = np.stack([ctx["per_layer_parents"][l][bi, ti, hi].cpu().numpy() for l in range(L)])
+    pick = lambda x: x.float().cpu().numpy().reshape(c["B"], c["T"], 2, G, -1)[bi, ti, hi]
+    fwd["gmax"] = pick(ctx["global_max"])[..., 0]; fwd["gsum"] = pick(ctx["global_sum"])[..., 0]
+    fwd["out_rounded"] = pick(out)
+    g = oracle.backward(parity.f32(q), fwd, pick(dOd), c["CR"], c["TK"], dtype, queries=queries)
+    tol = 1e-4 if dtype == "float32" else 2e-3
+    assert float(np.abs(pick(dq) - g["dq_f32"]).max()) <= tol * max(1.0, float(np.abs(g["dq_f32"]).max()))
+
+
+def _seq_worker(rank, world, port, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      NCCL_NVLS_ENABLE="0")
+    import torch.distributed as tdist
+    import htree_b200 as ht
+    from htree_b200 import dist as hdist
+    torch.cuda.set_device(rank)
+    tdist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        B, T, H, Hkv, D, CR, TK, MTN = 1, 32768, 16, 2, 128, 16, 64, 64          # 32768 -> 2048 -> 128 -> 8
+        q, k, v, _ = parity.make_inputs(B, T, H, Hkv, D, D, "bfloat16", 77)
+        dev = f"cuda:{rank}"
+        qd, kd, vd = q.to(dev), k.to(dev), v.to(dev)
+        t0, t1 = hdist.query_range(T, world, rank, CR, 4)
+        out_loc = hdist.htree_forward_sequence_parallel(qd[:, t0:t1].contiguous(), kd, vd, CR, MTN, TK)
+        full = ht.htree_forward(qd, kd, vd, CR, MTN, TK)
+        torch.cuda.synchronize()
+        ret.put((rank, bool(torch.equal(out_loc, full[:, t0:t1]))))
+    finally:
+        tdist.destroy_process_group()
+
+
+def test_sequence_sharded_forward_two_gpus():
+    """Mode B: query positions split over 2 GPUs, pooled levels all-gathered with NCCL; each rank's slice must equal
+    the single-GPU forward bit for bit."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    ret = ctx.Queue()
+    procs = [ctx.Process(target=_seq_worker, args=(r, 2, port, ret)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = sorted(ret.get(timeout=300) for _ in procs)
+    for p in procs:
+        p.join(60)
+    assert results == [(0, True), (1, True)]
