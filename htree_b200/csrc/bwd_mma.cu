@@ -18,7 +18,15 @@
 
 namespace htree {
 
-constexpr int MWB = 4;   // warps (= queries) per block
+#ifdef HTREE_BWD_MAXNREG
+#define HTREE_BWD_BOUNDS __maxnreg__(HTREE_BWD_MAXNREG)
+#else
+#define HTREE_BWD_BOUNDS __launch_bounds__(HTREE_BWD_WARPS * 32, HTREE_BWD_MIN_BLOCKS)
+#endif
+#ifndef HTREE_BWD_WARPS
+#define HTREE_BWD_WARPS 4
+#endif
+constexpr int MWB = HTREE_BWD_WARPS;   // warps (= queries) per block
 #ifndef HTREE_BWD_MIN_BLOCKS
 #define HTREE_BWD_MIN_BLOCKS 2   // register budget: 2 blocks of 128 threads per SM (255 registers)
 #endif
@@ -26,7 +34,7 @@ constexpr int MWB = 4;   // warps (= queries) per block
 __host__ __device__ inline size_t bwd_mma_smem_per_warp(int TK) { return sizeof(int32_t) * 3 * (size_t)TK; }
 
 template <typename T, bool ROT16>
-__global__ void __launch_bounds__(MWB * 32, HTREE_BWD_MIN_BLOCKS) bwd_mma_kernel(const __grid_constant__ AttnParams p) {
+__global__ void HTREE_BWD_BOUNDS bwd_mma_kernel(const __grid_constant__ AttnParams p) {
     constexpr int D = 128, CR = 16, HALF = 64, KS = 8, PPT = 16, NOT = 16;
     using F = Frag<T>;
     using FS = Frag<__half>;

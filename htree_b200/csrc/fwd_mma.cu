@@ -29,7 +29,15 @@
 
 namespace htree {
 
-constexpr int MW = 4;   // warps (= queries) per block
+#ifdef HTREE_FWD_MAXNREG
+#define HTREE_FWD_BOUNDS __maxnreg__(HTREE_FWD_MAXNREG)
+#else
+#define HTREE_FWD_BOUNDS __launch_bounds__(HTREE_FWD_WARPS * 32, HTREE_FWD_MIN_BLOCKS)
+#endif
+#ifndef HTREE_FWD_WARPS
+#define HTREE_FWD_WARPS 4
+#endif
+constexpr int MW = HTREE_FWD_WARPS;   // warps (= queries) per block
 #ifndef HTREE_FWD_MIN_BLOCKS
 #define HTREE_FWD_MIN_BLOCKS 2   // register budget: 2 blocks of 128 threads per SM (255 registers)
 #endif
@@ -48,7 +56,7 @@ __host__ __device__ inline size_t mma_smem_per_warp(int TK, int CR) {
 }
 
 template <typename T, int D, bool ROT16>
-__global__ void __launch_bounds__(MW * 32, HTREE_FWD_MIN_BLOCKS) fwd_mma_kernel(const __grid_constant__ AttnParams p) {
+__global__ void HTREE_FWD_BOUNDS fwd_mma_kernel(const __grid_constant__ AttnParams p) {
     constexpr int CR = 16;
     constexpr int HALF = D / 2;
     constexpr int KS = D / 16;        // k-steps of the score product

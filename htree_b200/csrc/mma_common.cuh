@@ -100,6 +100,7 @@ __device__ __forceinline__ void score_chunk(const AttnParams& p, const __half* l
     }
     S0[0] = S0[1] = S0[2] = S0[3] = 0.f;
     S1[0] = S1[1] = S1[2] = S1[3] = 0.f;
+    float T0[4] = {0.f, 0.f, 0.f, 0.f}, T1[4] = {0.f, 0.f, 0.f, 0.f};
     if (ROT16) {
         const __half* chp = p.cosh + (size_t)delta * HALF + PPT * r;
         const __half* shp = p.sinh + (size_t)delta * HALF + PPT * r;
@@ -120,9 +121,16 @@ __device__ __forceinline__ void score_chunk(const AttnParams& p, const __half* l
                 a[2 + rr] = *reinterpret_cast<const uint32_t*>(&y);
             }
             if (KEEP_A) { qa[KEEP_A ? ks : 0][0] = a[0]; qa[KEEP_A ? ks : 0][1] = a[1]; qa[KEEP_A ? ks : 0][2] = a[2]; qa[KEEP_A ? ks : 0][3] = a[3]; }
-            FS::mma(S0, a[0], a[1], a[2], a[3], kb[0][0][ks], kb[0][1][ks]);
-            FS::mma(S1, a[0], a[1], a[2], a[3], kb[1][0][ks], kb[1][1][ks]);
+            if (ks & 1) {   // two accumulation chains per tile: halves the dependent-MMA latency on the critical path
+                FS::mma(T0, a[0], a[1], a[2], a[3], kb[0][0][ks], kb[0][1][ks]);
+                FS::mma(T1, a[0], a[1], a[2], a[3], kb[1][0][ks], kb[1][1][ks]);
+            } else {
+                FS::mma(S0, a[0], a[1], a[2], a[3], kb[0][0][ks], kb[0][1][ks]);
+                FS::mma(S1, a[0], a[1], a[2], a[3], kb[1][0][ks], kb[1][1][ks]);
+            }
         }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { S0[i] += T0[i]; S1[i] += T1[i]; }
         return;
     }
 #pragma unroll
@@ -143,10 +151,17 @@ __device__ __forceinline__ void score_chunk(const AttnParams& p, const __half* l
                 a[2 + rr] = FS::pack(lo.x * s0 + hi.x * c0, lo.y * s1 + hi.y * c1);     // rotated high half
             }
             if (KEEP_A) { qa[KEEP_A ? ks : 0][0] = a[0]; qa[KEEP_A ? ks : 0][1] = a[1]; qa[KEEP_A ? ks : 0][2] = a[2]; qa[KEEP_A ? ks : 0][3] = a[3]; }
-            FS::mma(S0, a[0], a[1], a[2], a[3], kb[0][0][ks], kb[0][1][ks]);
-            FS::mma(S1, a[0], a[1], a[2], a[3], kb[1][0][ks], kb[1][1][ks]);
+            if (u) {
+                FS::mma(T0, a[0], a[1], a[2], a[3], kb[0][0][ks], kb[0][1][ks]);
+                FS::mma(T1, a[0], a[1], a[2], a[3], kb[1][0][ks], kb[1][1][ks]);
+            } else {
+                FS::mma(S0, a[0], a[1], a[2], a[3], kb[0][0][ks], kb[0][1][ks]);
+                FS::mma(S1, a[0], a[1], a[2], a[3], kb[1][0][ks], kb[1][1][ks]);
+            }
         }
     }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { S0[i] += T0[i]; S1[i] += T1[i]; }
 }
 
 // Raw rows g and g+8 of a [heads, D] block in the fragment order used above (zero for rows beyond the group).
