@@ -35,7 +35,10 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 
 # DRAM traffic per launch of the attention kernels at the default workload, from the ncu captures summarised under
 # profiles/ (None until a capture exists for the kernel that is currently dominant).
-NCU_TRAFFIC_BYTES = {"forward": None, "backward": None}
+# Measured with `ncu --set full` on the same workload at a quarter of the sequence length (profiles/*_cfg3_quarter.md);
+# DRAM traffic grows in proportion to the number of (batch, position, kv head) groups, so the figure is scaled by the
+# ratio of groups.  Values are dram__bytes_read.sum + dram__bytes_write.sum per launch for cfg3 / T=16384.
+NCU_TRAFFIC_BYTES_QUARTER_CFG3 = {"forward": 1.228312e9 + 1.271541e9, "backward": 3.894620e9 + 2.393859e9}
 
 
 def peaks():
@@ -270,6 +273,19 @@ def main():
     bwd_ms = max_over_ranks(statistics.mean(e[1].elapsed_time(e[2]) for e in ev)) if bwd else None
     ht.check_status(dev)
 
+    # ---- streaming kernels: mean-pool tree build + key pre-rotation, timed alone (inputs larger than L2) ----
+    from htree_b200 import ops as hops
+    sa = torch.cuda.Event(enable_timing=True); sb = torch.cuda.Event(enable_timing=True)
+    hops.build_tree(k, v, CR, MTN, 10000.0)
+    torch.cuda.synchronize()
+    n_tb = 10
+    sa.record()
+    for _ in range(n_tb):
+        hops.build_tree(k, v, CR, MTN, 10000.0)
+    sb.record()
+    torch.cuda.synchronize()
+    tree_ms = sa.elapsed_time(sb) / n_tb
+
     # ---- end-to-end timing with host buffers ----
     e2e = None
     if not args.no_e2e:
@@ -320,18 +336,29 @@ def main():
     roofline = {"kernel": f"fused {dominant} attention kernel (all tree levels, one launch per step per rank)",
                 "bound": "tensor", "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s",
                 "frac": achieved / peak_tf, "peak_source": f"{pk['_source']} bf16 dense, sustained",
-                "traffic": NCU_TRAFFIC_BYTES[dominant],
+                "traffic": (NCU_TRAFFIC_BYTES_QUARTER_CFG3[dominant] * (B * T * Hkv) / (4 * 16384 * 4) / world
+                            if args.workload == "cfg3" else None),
+                "traffic_source": "ncu capture at T=16384 scaled by the number of groups" if args.workload == "cfg3" else None,
                 "algorithmic_flops_per_launch": dom_flops,
                 "forward_ms": fwd_ms, "backward_ms": bwd_ms,
                 "forward_tflops": cm["flops_fwd"] / world / (fwd_ms * 1e-3) / 1e12,
                 "backward_tflops": (cm["flops_bwd"] / world / (bwd_ms * 1e-3) / 1e12) if bwd else None,
                 "forward_requested_gather_gbs": cm["gather_bytes_fwd"] / world / (fwd_ms * 1e-3) / 1e9,
                 "forward_compulsory_hbm_frac": cm["bytes_fwd"] / world / (fwd_ms * 1e-3) / 1e9 / pk["hbm_gbs"]}
+    es = 4 if c["dtype"] == "float32" else 2
+    lv_sizes = cm["levels"]
+    tree_bytes = es * U * 2 * D * sum(lv_sizes[i] + lv_sizes[i + 1] for i in range(len(lv_sizes) - 1))     # pool K and V
+    if es == 2:
+        tree_bytes += 2 * 2 * U * D * sum(lv_sizes)                                                         # K -> K'
+    streaming = {"kernels": "tree_build_kernel + rotate_keys_kernel (all levels, rank 0)", "ms": tree_ms,
+                 "algorithmic_bytes": tree_bytes, "achieved": tree_bytes / (tree_ms * 1e-3) / 1e9, "unit": "GB/s",
+                 "peak": pk["hbm_gbs"], "frac": tree_bytes / (tree_ms * 1e-3) / 1e9 / pk["hbm_gbs"],
+                 "note": "CUDA events around 10 back-to-back builds, includes launch gaps between the per-level kernels"}
     line = {"metric": metric, "value": B * T / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16" if c["dtype"] == "bfloat16" else c["dtype"],
             "data": "synthetic", "config": cfg_desc,
-            "fwd_tokens_per_s": B * T / (fwd_ms * 1e-3), "roofline": roofline, "e2e": e2e,
+            "fwd_tokens_per_s": B * T / (fwd_ms * 1e-3), "roofline": roofline, "streaming": streaming, "e2e": e2e,
             "gpu_launches": int(launches), "clocks": clocks}
     if not args.no_cpu_baseline and world == 1:
         tps, info = cpu_oracle_leg(c, args.cpu_seconds)
