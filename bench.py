@@ -295,11 +295,12 @@ def main():
         host_out = [torch.empty(o.shape, dtype=d, pin_memory=True) for o, d in zip(outs, res_dt)]
         del outs
 
+        from htree_b200 import host as hhost
+        e2e_chunk = max(1, U // 8)      # units resident per pipeline stage (two stages in flight)
+
         def e2e_step():
-            dev_in = [h.to(dev, non_blocking=True) for h in host_in]
-            res = step(dev_in[0], dev_in[1], dev_in[2], dev_in[3] if bwd else None)
-            for h, r in zip(host_out, res):
-                h.copy_(r.to(h.dtype), non_blocking=True)
+            hhost.forward_backward_host(host_in[0], host_in[1], host_in[2], host_in[3] if bwd else None, CR, MTN, TK,
+                                        chunk=e2e_chunk, device=dev, outputs=host_out)
 
         e2e_step()
         barrier()
@@ -318,7 +319,9 @@ def main():
             tdist.all_reduce(tt)
             h2d, d2h = int(tt[0].item()), int(tt[1].item())
         e2e = {"value": B * T / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
-               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": n_e2e}
+               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": n_e2e,
+               "api": "htree_b200.host.forward_backward_host: pinned host tensors in and out, batch chunks pipelined "
+                      "over three streams (H2D | kernels | D2H)"}
         del host_in, host_out
 
     if rank != 0:

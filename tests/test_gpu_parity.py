@@ -351,3 +351,20 @@ def test_tensor_core_backward_matches_generic_on_long_case():
         scale = max(1.0, float(b.abs().max()))
         print(f"\n[long] {nm}: max|generic|={float(b.abs().max()):.3f} {st}")
         assert st["max"] <= 2e-2 * scale and st["p99"] <= 5e-3 * scale, (nm, st)
+
+
+def test_host_buffer_pipeline_matches_device_calls():
+    """htree_b200.host.forward_backward_host (chunks pipelined over three streams) against the plain device calls."""
+    ops = _ops()
+    from htree_b200 import host
+    c = dict(B=4, T=1024, H=16, H_kv=1, K=128, V=128, CR=16, TK=16, MTN=64, dtype="bfloat16", seed=61)
+    q, k, v, dO = parity.case_inputs(c)
+    hq, hk, hv, hd = (x.pin_memory() for x in (q, k, v, dO))
+    out_h, dq_h, dk_h, dv_h = host.forward_backward_host(hq, hk, hv, hd, c["CR"], c["MTN"], c["TK"], chunk=1)
+    out, ctx = ops.htree_forward(q.to(DEV), k.to(DEV), v.to(DEV), c["CR"], c["MTN"], c["TK"], _save_for_backward=True)
+    dq, dk, dv = ops.htree_backward(dO.to(DEV), q.to(DEV), out, ctx)
+    assert torch.equal(out_h, out.cpu())
+    for a, b in ((dq_h, dq), (dk_h, dk), (dv_h, dv)):
+        assert torch.allclose(a.float(), b.to(torch.bfloat16).float().cpu(), rtol=2e-2, atol=2e-3)   # reduction order
+    (o2,) = host.forward_backward_host(hq, hk, hv, None, c["CR"], c["MTN"], c["TK"], chunk=3)
+    assert torch.equal(o2, out.cpu())
