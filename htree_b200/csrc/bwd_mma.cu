@@ -33,9 +33,9 @@ constexpr int MWB = HTREE_BWD_WARPS;   // warps (= queries) per block
 
 __host__ __device__ inline size_t bwd_mma_smem_per_warp(int TK) { return sizeof(int32_t) * 3 * (size_t)TK; }
 
-template <typename T, bool ROT16>
+template <typename T, int D, bool ROT16>
 __global__ void HTREE_BWD_BOUNDS bwd_mma_kernel(const __grid_constant__ AttnParams p) {
-    constexpr int D = 128, CR = 16, HALF = 64, KS = 8, PPT = 16, NOT = 16;
+    constexpr int CR = 16, HALF = D / 2, KS = D / 16, PPT = HALF / 4, NV = PPT / 8, NOT = D / 8;
     using F = Frag<T>;
     using FS = Frag<__half>;
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -80,7 +80,7 @@ __global__ void HTREE_BWD_BOUNDS bwd_mma_kernel(const __grid_constant__ AttnPara
         }
     }
 
-    float dqa[NOT][4];   // dq of rows g, g+8; tile (hh, w) column n <-> dim 64*hh + 8*n + w
+    float dqa[NOT][4];   // dq of rows g, g+8; tile 2*ks + half, columns 2r, 2r+1 <-> dims half*HALF + PPT*r + 2*ks + {0,1}
 #pragma unroll
     for (int i = 0; i < NOT; ++i) { dqa[i][0] = dqa[i][1] = dqa[i][2] = dqa[i][3] = 0.f; }
 
@@ -124,12 +124,6 @@ __global__ void HTREE_BWD_BOUNDS bwd_mma_kernel(const __grid_constant__ AttnPara
             const int col[4] = {2 * r, 2 * r + 1, 8 + 2 * r, 9 + 2 * r};
             const bool cv[4] = {(mask >> col[0] & 1) != 0, (mask >> col[1] & 1) != 0, (mask >> col[2] & 1) != 0, (mask >> col[3] & 1) != 0};
 
-            // ---- S and the rotated-query fragments ----
-            float S0[4], S1[4];
-            uint32_t qa[KS][4];
-            if (rot16) score_chunk<D, true, true>(p, lkr, Nl, b, hk, node0, delta, g, r, qraw, S0, S1, qa);
-            else score_chunk<D, true, false>(p, lkr, Nl, b, hk, node0, delta, g, r, qraw, S0, S1, qa);
-
             // ---- dP = dO V^T: value rows in the same (column n = child, permuted contraction) fragment order ----
             float dP0[4] = {0.f, 0.f, 0.f, 0.f}, dP1[4] = {0.f, 0.f, 0.f, 0.f};
             {
@@ -139,8 +133,8 @@ __global__ void HTREE_BWD_BOUNDS bwd_mma_kernel(const __grid_constant__ AttnPara
                 uint32_t vb[2][2][KS];
 #pragma unroll
                 for (int hf = 0; hf < 2; ++hf) {
-                    ldg_vec<2>(v0 + hf * HALF, n0 < Nl, vb[0][hf]);
-                    ldg_vec<2>(v1 + hf * HALF, n1 < Nl, vb[1][hf]);
+                    ldg_vec<NV>(v0 + hf * HALF, n0 < Nl, vb[0][hf]);
+                    ldg_vec<NV>(v1 + hf * HALF, n1 < Nl, vb[1][hf]);
                 }
 #pragma unroll
                 for (int ks = 0; ks < KS; ++ks) {
@@ -148,6 +142,11 @@ __global__ void HTREE_BWD_BOUNDS bwd_mma_kernel(const __grid_constant__ AttnPara
                     F::mma(dP1, dOraw[0][0][ks], dOraw[1][0][ks], dOraw[0][1][ks], dOraw[1][1][ks], vb[1][0][ks], vb[1][1][ks]);
                 }
             }
+
+            // ---- S, the rotated-query fragments and the keys rotated back into q's frame ----
+            float S0[4], S1[4];
+            uint32_t qa[KS][4], kr[2][2][KS];
+            score_chunk<D, true, ROT16, true>(p, lkr, Nl, b, hk, node0, delta, g, r, qraw, S0, S1, qa, kr);
 
             // ---- P and dS (src/naive.py:379-382), zero outside the accumulated set ----
             float P[2][4], dS[2][4];   // [row][tile0 c0, tile0 c1, tile1 c0, tile1 c1]
@@ -171,59 +170,11 @@ __global__ void HTREE_BWD_BOUNDS bwd_mma_kernel(const __grid_constant__ AttnPara
             const uint32_t pt0 = movmatrix_trans(F::pack(P[0][0], P[0][1])), pt1 = movmatrix_trans(F::pack(P[0][2], P[0][3]));
             const uint32_t pt2 = movmatrix_trans(F::pack(P[1][0], P[1][1])), pt3 = movmatrix_trans(F::pack(P[1][2], P[1][3]));
 
-            // ---- dq += scale * dS (R(-delta) K'): keys row-wise (16-byte chunk g of both halves), rotated back ----
-            {
-                uint32_t klo[4][4], khi[4][4];   // [child of this thread][packed pairs] after the rotation
-                if (rot16) {
-                    const uint4 cw = ldg16(p.cosh + (size_t)delta * HALF + 8 * g), sw = ldg16(p.sinh + (size_t)delta * HALF + 8 * g);
-                    const uint32_t cs[4] = {cw.x, cw.y, cw.z, cw.w}, sn[4] = {sw.x, sw.y, sw.z, sw.w};
+            // ---- dq += dS K~: B fragments = the rotated keys of the score product, transposed in registers ----
 #pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        const __half* krow = lkr + (((int64_t)b * Nl + node0 + col[c]) * p.Hkv + hk) * D + 8 * g;
-                        uint4 x = make_uint4(0, 0, 0, 0), y = make_uint4(0, 0, 0, 0);
-                        if (cv[c]) { x = ldg16(krow); y = ldg16(krow + HALF); }
-                        const uint32_t xw[4] = {x.x, x.y, x.z, x.w}, yw[4] = {y.x, y.y, y.z, y.w};
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            const __half2 lo = *reinterpret_cast<const __half2*>(&xw[i]), hi = *reinterpret_cast<const __half2*>(&yw[i]);
-                            const __half2 c2 = *reinterpret_cast<const __half2*>(&cs[i]), s2 = *reinterpret_cast<const __half2*>(&sn[i]);
-                            const __half2 u = __hfma2(lo, c2, __hmul2(hi, s2));                 // lo*cos + hi*sin
-                            const __half2 w2 = __hfma2(hi, c2, __hneg2(__hmul2(lo, s2)));       // hi*cos - lo*sin
-                            klo[c][i] = *reinterpret_cast<const uint32_t*>(&u);
-                            khi[c][i] = *reinterpret_cast<const uint32_t*>(&w2);
-                        }
-                    }
-                } else {
-                    const float* cp = p.cosc + (size_t)delta * HALF + 8 * g;
-                    const float* sp = p.sinc + (size_t)delta * HALF + 8 * g;
-                    const float4 c0 = __ldg(reinterpret_cast<const float4*>(cp)), c1 = __ldg(reinterpret_cast<const float4*>(cp + 4));
-                    const float4 s0 = __ldg(reinterpret_cast<const float4*>(sp)), s1 = __ldg(reinterpret_cast<const float4*>(sp + 4));
-                    const float cs[8] = {c0.x * p.scale, c0.y * p.scale, c0.z * p.scale, c0.w * p.scale,
-                                         c1.x * p.scale, c1.y * p.scale, c1.z * p.scale, c1.w * p.scale};
-                    const float sn[8] = {s0.x * p.scale, s0.y * p.scale, s0.z * p.scale, s0.w * p.scale,
-                                         s1.x * p.scale, s1.y * p.scale, s1.z * p.scale, s1.w * p.scale};
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        const __half* krow = lkr + (((int64_t)b * Nl + node0 + col[c]) * p.Hkv + hk) * D + 8 * g;
-                        uint4 x = make_uint4(0, 0, 0, 0), y = make_uint4(0, 0, 0, 0);
-                        if (cv[c]) { x = ldg16(krow); y = ldg16(krow + HALF); }
-                        const uint32_t xw[4] = {x.x, x.y, x.z, x.w}, yw[4] = {y.x, y.y, y.z, y.w};
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            const float2 lo = FS::unpack(xw[i]), hi = FS::unpack(yw[i]);
-                            klo[c][i] = FS::pack(lo.x * cs[2 * i] + hi.x * sn[2 * i], lo.y * cs[2 * i + 1] + hi.y * sn[2 * i + 1]);
-                            khi[c][i] = FS::pack(hi.x * cs[2 * i] - lo.x * sn[2 * i], hi.y * cs[2 * i + 1] - lo.y * sn[2 * i + 1]);
-                        }
-                    }
-                }
-#pragma unroll
-                for (int w = 0; w < 8; ++w) {
-                    const uint32_t sel = (w & 1) ? 0x7632u : 0x5410u;
-                    FS::mma(dqa[w], ds0, ds1, ds2, ds3, __byte_perm(klo[0][w >> 1], klo[1][w >> 1], sel),
-                            __byte_perm(klo[2][w >> 1], klo[3][w >> 1], sel));
-                    FS::mma(dqa[8 + w], ds0, ds1, ds2, ds3, __byte_perm(khi[0][w >> 1], khi[1][w >> 1], sel),
-                            __byte_perm(khi[2][w >> 1], khi[3][w >> 1], sel));
-                }
+            for (int ks = 0; ks < KS; ++ks) {
+                FS::mma(dqa[2 * ks], ds0, ds1, ds2, ds3, movmatrix_trans(kr[0][0][ks]), movmatrix_trans(kr[1][0][ks]));
+                FS::mma(dqa[2 * ks + 1], ds0, ds1, ds2, ds3, movmatrix_trans(kr[0][1][ks]), movmatrix_trans(kr[1][1][ks]));
             }
 
             // ---- dK'[node0 + c] += dS^T q^_a and dV[node0 + c] += P^T dO, rows c = g and g + 8 ----
@@ -236,7 +187,7 @@ __global__ void HTREE_BWD_BOUNDS bwd_mma_kernel(const __grid_constant__ AttnPara
             float* dvrow[2];
 #pragma unroll
             for (int rr = 0; rr < 2; ++rr) {
-                const int64_t off = (((int64_t)b * Nl + node0 + g + 8 * rr) * p.Hkv + hk) * D + 4 * r;
+                const int64_t off = (((int64_t)b * Nl + node0 + g + 8 * rr) * p.Hkv + hk) * D + 4 * r;   // position 16m + 4r + i
                 dkrow[rr] = dkl + off;
                 dvrow[rr] = dvl + off;
             }
@@ -269,33 +220,35 @@ __global__ void HTREE_BWD_BOUNDS bwd_mma_kernel(const __grid_constant__ AttnPara
         }
     }
 
-    // ---- dq: this thread owns columns 64*hh + 16*r + [0,16) of rows g and g+8 ----
+    // ---- dq: this thread owns columns PPT*r + [0, PPT) of both halves of rows g and g+8 ----
 #pragma unroll
     for (int rr = 0; rr < 2; ++rr) {
         if (!row_ok[rr]) continue;
         float* dqrow = p.dq + (hbase + g + 8 * rr) * D;
 #pragma unroll
-        for (int hh = 0; hh < 2; ++hh) {
-            float4* dst = reinterpret_cast<float4*>(dqrow + 64 * hh + 16 * r);
-            dst[0] = make_float4(dqa[hh * 8 + 0][2 * rr], dqa[hh * 8 + 1][2 * rr], dqa[hh * 8 + 2][2 * rr], dqa[hh * 8 + 3][2 * rr]);
-            dst[1] = make_float4(dqa[hh * 8 + 4][2 * rr], dqa[hh * 8 + 5][2 * rr], dqa[hh * 8 + 6][2 * rr], dqa[hh * 8 + 7][2 * rr]);
-            dst[2] = make_float4(dqa[hh * 8 + 0][2 * rr + 1], dqa[hh * 8 + 1][2 * rr + 1], dqa[hh * 8 + 2][2 * rr + 1], dqa[hh * 8 + 3][2 * rr + 1]);
-            dst[3] = make_float4(dqa[hh * 8 + 4][2 * rr + 1], dqa[hh * 8 + 5][2 * rr + 1], dqa[hh * 8 + 6][2 * rr + 1], dqa[hh * 8 + 7][2 * rr + 1]);
+        for (int hf = 0; hf < 2; ++hf) {
+            float4* dst = reinterpret_cast<float4*>(dqrow + hf * HALF + PPT * r);
+#pragma unroll
+            for (int m = 0; m < KS / 2; ++m)
+                dst[m] = make_float4(dqa[2 * (2 * m) + hf][2 * rr], dqa[2 * (2 * m) + hf][2 * rr + 1],
+                                     dqa[2 * (2 * m + 1) + hf][2 * rr], dqa[2 * (2 * m + 1) + hf][2 * rr + 1]);
         }
     }
 }
 
 // Turns the private accumulator layout of bwd_mma_kernel into gradients, in place, one 16-lane group per row:
-// un-permute both buffers (position 16m + 4r + i of each half <-> column 16r + 4m + i) and rotate dK' back by the
+// un-permute both buffers (position 16m + 4r + i of each half <-> column (D/8)*r + 4m + i) and rotate dK' back by the
 // node's child index, dK = R(node % CR)^T dK' (inverse of the rotation in rotate_keys_kernel; src/naive.py:31-38).
+template <int D>
 __global__ void __launch_bounds__(256) finalize_grads_kernel(float* dk, float* dv, const float* cosc, const float* sinc,
                                                              int64_t rows, int Hkv, int N, int CR) {
-    constexpr int D = 128, HALF = 64;
-    const int64_t row = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 4;
-    const int j = threadIdx.x & 15;                      // position group 4j .. 4j+3 of each half
+    constexpr int HALF = D / 2, PPT = HALF / 4, LPR = HALF / 4;   // LPR lanes per row: one float4 of each half per lane
+    const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t row = tid / LPR;
+    const int j = (int)(tid % LPR);                      // position group 4j .. 4j+3 of each half
     const bool on = row < rows;
     const int m = j >> 2, r = j & 3;
-    const int col = 16 * r + 4 * m;                      // first of the 4 columns stored at positions 4j .. 4j+3
+    const int col = PPT * r + 4 * m;                     // first of the 4 columns stored at positions 4j .. 4j+3
     float4 klo = make_float4(0, 0, 0, 0), khi = klo, vlo = klo, vhi = klo;
     float* dkr = dk + row * D;
     float* dvr = dv + row * D;
@@ -319,25 +272,25 @@ __global__ void __launch_bounds__(256) finalize_grads_kernel(float* dk, float* d
 
 bool bwd_mma_supported(const AttnParams& p, int dtype) {
     if (dtype != HTREE_BF16 && dtype != HTREE_F16) return false;
-    if (p.K != 128 || p.V != 128 || p.G > 16 || p.CR != 16) return false;
+    if (p.K != p.V || (p.K != 64 && p.K != 128) || p.G > 16 || p.CR != 16) return false;
     for (int l = 0; l < p.L; ++l) if (!p.lkr[l]) return false;
     return bwd_mma_smem_per_warp(p.TK) * MWB <= 200 * 1024;
 }
 
-template <typename T, bool ROT16>
+template <typename T, int D, bool ROT16>
 static int launch_bwd_mma_t(const AttnParams& p, cudaStream_t st) {
     const size_t smem = bwd_mma_smem_per_warp(p.TK) * MWB;
     dim3 grid((p.T + MWB - 1) / MWB, p.B * p.Hkv);
-    cudaError_t e = cudaFuncSetAttribute(bwd_mma_kernel<T, ROT16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(bwd_mma_kernel<T, D, ROT16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    bwd_mma_kernel<T, ROT16><<<grid, MWB * 32, smem, st>>>(p);
+    bwd_mma_kernel<T, D, ROT16><<<grid, MWB * 32, smem, st>>>(p);
     note_launch();
     e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
     for (int l = 0; l < p.L; ++l) {
         const int64_t rows = (int64_t)p.B * p.ln[l] * p.Hkv;
-        const unsigned blocks = (unsigned)((rows * 16 + 255) / 256);
-        finalize_grads_kernel<<<blocks, 256, 0, st>>>(p.dk[l], p.dv[l], p.cosc, p.sinc, rows, p.Hkv, p.ln[l], p.CR);
+        const unsigned blocks = (unsigned)((rows * (D / 8) + 255) / 256);
+        finalize_grads_kernel<D><<<blocks, 256, 0, st>>>(p.dk[l], p.dv[l], p.cosc, p.sinc, rows, p.Hkv, p.ln[l], p.CR);
         note_launch();
         e = cudaGetLastError();
         if (e != cudaSuccess) return (int)e;
@@ -347,8 +300,12 @@ static int launch_bwd_mma_t(const AttnParams& p, cudaStream_t st) {
 
 int launch_bwd_mma(const AttnParams& p, int dtype, cudaStream_t st) {
     const bool rot16 = p.cosh != nullptr && p.sinh != nullptr;
-    if (dtype == HTREE_BF16) return rot16 ? launch_bwd_mma_t<__nv_bfloat16, true>(p, st) : launch_bwd_mma_t<__nv_bfloat16, false>(p, st);
-    return rot16 ? launch_bwd_mma_t<__half, true>(p, st) : launch_bwd_mma_t<__half, false>(p, st);
+    if (p.K == 128) {
+        if (dtype == HTREE_BF16) return rot16 ? launch_bwd_mma_t<__nv_bfloat16, 128, true>(p, st) : launch_bwd_mma_t<__nv_bfloat16, 128, false>(p, st);
+        return rot16 ? launch_bwd_mma_t<__half, 128, true>(p, st) : launch_bwd_mma_t<__half, 128, false>(p, st);
+    }
+    if (dtype == HTREE_BF16) return rot16 ? launch_bwd_mma_t<__nv_bfloat16, 64, true>(p, st) : launch_bwd_mma_t<__nv_bfloat16, 64, false>(p, st);
+    return rot16 ? launch_bwd_mma_t<__half, 64, true>(p, st) : launch_bwd_mma_t<__half, 64, false>(p, st);
 }
 
 }  // namespace htree

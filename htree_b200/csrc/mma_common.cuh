@@ -81,10 +81,12 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
 //   qraw holds the query rows as IEEE half pairs (load_rows_half).  ROT16 selects how the query is rotated: false =
 //   fp32 arithmetic with the fp32 tables, one rounding to half at the end; true = packed half2 arithmetic with the
 //   pre-scaled half tables (4 instead of 14 instructions per pair of pairs, about twice the rounding noise).
-template <int D, bool KEEP_A, bool ROT16>
+//   With KEEP_K (backward) kr receives the keys rotated back into the query's frame, scale * R(-delta) K', in the same
+//   fragment order ([tile][half][k-step]); transposed with movmatrix they are the B fragments of dq += dS K~.
+template <int D, bool KEEP_A, bool ROT16, bool KEEP_K = false>
 __device__ __forceinline__ void score_chunk(const AttnParams& p, const __half* lkr, int Nl, int b, int hk, int node0, int delta,
                                             int g, int r, const uint32_t (&qraw)[2][2][D / 16], float (&S0)[4], float (&S1)[4],
-                                            uint32_t (&qa)[KEEP_A ? D / 16 : 1][4]) {
+                                            uint32_t (&qa)[KEEP_A ? D / 16 : 1][4], uint32_t (*kr)[2][D / 16] = nullptr) {
     constexpr int HALF = D / 2, KS = D / 16, PPT = HALF / 4, NV = PPT / 8;
     using FS = Frag<__half>;
     const float* cp = p.cosc + (size_t)delta * HALF + PPT * r;
@@ -107,6 +109,19 @@ __device__ __forceinline__ void score_chunk(const AttnParams& p, const __half* l
         uint32_t ch[KS], sh[KS];   // (cos, sin) * scale of pairs (2ks, 2ks+1), packed half2
         ldg_vec<NV>(chp, true, ch);
         ldg_vec<NV>(shp, true, sh);
+        if (KEEP_K) {
+#pragma unroll
+            for (int tl = 0; tl < 2; ++tl)
+#pragma unroll
+                for (int ks = 0; ks < KS; ++ks) {
+                    const __half2 c2 = *reinterpret_cast<const __half2*>(&ch[ks]), s2 = *reinterpret_cast<const __half2*>(&sh[ks]);
+                    const __half2 lo = *reinterpret_cast<const __half2*>(&kb[tl][0][ks]), hi = *reinterpret_cast<const __half2*>(&kb[tl][1][ks]);
+                    const __half2 u = __hfma2(lo, c2, __hmul2(hi, s2));                 // lo*cos + hi*sin
+                    const __half2 w = __hfma2(hi, c2, __hneg2(__hmul2(lo, s2)));        // hi*cos - lo*sin
+                    kr[tl][0][ks] = *reinterpret_cast<const uint32_t*>(&u);
+                    kr[tl][1][ks] = *reinterpret_cast<const uint32_t*>(&w);
+                }
+        }
 #pragma unroll
         for (int ks = 0; ks < KS; ++ks) {
             uint32_t a[4];
@@ -151,6 +166,15 @@ __device__ __forceinline__ void score_chunk(const AttnParams& p, const __half* l
                 a[2 + rr] = FS::pack(lo.x * s0 + hi.x * c0, lo.y * s1 + hi.y * c1);     // rotated high half
             }
             if (KEEP_A) { qa[KEEP_A ? ks : 0][0] = a[0]; qa[KEEP_A ? ks : 0][1] = a[1]; qa[KEEP_A ? ks : 0][2] = a[2]; qa[KEEP_A ? ks : 0][3] = a[3]; }
+            if (KEEP_K) {
+#pragma unroll
+                for (int tl = 0; tl < 2; ++tl) {
+                    const float2 lo = FS::unpack(kb[tl][0][ks]), hi = FS::unpack(kb[tl][1][ks]);
+                    const float c0 = cs[2 * u], c1 = cs[2 * u + 1], s0 = sn[2 * u], s1 = sn[2 * u + 1];
+                    kr[tl][0][ks] = FS::pack(lo.x * c0 + hi.x * s0, lo.y * c1 + hi.y * s1);
+                    kr[tl][1][ks] = FS::pack(hi.x * c0 - lo.x * s0, hi.y * c1 - lo.y * s1);
+                }
+            }
             if (u) {
                 FS::mma(T0, a[0], a[1], a[2], a[3], kb[0][0][ks], kb[0][1][ks]);
                 FS::mma(T1, a[0], a[1], a[2], a[3], kb[1][0][ks], kb[1][1][ks]);

@@ -316,7 +316,7 @@ def _oracle_grads_with_our_forward(c, q, k, v, dO, out, ctx):
     return oracle.backward(parity.f32(q), fwd, parity.f32(dO), c["CR"], c["TK"], c["dtype"])
 
 
-@pytest.mark.parametrize("name", ["bf16_D128_G16_T2048", "f16_D128_G4_T1500"])
+@pytest.mark.parametrize("name", ["bf16_D128_G16_T2048", "f16_D128_G4_T1500", "bf16_D64_G8_T3000"])
 def test_tensor_core_backward_against_oracle(name):
     ops = _ops()
     c = MMA_CASES[name]
