@@ -156,6 +156,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg3", choices=sorted(configs.CONFIGS))
     ap.add_argument("--t-scale", type=int, default=1, help="divide T by this (debug only; reported in config)")
+    ap.add_argument("--shard", default="auto", choices=["auto", "units", "sequence"],
+                    help="units: (batch, kv head) round-robin; sequence: query positions split, pooled levels all-gathered "
+                         "(forward-only workloads); auto = sequence for cfg4, units otherwise")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=15.0)
@@ -203,17 +206,30 @@ def main():
 
     B, T, H, Hkv, D, CR, TK, MTN = c["B"], c["T"], c["H"], c["H_kv"], c["D"], c["CR"], c["TK"], c["MTN"]
     G = H // Hkv
-    units = hdist.unit_partition(B * Hkv, world, rank)
-    U = len(units)
     bwd = "bwd" in c["mode"]
-    gen = torch.Generator(device=dev).manual_seed(42 + rank)
+    seq_mode = (args.shard == "sequence" or (args.shard == "auto" and args.workload == "cfg4")) and not bwd
+    if seq_mode:
+        cfg_desc["sharding"] = ("query positions split evenly over ranks; k, v replicated; one all_gather_into_tensor per "
+                                "pooled tree level (NCCL)")
+    units = hdist.unit_partition(B * Hkv, world, rank) if not seq_mode else list(range(B * Hkv))
+    U = len(units)
+    gen = torch.Generator(device=dev).manual_seed(42 + (0 if seq_mode else rank))
 
     def randn(*shape):
         return torch.randn(*shape, generator=gen, device=dev, dtype=torch.float32).to(tdt)
 
-    # local problem: U independent single-KV-head sequences
-    q = randn(U, T, G, D); k = randn(U, T, 1, D); v = randn(U, T, 1, D)
-    dO = randn(U, T, G, D) if bwd else None
+    if seq_mode:
+        # one long sequence per batch element: every rank holds the same k, v and its own slice of the queries
+        k = randn(B, T, Hkv, D); v = randn(B, T, Hkv, D)
+        n_lv = len(configs.level_sizes(T, CR, MTN))
+        t0, t1 = hdist.query_range(T, world, rank, CR, n_lv) if world > 1 else (0, T)
+        gen.manual_seed(1042 + rank)
+        q = randn(B, t1 - t0, H, D)
+        dO = None
+    else:
+        # local problem: U independent single-KV-head sequences
+        q = randn(U, T, G, D); k = randn(U, T, 1, D); v = randn(U, T, 1, D)
+        dO = randn(U, T, G, D) if bwd else None
 
     def step(q_, k_, v_, dO_, timers=None):
         if timers is not None:
@@ -226,7 +242,10 @@ def main():
             if timers is not None:
                 timers[2].record()
             return out, dq, dk, dv
-        out = ht.htree_forward(q_, k_, v_, CR, MTN, TK)
+        if seq_mode:
+            out = hdist.htree_forward_sequence_parallel(q_, k_, v_, CR, MTN, TK) if world > 1 else ht.htree_forward(q_, k_, v_, CR, MTN, TK)
+        else:
+            out = ht.htree_forward(q_, k_, v_, CR, MTN, TK)
         if timers is not None:
             timers[1].record()
         return (out,)
@@ -299,6 +318,12 @@ def main():
         e2e_chunk = max(1, U // 8)      # units resident per pipeline stage (two stages in flight)
 
         def e2e_step():
+            if seq_mode:      # a single long sequence cannot be cut along the batch: plain copies around the call
+                dev_in = [h.to(dev, non_blocking=True) for h in host_in]
+                res = step(dev_in[0], dev_in[1], dev_in[2], None)
+                host_out[0].copy_(res[0], non_blocking=True)
+                torch.cuda.synchronize()
+                return
             hhost.forward_backward_host(host_in[0], host_in[1], host_in[2], host_in[3] if bwd else None, CR, MTN, TK,
                                         chunk=e2e_chunk, device=dev, outputs=host_out)
 
@@ -320,8 +345,9 @@ def main():
             h2d, d2h = int(tt[0].item()), int(tt[1].item())
         e2e = {"value": B * T / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": n_e2e,
-               "api": "htree_b200.host.forward_backward_host: pinned host tensors in and out, batch chunks pipelined "
-                      "over three streams (H2D | kernels | D2H)"}
+               "api": ("htree_forward_sequence_parallel with pinned host tensors copied in and out around the call" if seq_mode
+                       else "htree_b200.host.forward_backward_host: pinned host tensors in and out, batch chunks "
+                            "pipelined over three streams (H2D | kernels | D2H)")}
         del host_in, host_out
 
     if rank != 0:
@@ -350,9 +376,10 @@ def main():
                 "forward_compulsory_hbm_frac": cm["bytes_fwd"] / world / (fwd_ms * 1e-3) / 1e9 / pk["hbm_gbs"]}
     es = 4 if c["dtype"] == "float32" else 2
     lv_sizes = cm["levels"]
-    tree_bytes = es * U * 2 * D * sum(lv_sizes[i] + lv_sizes[i + 1] for i in range(len(lv_sizes) - 1))     # pool K and V
+    n_rows = B * Hkv if seq_mode else U
+    tree_bytes = es * n_rows * 2 * D * sum(lv_sizes[i] + lv_sizes[i + 1] for i in range(len(lv_sizes) - 1))     # pool K and V
     if es == 2:
-        tree_bytes += 2 * 2 * U * D * sum(lv_sizes)                                                         # K -> K'
+        tree_bytes += 2 * 2 * n_rows * D * sum(lv_sizes)                                                         # K -> K'
     streaming = {"kernels": "tree_build_kernel + rotate_keys_kernel (all levels, rank 0)", "ms": tree_ms,
                  "algorithmic_bytes": tree_bytes, "achieved": tree_bytes / (tree_ms * 1e-3) / 1e9, "unit": "GB/s",
                  "peak": pk["hbm_gbs"], "frac": tree_bytes / (tree_ms * 1e-3) / 1e9 / pk["hbm_gbs"],
