@@ -368,3 +368,43 @@ def test_host_buffer_pipeline_matches_device_calls():
         assert torch.allclose(a.float(), b.to(torch.bfloat16).float().cpu(), rtol=2e-2, atol=2e-3)   # reduction order
     (o2,) = host.forward_backward_host(hq, hk, hv, None, c["CR"], c["MTN"], c["TK"], chunk=3)
     assert torch.equal(o2, out.cpu())
+
+
+@pytest.mark.parametrize("c", [
+    # group of 32 heads per KV head: outside the tensor-core kernel (<= 16), generic kernel processes heads in chunks
+    dict(B=1, T=600, H=32, H_kv=1, K=64, V=64, CR=16, TK=8, MTN=40, dtype="bfloat16", seed=71),
+    # K != V with 16-bit storage: generic kernel
+    dict(B=2, T=500, H=4, H_kv=2, K=64, V=32, CR=16, TK=4, MTN=32, dtype="float16", seed=72),
+    # top_k not a multiple of anything, sequence shorter than one parent block, one-token sequence
+    dict(B=1, T=333, H=6, H_kv=2, K=32, V=32, CR=4, TK=7, MTN=20, dtype="float32", seed=73),
+    dict(B=2, T=3, H=2, H_kv=1, K=16, V=16, CR=16, TK=4, MTN=8, dtype="float32", seed=74),
+    dict(B=1, T=1, H=2, H_kv=2, K=16, V=16, CR=4, TK=2, MTN=4, dtype="float32", seed=75),
+    # tensor-core kernel with a ragged tail, odd top_k and a group of 5 (rows 5..15 of the MMA are padding)
+    dict(B=1, T=1777, H=5, H_kv=1, K=128, V=128, CR=16, TK=11, MTN=100, dtype="bfloat16", seed=76),
+], ids=["G32", "KneV", "odd_topk", "T3", "T1", "mma_ragged_G5"])
+def test_edge_shapes_forward_backward(c):
+    ops = _ops()
+    q, k, v, dO = parity.case_inputs(c)
+    qd, kd, vd, dOd = (x.to(DEV) for x in (q, k, v, dO))
+    out, ctx = ops.htree_forward(qd, kd, vd, c["CR"], c["MTN"], c["TK"], _save_for_backward=True)
+    dq, dk, dv = ops.htree_backward(dOd, qd, out, ctx)
+    torch.cuda.synchronize(); ops.check_status()
+    ref = oracle.forward(parity.f32(q), parity.f32(k), parity.f32(v), c["CR"], c["MTN"], c["TK"], dtype=c["dtype"],
+                         return_importance=True)
+    L = ctx["num_layers"]
+    assert L == ref["num_layers"]
+    ours_parents = [ctx["per_layer_parents"][l].cpu().numpy() for l in range(L)]
+    fast = ctx["layers_k_rot"] is not None and c["K"] == c["V"] and c["K"] in (64, 128) and c["H"] // c["H_kv"] <= 16 and c["CR"] == 16
+    same, near = compare_with_oracle(c, q, k, v, ours_parents, ref, EPS_SEL_MMA if fast else EPS_SEL[c["dtype"]])
+    G = c["H"] // c["H_kv"]
+    rows = np.repeat(same, G).reshape(c["B"], c["T"], c["H"])
+    assert same.mean() > 0.97
+    assert_out_close(parity.f32(out)[rows], ref["out_rounded"][rows], c["dtype"])
+    fwd = dict(ref)
+    fwd["parents"] = np.stack(ours_parents)
+    fwd["gmax"] = parity.f32(ctx["global_max"]); fwd["gsum"] = parity.f32(ctx["global_sum"]); fwd["out_rounded"] = parity.f32(out)
+    g = oracle.backward(parity.f32(q), fwd, parity.f32(dO), c["CR"], c["TK"], c["dtype"])
+    tol = 1e-4 if c["dtype"] == "float32" else (2e-2 if fast else 2e-3)
+    for nm, t in (("dq", dq), ("dk", dk), ("dv", dv)):
+        r = g[nm + "_f32"]
+        assert float(np.abs(parity.f32(t) - r).max()) <= tol * max(1.0, float(np.abs(r).max())), nm
