@@ -55,8 +55,14 @@ __host__ __device__ inline size_t mma_smem_per_warp(int TK, int CR) {
     return (b + 15) & ~size_t(15);
 }
 
-template <typename T, int D, bool ROT16>
-__global__ void HTREE_FWD_BOUNDS fwd_mma_kernel(const __grid_constant__ AttnParams p) {
+// MODE 0: whole forward in one kernel.  MODE 1: selections only (no accumulator state, so far fewer registers and more
+// resident warps); MODE 2: accumulation only, reading the per-level parent lists that a MODE 1 launch wrote.  When the
+// caller provides parent buffers the forward runs as MODE 1 + MODE 2.
+#ifndef HTREE_SEL_MIN_BLOCKS
+#define HTREE_SEL_MIN_BLOCKS 4   // the selection kernel carries no accumulators: 128 registers, 16 warps per SM
+#endif
+template <typename T, int D, bool ROT16, int MODE>
+__global__ void __launch_bounds__(MW * 32, MODE == 1 ? HTREE_SEL_MIN_BLOCKS : HTREE_FWD_MIN_BLOCKS) fwd_mma_kernel(const __grid_constant__ AttnParams p) {
     constexpr int CR = 16;
     constexpr int HALF = D / 2;
     constexpr int KS = D / 16;        // k-steps of the score product
@@ -82,7 +88,8 @@ __global__ void HTREE_FWD_BOUNDS fwd_mma_kernel(const __grid_constant__ AttnPara
     int32_t* par = reinterpret_cast<int32_t*>(selw + (maxc + 31) / 32);
     int32_t* nxt = par + TK;
 
-    const bool select_only = (p.flags & HTREE_FWD_SELECT_ONLY) != 0;
+    constexpr bool kSelectKernel = MODE == 1, kAccumulateKernel = MODE == 2;
+    const bool select_only = kSelectKernel || (MODE == 0 && (p.flags & HTREE_FWD_SELECT_ONLY) != 0);
     const int64_t hbase = ((int64_t)b * p.Tq + tl) * p.H + (int64_t)hk * G;
     const int64_t qidx = ((int64_t)b * p.Tq + tl) * p.Hkv + hk;
     const bool row_ok[2] = {g < G, g + 8 < G};
@@ -108,7 +115,13 @@ __global__ void HTREE_FWD_BOUNDS fwd_mma_kernel(const __grid_constant__ AttnPara
         const int Nl = p.ln[l];
         const __half* lkr = reinterpret_cast<const __half*>(p.lkr[l]);
         const T* lv = reinterpret_cast<const T*>(p.lv[l]);
-        if (p.parents[l]) for (int i = lane; i < TK; i += 32) p.parents[l][qidx * TK + i] = par[i];
+        if (kAccumulateKernel) {
+            __syncwarp();
+            for (int i = lane; i < TK; i += 32) par[i] = p.parents[l][qidx * TK + i];
+            __syncwarp();
+        } else if (p.parents[l]) {
+            for (int i = lane; i < TK; i += 32) p.parents[l][qidx * TK + i] = par[i];
+        }
         if (select_only && l == 0) break;
         int np = 0;
         for (int i = lane; i < TK; i += 32) np += par[i] >= 0;
@@ -186,7 +199,35 @@ __global__ void HTREE_FWD_BOUNDS fwd_mma_kernel(const __grid_constant__ AttnPara
                 }
         };
 
-        if (l > 0) {
+        if (l > 0 && kAccumulateKernel) {
+            if (nc > TK) {
+                // kept-candidate bit mask from the two sorted lists: the level's parents and the next level's parents
+                for (int i = lane; i < (nc + 31) / 32; i += 32) selw[i] = 0u;
+                for (int i = lane; i < TK; i += 32) nxt[i] = p.parents[l - 1][qidx * TK + i];
+                __syncwarp();
+                for (int i = lane; i < TK; i += 32) {
+                    const int node = nxt[i];
+                    if (node < 0) continue;
+                    const int parent = node / CR;
+                    int lo = 0, hi = np;
+                    while (lo < hi) { const int mid = (lo + hi) >> 1; if (par[mid] < parent) lo = mid + 1; else hi = mid; }
+                    if (lo < np && par[lo] == parent) {
+                        const int j = lo * CR + node % CR;
+                        atomicOr(&selw[j >> 5], 1u << (j & 31));
+                    }
+                }
+                __syncwarp();
+                for (int a = 0; a < np; ++a) {
+                    const uint32_t kept = (selw[a >> 1] >> (16 * (a & 1))) & 0xffffu;
+                    const uint32_t valid = a == np - 1 ? ((2u << rc) - 1u) : 0xffffu;
+                    const uint32_t mask = ~kept & valid;
+                    if (mask == 0) continue;
+                    float S0[4], S1[4];
+                    score(a, S0, S1, false);
+                    accumulate_chunk(a, S0, S1, mask);
+                }
+            }
+        } else if (l > 0) {
             if (nc <= TK) {   // every candidate is kept, nothing to score or accumulate
                 __syncwarp();
                 for (int j = lane; j < TK; j += 32) nxt[j] = j < nc ? par[j / CR] * CR + j % CR : -1;
@@ -314,16 +355,26 @@ __global__ void HTREE_FWD_BOUNDS fwd_mma_kernel(const __grid_constant__ AttnPara
     }
 }
 
-template <typename T, int D, bool ROT16>
-static int launch_mma_tdr(const AttnParams& p, cudaStream_t st) {
+template <typename T, int D, bool ROT16, int MODE>
+static int launch_mma_mode(const AttnParams& p, cudaStream_t st) {
     const size_t smem = mma_smem_per_warp(p.TK, 16) * MW;
     if (smem > 200 * 1024) return HTREE_E_UNSUPPORTED;
-    cudaError_t e = cudaFuncSetAttribute(fwd_mma_kernel<T, D, ROT16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(fwd_mma_kernel<T, D, ROT16, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     dim3 grid((p.Tq + MW - 1) / MW, p.B * p.Hkv);
-    fwd_mma_kernel<T, D, ROT16><<<grid, MW * 32, smem, st>>>(p);
+    fwd_mma_kernel<T, D, ROT16, MODE><<<grid, MW * 32, smem, st>>>(p);
     note_launch();
     return (int)cudaGetLastError();
+}
+
+template <typename T, int D, bool ROT16>
+static int launch_mma_tdr(const AttnParams& p, cudaStream_t st) {
+    if (p.flags & HTREE_FWD_SELECT_ONLY) return launch_mma_mode<T, D, ROT16, 1>(p, st);
+    bool have_parents = !(p.flags & HTREE_FWD_FUSED);
+    for (int l = 0; l < p.L; ++l) have_parents = have_parents && p.parents[l] != nullptr;
+    if (!have_parents) return launch_mma_mode<T, D, ROT16, 0>(p, st);
+    const int rc = launch_mma_mode<T, D, ROT16, 1>(p, st);          // selections -> parents[l]
+    return rc ? rc : launch_mma_mode<T, D, ROT16, 2>(p, st);         // accumulation given the selections
 }
 
 template <typename T, int D>
