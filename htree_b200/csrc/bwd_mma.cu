@@ -180,16 +180,21 @@ __global__ void HTREE_BWD_BOUNDS bwd_mma_kernel(const __grid_constant__ AttnPara
             // ---- dK'[node0 + c] += dS^T q^_a and dV[node0 + c] += P^T dO, rows c = g and g + 8 ----
             // The level buffers are used in a private layout here: dK' is the gradient of the pre-rotated key (the
             // rotation by the child index is undone once per node by finalize_grads_kernel, not once per visit), and
-            // within each 64-wide half position 16*m + 4*r + i holds column 16*r + 4*m + i, so that the four threads
-            // of a quad reduce into 64 contiguous bytes (two full sectors per row and instruction).
-            const bool rowc[2] = {(mask >> g & 1) != 0, (mask >> (g + 8) & 1) != 0};
-            float* dkrow[2];
-            float* dvrow[2];
+            // position 32*m + 16*half + 4*r + i of a row holds column half*D/2 + (D/8)*r + 4*m + i.
+            // Rows are written by PAIRS of quads: lanes of rows g and g^1 swap one half each, so that the 8 lanes write
+            // 128 contiguous bytes (a whole cache line) of ONE row per instruction: position 32*m + 16*half + 4*r + i.
+            const bool odd = (g & 1) != 0;
+            const int ge = g & ~1;
+            bool rowa[2], rowb[2];
+            float* dka[2]; float* dkb[2]; float* dva[2]; float* dvb[2];
 #pragma unroll
             for (int rr = 0; rr < 2; ++rr) {
-                const int64_t off = (((int64_t)b * Nl + node0 + g + 8 * rr) * p.Hkv + hk) * D + 4 * r;   // position 16m + 4r + i
-                dkrow[rr] = dkl + off;
-                dvrow[rr] = dvl + off;
+                rowa[rr] = (mask >> (ge + 8 * rr) & 1) != 0;          // even row of the pair
+                rowb[rr] = (mask >> (ge + 1 + 8 * rr) & 1) != 0;      // odd row of the pair
+                const int64_t offa = (((int64_t)b * Nl + node0 + ge + 8 * rr) * p.Hkv + hk) * D + (odd ? 16 : 0) + 4 * r;
+                const int64_t offb = offa + (int64_t)p.Hkv * D;
+                dka[rr] = dkl + offa; dkb[rr] = dkl + offb;
+                dva[rr] = dvl + offa; dvb[rr] = dvl + offb;
             }
 #pragma unroll
             for (int m = 0; m < KS / 2; ++m) {
@@ -210,11 +215,23 @@ __global__ void HTREE_BWD_BOUNDS bwd_mma_kernel(const __grid_constant__ AttnPara
                 }
 #pragma unroll
                 for (int rr = 0; rr < 2; ++rr) {
-                    if (!rowc[rr]) continue;
-                    red_add_v4(dkrow[rr] + 16 * m, klo_[rr][0], klo_[rr][1], klo_[rr][2], klo_[rr][3]);
-                    red_add_v4(dkrow[rr] + HALF + 16 * m, khi_[rr][0], khi_[rr][1], khi_[rr][2], khi_[rr][3]);
-                    red_add_v4(dvrow[rr] + 16 * m, vlo_[rr][0], vlo_[rr][1], vlo_[rr][2], vlo_[rr][3]);
-                    red_add_v4(dvrow[rr] + HALF + 16 * m, vhi_[rr][0], vhi_[rr][1], vhi_[rr][2], vhi_[rr][3]);
+                    float ka[4], kb_[4], va[4], vb_[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        // even lanes give away their high half and receive the partner's low half; odd lanes the reverse
+                        const float rk = __shfl_xor_sync(0xffffffffu, odd ? klo_[rr][i] : khi_[rr][i], 4);
+                        const float rv = __shfl_xor_sync(0xffffffffu, odd ? vlo_[rr][i] : vhi_[rr][i], 4);
+                        ka[i] = odd ? rk : klo_[rr][i];  kb_[i] = odd ? khi_[rr][i] : rk;
+                        va[i] = odd ? rv : vlo_[rr][i];  vb_[i] = odd ? vhi_[rr][i] : rv;
+                    }
+                    if (rowa[rr]) {
+                        red_add_v4(dka[rr] + 32 * m, ka[0], ka[1], ka[2], ka[3]);
+                        red_add_v4(dva[rr] + 32 * m, va[0], va[1], va[2], va[3]);
+                    }
+                    if (rowb[rr]) {
+                        red_add_v4(dkb[rr] + 32 * m, kb_[0], kb_[1], kb_[2], kb_[3]);
+                        red_add_v4(dvb[rr] + 32 * m, vb_[0], vb_[1], vb_[2], vb_[3]);
+                    }
                 }
             }
         }
@@ -237,7 +254,7 @@ __global__ void HTREE_BWD_BOUNDS bwd_mma_kernel(const __grid_constant__ AttnPara
 }
 
 // Turns the private accumulator layout of bwd_mma_kernel into gradients, in place, one 16-lane group per row:
-// un-permute both buffers (position 16m + 4r + i of each half <-> column (D/8)*r + 4m + i) and rotate dK' back by the
+// un-permute both buffers (position 32m + 16*half + 4r + i <-> column half*D/2 + (D/8)*r + 4m + i) and rotate dK' back by the
 // node's child index, dK = R(node % CR)^T dK' (inverse of the rotation in rotate_keys_kernel; src/naive.py:31-38).
 template <int D>
 __global__ void __launch_bounds__(256) finalize_grads_kernel(float* dk, float* dv, const float* cosc, const float* sinc,
@@ -253,8 +270,9 @@ __global__ void __launch_bounds__(256) finalize_grads_kernel(float* dk, float* d
     float* dkr = dk + row * D;
     float* dvr = dv + row * D;
     if (on) {
-        klo = *reinterpret_cast<const float4*>(dkr + 4 * j); khi = *reinterpret_cast<const float4*>(dkr + HALF + 4 * j);
-        vlo = *reinterpret_cast<const float4*>(dvr + 4 * j); vhi = *reinterpret_cast<const float4*>(dvr + HALF + 4 * j);
+        const int pos = 32 * m + 4 * r;                  // low-half piece; the high-half piece follows 16 floats later
+        klo = *reinterpret_cast<const float4*>(dkr + pos); khi = *reinterpret_cast<const float4*>(dkr + pos + 16);
+        vlo = *reinterpret_cast<const float4*>(dvr + pos); vhi = *reinterpret_cast<const float4*>(dvr + pos + 16);
     }
     __syncwarp();                                        // every lane of the row has read before anyone writes
     if (!on) return;
