@@ -38,7 +38,8 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 # Measured with `ncu --set full` on the same workload at a quarter of the sequence length (profiles/*_cfg3_quarter.md);
 # DRAM traffic grows in proportion to the number of (batch, position, kv head) groups, so the figure is scaled by the
 # ratio of groups.  Values are dram__bytes_read.sum + dram__bytes_write.sum per launch for cfg3 / T=16384.
-NCU_TRAFFIC_BYTES_QUARTER_CFG3 = {"forward": 1.228312e9 + 1.271541e9, "backward": 3.894620e9 + 2.393859e9}
+NCU_TRAFFIC_BYTES_QUARTER_CFG3 = {"forward": (1.081870e9 + 0.193277e9) + (1.421465e9 + 1.073665e9),   # selection + accumulation
+                                  "backward": 3.897394e9 + 2.394069e9}
 
 
 def peaks():
