@@ -198,6 +198,7 @@ def htree_forward(
     scale: Optional[float] = None, rope_base: float = 10000.0,
     _save_for_backward: bool = False, _save_parents: bool = True,
     return_trace: bool = False, _force_generic: bool = False, _q_offset: Optional[int] = None, _layers=None,
+    _fused: bool = False,
 ):
     """htree forward.  q [B,T,H,K], k [B,T,H_kv,K], v [B,T,H_kv,V] -> out [B,T,H,V] in q's dtype.
 
@@ -225,15 +226,18 @@ def htree_forward(
     gmax = torch.empty(B, T, H, dtype=torch.float32, device=dev)
     gsum = torch.empty(B, T, H, dtype=torch.float32, device=dev)
     want_parents = (_save_for_backward and _save_parents) or return_trace
-    parents = [torch.empty(B, T, H_kv, top_k_per_layer, dtype=torch.int32, device=dev) for _ in range(L)] \
-        if want_parents else None
+    # the tensor-core forward is faster as selection kernel + accumulation kernel, which hand the selections over in
+    # these buffers; so they are allocated there even when the caller does not keep them
+    split_forward = layers_kr is not None and not (_force_generic or return_trace or _fused)
+    parents = [torch.empty(B, q.shape[1], H_kv, top_k_per_layer, dtype=torch.int32, device=dev) for _ in range(L)] \
+        if (want_parents or split_forward) else None
     trace = tr = None
     if return_trace:
         tr = (torch.empty(L, B, T, H, dtype=torch.float32, device=dev),
               torch.empty(L, B, T, H, dtype=torch.float32, device=dev),
               torch.empty(L, B, T, H, V, dtype=torch.float32, device=dev))
         trace = _lib.HtreeTrace(tr[0].data_ptr(), tr[1].data_ptr(), tr[2].data_ptr())
-    flags = _lib.FWD_GENERIC if (_force_generic or return_trace) else 0
+    flags = _lib.FWD_GENERIC if (_force_generic or return_trace) else (_lib.FWD_FUSED if _fused else 0)
     half_tables = rope_cache_half(K, cos_cache.shape[0], rope_base, scale, dev) if layers_kr is not None else None
     _run_forward(shape, q, layers_k, layers_v, cos_cache, sin_cache, scale, out, gmax, gsum, parents, trace, flags,
                  layers_kr, half_tables)
@@ -244,7 +248,7 @@ def htree_forward(
         G = H // H_kv
         result.append(dict(
             global_max=gmax, global_sum=gsum,
-            per_layer_parents={l: parents[l] for l in range(L)} if (_save_parents and parents is not None) else None,
+            per_layer_parents={l: parents[l] for l in range(L)} if (_save_parents and want_parents) else None,
             layers_k=layers_k, layers_v=layers_v, layers_k_rot=layers_kr, cos_cache=cos_cache, sin_cache=sin_cache,
             rope_half=half_tables,
             num_layers=L, rope_base=rope_base,

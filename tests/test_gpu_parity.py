@@ -408,3 +408,17 @@ def test_edge_shapes_forward_backward(c):
     for nm, t in (("dq", dq), ("dk", dk), ("dv", dv)):
         r = g[nm + "_f32"]
         assert float(np.abs(parity.f32(t) - r).max()) <= tol * max(1.0, float(np.abs(r).max())), nm
+
+
+def test_split_and_fused_tensor_core_forward_agree():
+    """Selection kernel + accumulation kernel (default) against the single fused kernel: same bits."""
+    ops = _ops()
+    c = MMA_CASES["bf16_D128_G16_T6000_tk64"]
+    q, k, v, _ = (x.to(DEV) for x in parity.case_inputs(c))
+    a, ctx_a = ops.htree_forward(q, k, v, c["CR"], c["MTN"], c["TK"], _save_for_backward=True)
+    b, ctx_b = ops.htree_forward(q, k, v, c["CR"], c["MTN"], c["TK"], _save_for_backward=True, _fused=True)
+    plain = ops.htree_forward(q, k, v, c["CR"], c["MTN"], c["TK"])
+    assert torch.equal(a, b) and torch.equal(a, plain)
+    assert torch.equal(ctx_a["global_max"], ctx_b["global_max"]) and torch.equal(ctx_a["global_sum"], ctx_b["global_sum"])
+    for l in range(ctx_a["num_layers"]):
+        assert torch.equal(ctx_a["per_layer_parents"][l], ctx_b["per_layer_parents"][l])
