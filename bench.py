@@ -316,7 +316,7 @@ def main():
         del outs
 
         from htree_b200 import host as hhost
-        e2e_chunk = max(1, U // 8)      # units resident per pipeline stage (two stages in flight)
+        e2e_chunk = 1                   # units resident per pipeline stage (two stages in flight); small head/tail
 
         def e2e_step():
             if seq_mode:      # a single long sequence cannot be cut along the batch: plain copies around the call
