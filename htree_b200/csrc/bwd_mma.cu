@@ -33,7 +33,7 @@ constexpr int MWB = HTREE_BWD_WARPS;   // warps (= queries) per block
 
 __host__ __device__ inline size_t bwd_mma_smem_per_warp(int TK) { return sizeof(int32_t) * 3 * (size_t)TK; }
 
-template <typename T, int D, bool ROT16>
+template <typename T, int D, bool ROT16, int NR>
 __global__ void HTREE_BWD_BOUNDS bwd_mma_kernel(const __grid_constant__ AttnParams p) {
     constexpr int CR = 16, HALF = D / 2, KS = D / 16, PPT = HALF / 4, NV = PPT / 8, NOT = D / 8;
     using F = Frag<T>;
@@ -52,7 +52,7 @@ __global__ void HTREE_BWD_BOUNDS bwd_mma_kernel(const __grid_constant__ AttnPara
 
     const int64_t hbase = ((int64_t)b * p.T + t) * p.H + (int64_t)hk * G;
     const int64_t qidx = ((int64_t)b * p.T + t) * p.Hkv + hk;
-    const bool row_ok[2] = {g < G, g + 8 < G};
+    const bool row_ok[2] = {g < G, NR == 2 && g + 8 < G};   // NR = 1: at most 8 heads, rows g+8 are padding
 
     uint32_t qraw[2][2][KS], dOraw[2][2][KS];
     load_rows_half<T, D>(reinterpret_cast<const T*>(p.q) + hbase * D, g, r, row_ok, qraw);
@@ -146,15 +146,15 @@ __global__ void HTREE_BWD_BOUNDS bwd_mma_kernel(const __grid_constant__ AttnPara
             // ---- S, the rotated-query fragments and the keys rotated back into q's frame ----
             float S0[4], S1[4];
             uint32_t qa[KS][4], kr[2][2][KS];
-            score_chunk<D, true, ROT16, true>(p, lkr, Nl, b, hk, node0, delta, g, r, qraw, S0, S1, qa, kr);
+            score_chunk<D, true, ROT16, true, NR>(p, lkr, Nl, b, hk, node0, delta, g, r, qraw, S0, S1, qa, kr);
 
             // ---- P and dS (src/naive.py:379-382), zero outside the accumulated set ----
-            float P[2][4], dS[2][4];   // [row][tile0 c0, tile0 c1, tile1 c0, tile1 c1]
+            float P[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}}, dS[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
             {
                 const float s[2][4] = {{S0[0], S0[1], S1[0], S1[1]}, {S0[2], S0[3], S1[2], S1[3]}};
                 const float dp[2][4] = {{dP0[0], dP0[1], dP1[0], dP1[1]}, {dP0[2], dP0[3], dP1[2], dP1[3]}};
 #pragma unroll
-                for (int rr = 0; rr < 2; ++rr)
+                for (int rr = 0; rr < NR; ++rr)
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {
                         const bool on = cv[c] && row_ok[rr];
@@ -295,13 +295,13 @@ bool bwd_mma_supported(const AttnParams& p, int dtype) {
     return bwd_mma_smem_per_warp(p.TK) * MWB <= 200 * 1024;
 }
 
-template <typename T, int D, bool ROT16>
-static int launch_bwd_mma_t(const AttnParams& p, cudaStream_t st) {
+template <typename T, int D, bool ROT16, int NR>
+static int launch_bwd_mma_nr(const AttnParams& p, cudaStream_t st) {
     const size_t smem = bwd_mma_smem_per_warp(p.TK) * MWB;
     dim3 grid((p.T + MWB - 1) / MWB, p.B * p.Hkv);
-    cudaError_t e = cudaFuncSetAttribute(bwd_mma_kernel<T, D, ROT16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(bwd_mma_kernel<T, D, ROT16, NR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    bwd_mma_kernel<T, D, ROT16><<<grid, MWB * 32, smem, st>>>(p);
+    bwd_mma_kernel<T, D, ROT16, NR><<<grid, MWB * 32, smem, st>>>(p);
     note_launch();
     e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
@@ -314,6 +314,11 @@ static int launch_bwd_mma_t(const AttnParams& p, cudaStream_t st) {
         if (e != cudaSuccess) return (int)e;
     }
     return 0;
+}
+
+template <typename T, int D, bool ROT16>
+static int launch_bwd_mma_t(const AttnParams& p, cudaStream_t st) {
+    return p.G <= 8 ? launch_bwd_mma_nr<T, D, ROT16, 1>(p, st) : launch_bwd_mma_nr<T, D, ROT16, 2>(p, st);
 }
 
 int launch_bwd_mma(const AttnParams& p, int dtype, cudaStream_t st) {

@@ -61,7 +61,8 @@ __host__ __device__ inline size_t mma_smem_per_warp(int TK, int CR) {
 #ifndef HTREE_SEL_MIN_BLOCKS
 #define HTREE_SEL_MIN_BLOCKS 4   // the selection kernel carries no accumulators: 128 registers, 16 warps per SM
 #endif
-template <typename T, int D, bool ROT16, int MODE>
+// NR = 1: groups of at most 8 heads (rows g+8 of every fragment are padding and their ALU work is skipped).
+template <typename T, int D, bool ROT16, int MODE, int NR>
 __global__ void __launch_bounds__(MW * 32, MODE == 1 ? HTREE_SEL_MIN_BLOCKS : HTREE_FWD_MIN_BLOCKS) fwd_mma_kernel(const __grid_constant__ AttnParams p) {
     constexpr int CR = 16;
     constexpr int HALF = D / 2;
@@ -92,7 +93,7 @@ __global__ void __launch_bounds__(MW * 32, MODE == 1 ? HTREE_SEL_MIN_BLOCKS : HT
     const bool select_only = kSelectKernel || (MODE == 0 && (p.flags & HTREE_FWD_SELECT_ONLY) != 0);
     const int64_t hbase = ((int64_t)b * p.Tq + tl) * p.H + (int64_t)hk * G;
     const int64_t qidx = ((int64_t)b * p.Tq + tl) * p.Hkv + hk;
-    const bool row_ok[2] = {g < G, g + 8 < G};
+    const bool row_ok[2] = {g < G, NR == 2 && g + 8 < G};
 
     // raw queries of rows g and g+8: pairs [PPT*r, PPT*(r+1)) of the low and of the high half
     uint32_t qraw[2][2][KS];
@@ -135,8 +136,8 @@ __global__ void __launch_bounds__(MW * 32, MODE == 1 ? HTREE_SEL_MIN_BLOCKS : HT
             int node0 = par[a] * CR;
             if (node0 < 0 || node0 >= Nl) { if (p.status) atomicOr(p.status, 4); node0 = 0; }
             uint32_t unused[1][4];
-            if (rot16 && !select) score_chunk<D, false, true>(p, lkr, Nl, b, hk, node0, rp - CR * a, g, r, qraw, S0, S1, unused);
-            else score_chunk<D, false, false>(p, lkr, Nl, b, hk, node0, rp - CR * a, g, r, qraw, S0, S1, unused);
+            if (rot16 && !select) score_chunk<D, false, true, false, NR>(p, lkr, Nl, b, hk, node0, rp - CR * a, g, r, qraw, S0, S1, unused);
+            else score_chunk<D, false, false, false, NR>(p, lkr, Nl, b, hk, node0, rp - CR * a, g, r, qraw, S0, S1, unused);
         };
 
         // online-softmax accumulation of the columns in `mask` (bit c = child c of the parent at slot a)
@@ -162,9 +163,9 @@ __global__ void __launch_bounds__(MW * 32, MODE == 1 ? HTREE_SEL_MIN_BLOCKS : HT
             s[0][2] = (cv[2] && row_ok[0]) ? S1[0] : NINF; s[0][3] = (cv[3] && row_ok[0]) ? S1[1] : NINF;
             s[1][0] = (cv[0] && row_ok[1]) ? S0[2] : NINF; s[1][1] = (cv[1] && row_ok[1]) ? S0[3] : NINF;
             s[1][2] = (cv[2] && row_ok[1]) ? S1[2] : NINF; s[1][3] = (cv[3] && row_ok[1]) ? S1[3] : NINF;
-            float mr[2];
+            float mr[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-            for (int rr = 0; rr < 2; ++rr) {
+            for (int rr = 0; rr < NR; ++rr) {
                 float m = fmaxf(fmaxf(s[rr][0], s[rr][1]), fmaxf(s[rr][2], s[rr][3]));
                 m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
                 m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
@@ -176,11 +177,14 @@ __global__ void __launch_bounds__(MW * 32, MODE == 1 ? HTREE_SEL_MIN_BLOCKS : HT
                 m_run[0] = n0; m_run[1] = n1;
                 s_run[0] *= a0; s_run[1] *= a1;
 #pragma unroll
-                for (int i = 0; i < NOT; ++i) { O[i][0] *= a0; O[i][1] *= a0; O[i][2] *= a1; O[i][3] *= a1; }
+                for (int i = 0; i < NOT; ++i) {
+                    O[i][0] *= a0; O[i][1] *= a0;
+                    if (NR == 2) { O[i][2] *= a1; O[i][3] *= a1; }
+                }
             }
-            float pr[2][4];
+            float pr[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
-            for (int rr = 0; rr < 2; ++rr)
+            for (int rr = 0; rr < NR; ++rr)
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
                     pr[rr][c] = __expf(s[rr][c] - m_run[rr]);
@@ -250,7 +254,7 @@ __global__ void __launch_bounds__(MW * 32, MODE == 1 ? HTREE_SEL_MIN_BLOCKS : HT
                     float e[4];
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {
-                        e[c] = __expf(s[0][c] - cm) + __expf(s[1][c] - cm);
+                        e[c] = __expf(s[0][c] - cm) + (NR == 2 ? __expf(s[1][c] - cm) : 0.f);
                         e[c] += __shfl_xor_sync(0xffffffffu, e[c], 4);
                         e[c] += __shfl_xor_sync(0xffffffffu, e[c], 8);
                         e[c] += __shfl_xor_sync(0xffffffffu, e[c], 16);
@@ -355,16 +359,21 @@ __global__ void __launch_bounds__(MW * 32, MODE == 1 ? HTREE_SEL_MIN_BLOCKS : HT
     }
 }
 
-template <typename T, int D, bool ROT16, int MODE>
-static int launch_mma_mode(const AttnParams& p, cudaStream_t st) {
+template <typename T, int D, bool ROT16, int MODE, int NR>
+static int launch_mma_mode_nr(const AttnParams& p, cudaStream_t st) {
     const size_t smem = mma_smem_per_warp(p.TK, 16) * MW;
     if (smem > 200 * 1024) return HTREE_E_UNSUPPORTED;
-    cudaError_t e = cudaFuncSetAttribute(fwd_mma_kernel<T, D, ROT16, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(fwd_mma_kernel<T, D, ROT16, MODE, NR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     dim3 grid((p.Tq + MW - 1) / MW, p.B * p.Hkv);
-    fwd_mma_kernel<T, D, ROT16, MODE><<<grid, MW * 32, smem, st>>>(p);
+    fwd_mma_kernel<T, D, ROT16, MODE, NR><<<grid, MW * 32, smem, st>>>(p);
     note_launch();
     return (int)cudaGetLastError();
+}
+
+template <typename T, int D, bool ROT16, int MODE>
+static int launch_mma_mode(const AttnParams& p, cudaStream_t st) {
+    return p.G <= 8 ? launch_mma_mode_nr<T, D, ROT16, MODE, 1>(p, st) : launch_mma_mode_nr<T, D, ROT16, MODE, 2>(p, st);
 }
 
 template <typename T, int D, bool ROT16>

@@ -83,7 +83,8 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
 //   pre-scaled half tables (4 instead of 14 instructions per pair of pairs, about twice the rounding noise).
 //   With KEEP_K (backward) kr receives the keys rotated back into the query's frame, scale * R(-delta) K', in the same
 //   fragment order ([tile][half][k-step]); transposed with movmatrix they are the B fragments of dq += dS K~.
-template <int D, bool KEEP_A, bool ROT16, bool KEEP_K = false>
+//   NR = 1 when the group has at most 8 heads: rows g+8 are padding, their rotation is skipped and their A rows are zero.
+template <int D, bool KEEP_A, bool ROT16, bool KEEP_K = false, int NR = 2>
 __device__ __forceinline__ void score_chunk(const AttnParams& p, const __half* lkr, int Nl, int b, int hk, int node0, int delta,
                                             int g, int r, const uint32_t (&qraw)[2][2][D / 16], float (&S0)[4], float (&S1)[4],
                                             uint32_t (&qa)[KEEP_A ? D / 16 : 1][4], uint32_t (*kr)[2][D / 16] = nullptr) {
@@ -126,8 +127,9 @@ __device__ __forceinline__ void score_chunk(const AttnParams& p, const __half* l
         for (int ks = 0; ks < KS; ++ks) {
             uint32_t a[4];
             const __half2 c2 = *reinterpret_cast<const __half2*>(&ch[ks]), s2 = *reinterpret_cast<const __half2*>(&sh[ks]);
+            a[1] = 0u; a[3] = 0u;
 #pragma unroll
-            for (int rr = 0; rr < 2; ++rr) {
+            for (int rr = 0; rr < NR; ++rr) {
                 const __half2 lo = *reinterpret_cast<const __half2*>(&qraw[rr][0][ks]);
                 const __half2 hi = *reinterpret_cast<const __half2*>(&qraw[rr][1][ks]);
                 const __half2 x = __hfma2(lo, c2, __hneg2(__hmul2(hi, s2)));     // lo*cos - hi*sin
@@ -158,8 +160,9 @@ __device__ __forceinline__ void score_chunk(const AttnParams& p, const __half* l
         for (int u = 0; u < 2; ++u) {
             const int ks = ks2 + u;
             uint32_t a[4];
+            a[1] = 0u; a[3] = 0u;
 #pragma unroll
-            for (int rr = 0; rr < 2; ++rr) {
+            for (int rr = 0; rr < NR; ++rr) {
                 const float2 lo = FS::unpack(qraw[rr][0][ks]), hi = FS::unpack(qraw[rr][1][ks]);
                 const float c0 = cs[2 * u], c1 = cs[2 * u + 1], s0 = sn[2 * u], s1 = sn[2 * u + 1];
                 a[rr] = FS::pack(lo.x * c0 - hi.x * s0, lo.y * c1 - hi.y * s1);         // rotated low half
