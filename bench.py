@@ -157,7 +157,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg3", choices=sorted(configs.CONFIGS))
     ap.add_argument("--t-scale", type=int, default=1, help="divide T by this (debug only; reported in config)")
-    ap.add_argument("--shard", default="auto", choices=["auto", "units", "sequence"],
+    ap.add_argument("--shard", default="auto", choices=["auto", "units", "sequence", "sequence-balanced"],
                     help="units: (batch, kv head) round-robin; sequence: query positions split, pooled levels all-gathered "
                          "(forward-only workloads); auto = sequence for cfg4, units otherwise")
     ap.add_argument("--no-e2e", action="store_true")
@@ -208,7 +208,8 @@ def main():
     B, T, H, Hkv, D, CR, TK, MTN = c["B"], c["T"], c["H"], c["H_kv"], c["D"], c["CR"], c["TK"], c["MTN"]
     G = H // Hkv
     bwd = "bwd" in c["mode"]
-    seq_mode = (args.shard == "sequence" or (args.shard == "auto" and args.workload == "cfg4")) and not bwd
+    seq_mode = (args.shard in ("sequence", "sequence-balanced") or (args.shard == "auto" and args.workload == "cfg4")) and not bwd
+    seq_ranges = None
     if seq_mode:
         cfg_desc["sharding"] = ("query positions split evenly over ranks; k, v replicated; one all_gather_into_tensor per "
                                 "pooled tree level (NCCL)")
@@ -223,7 +224,12 @@ def main():
         # one long sequence per batch element: every rank holds the same k, v and its own slice of the queries
         k = randn(B, T, Hkv, D); v = randn(B, T, Hkv, D)
         n_lv = len(configs.level_sizes(T, CR, MTN))
-        t0, t1 = hdist.query_range(T, world, rank, CR, n_lv) if world > 1 else (0, T)
+        if args.shard == "sequence-balanced" and world > 1:
+            seq_ranges = hdist.balanced_query_ranges(T, world, CR, TK, MTN)
+            t0, t1 = seq_ranges[rank]
+            cfg_desc["sharding"] = cfg_desc["sharding"].replace("split evenly", "split by equal work (cost model)")
+        else:
+            t0, t1 = hdist.query_range(T, world, rank, CR, n_lv) if world > 1 else (0, T)
         gen.manual_seed(1042 + rank)
         q = randn(B, t1 - t0, H, D)
         dO = None
@@ -244,7 +250,7 @@ def main():
                 timers[2].record()
             return out, dq, dk, dv
         if seq_mode:
-            out = hdist.htree_forward_sequence_parallel(q_, k_, v_, CR, MTN, TK) if world > 1 else ht.htree_forward(q_, k_, v_, CR, MTN, TK)
+            out = hdist.htree_forward_sequence_parallel(q_, k_, v_, CR, MTN, TK, ranges=seq_ranges) if world > 1 else ht.htree_forward(q_, k_, v_, CR, MTN, TK)
         else:
             out = ht.htree_forward(q_, k_, v_, CR, MTN, TK)
         if timers is not None:

@@ -74,12 +74,42 @@ def query_range(T: int, world_size: int, rank: int, compression_rate: int, n_lev
     return rank * span, (rank + 1) * span
 
 
+def balanced_query_ranges(T: int, world_size: int, compression_rate: int, top_k: int, max_top_nodes: int):
+    """Contiguous query ranges [t0, t1) per rank with (nearly) equal WORK instead of equal length.
+
+    The cost of a query grows with its position until every level is saturated (later positions score more
+    candidates at the upper levels), so an even split leaves the last ranks with up to ~15 % more work.  Boundaries
+    stay multiples of compression_rate^(levels-1), so no pooled node straddles two ranks."""
+    import numpy as np
+    sizes = configs.level_sizes(T, compression_rate, max_top_nodes)
+    L = len(sizes)
+    grain = compression_rate ** (L - 1)
+    if T % grain or T // grain < world_size:
+        raise ValueError(f"T={T} must be a multiple of compression_rate^(levels-1)={grain} with at least one block per rank")
+    nc, acc = configs.attend_counts(T, compression_rate, top_k, L)
+    scored = np.where(nc[1:] > top_k, nc[1:], 0).sum(0) if L > 1 else 0      # candidates of the selection passes
+    cost = (scored + 2 * acc.sum(0)).astype(np.float64)                     # accumulation ~2x a selection-only score
+    block_cost = cost.reshape(-1, grain).sum(1)
+    csum = np.concatenate([[0.0], np.cumsum(block_cost)])
+    n_blocks = block_cost.size
+    cuts = [0]
+    for r in range(1, world_size):
+        target = csum[-1] * r / world_size
+        j = int(np.searchsorted(csum, target))
+        j = max(cuts[-1] + 1, min(j, n_blocks - (world_size - r)))
+        cuts.append(j)
+    cuts.append(n_blocks)
+    return [(cuts[r] * grain, cuts[r + 1] * grain) for r in range(world_size)]
+
+
 def build_tree_sequence_parallel(k: torch.Tensor, v: torch.Tensor, compression_rate: int, max_top_nodes: int,
-                                 group=None, _build=None):
+                                 group=None, _build=None, ranges=None):
     """Tree build for mode B: pool the local leaf range, all-gather every pooled level.
 
     k, v are the full (replicated) leaves [B,T,H_kv,*].  Returns full-length (layers_k, layers_v) in local memory.
-    `_build(k, v, compression_rate, max_top_nodes)` replaces the CUDA tree build in host-only tests."""
+    `_build(k, v, compression_rate, max_top_nodes)` replaces the CUDA tree build in host-only tests.
+    `ranges`: per-rank leaf ranges [(t0, t1), ...] (multiples of compression_rate^(levels-1)); default = even split.
+    With uneven ranges every rank pads its pooled slices to the longest one for the all-gather."""
     import torch.distributed as dist
     if _build is None:
         from .ops import build_tree as _build
@@ -92,28 +122,37 @@ def build_tree_sequence_parallel(k: torch.Tensor, v: torch.Tensor, compression_r
     L = len(sizes)
     if world == 1 or L == 1:
         return build_tree(k, v, compression_rate, max_top_nodes)
-    t0, t1 = query_range(T, world, rank, compression_rate, L)
+    if ranges is None:
+        ranges = [query_range(T, world, r, compression_rate, L) for r in range(world)]
+    t0, t1 = ranges[rank]
+    grain = compression_rate ** (L - 1)
+    assert all(a % grain == 0 and b % grain == 0 and b > a for a, b in ranges) and ranges[0][0] == 0 and ranges[-1][1] == T
     # pool the local slice to the same depth: its top level is this rank's share of the global top level
-    lk, lv = build_tree(k[:, t0:t1].contiguous(), v[:, t0:t1].contiguous(), compression_rate, sizes[-1] // world)
+    lk, lv = build_tree(k[:, t0:t1].contiguous(), v[:, t0:t1].contiguous(), compression_rate, (t1 - t0) // grain)
     assert len(lk) == L
     layers_k, layers_v = [k], [v]
     for l in range(1, L):
+        step = compression_rate ** l
+        lens = [(b - a) // step for a, b in ranges]
+        n_max = max(lens)
         for src, dst in ((lk[l], layers_k), (lv[l], layers_v)):
             n_loc = src.shape[1]
-            assert n_loc * world == sizes[l]
+            assert n_loc == lens[rank] and sum(lens) == sizes[l]
+            if n_loc < n_max:
+                pad = torch.zeros((B, n_max - n_loc) + tuple(src.shape[2:]), dtype=src.dtype, device=src.device)
+                src = torch.cat([src, pad], dim=1)
             gathered = torch.empty((world * B,) + tuple(src.shape[1:]), dtype=src.dtype, device=src.device)
             dist.all_gather_into_tensor(gathered, src.contiguous(), group=group)   # rank-major along dim 0
-            # [world, B, n_loc, H_kv, D] -> [B, world*n_loc, H_kv, D]
-            gathered = gathered.view(world, B, n_loc, H_kv, src.shape[-1])
-            dst.append(gathered.permute(1, 0, 2, 3, 4).reshape(B, sizes[l], H_kv, src.shape[-1]).contiguous())
+            gathered = gathered.view(world, B, n_max, H_kv, src.shape[-1])
+            dst.append(torch.cat([gathered[r, :, :lens[r]] for r in range(world)], dim=1).contiguous())
     return layers_k, layers_v
 
 
 def htree_forward_sequence_parallel(q_local: torch.Tensor, k: torch.Tensor, v: torch.Tensor, compression_rate: int = 16,
                                     max_top_nodes: int = 8192, top_k_per_layer: int = 512, scale: Optional[float] = None,
-                                    rope_base: float = 10000.0, group=None) -> torch.Tensor:
-    """Mode B forward: q_local holds this rank's query positions [B, T/world, H, K]; k, v are the full sequence.
-    Returns out_local [B, T/world, H, V]."""
+                                    rope_base: float = 10000.0, group=None, ranges=None) -> torch.Tensor:
+    """Mode B forward: q_local holds this rank's query positions [B, t1-t0, H, K]; k, v are the full sequence.
+    `ranges` (e.g. from balanced_query_ranges) overrides the even split.  Returns out_local [B, t1-t0, H, V]."""
     import torch.distributed as dist
     from .ops import htree_forward
 
@@ -121,10 +160,13 @@ def htree_forward_sequence_parallel(q_local: torch.Tensor, k: torch.Tensor, v: t
     rank = dist.get_rank(group)
     T = k.shape[1]
     L = len(configs.level_sizes(T, compression_rate, max_top_nodes))
-    t0, t1 = query_range(T, world, rank, compression_rate, L) if world > 1 else (0, T)
+    if ranges is not None:
+        t0, t1 = ranges[rank]
+    else:
+        t0, t1 = query_range(T, world, rank, compression_rate, L) if world > 1 else (0, T)
     assert q_local.shape[1] == t1 - t0
     from .ops import rotate_keys
-    layers_k, layers_v = build_tree_sequence_parallel(k, v, compression_rate, max_top_nodes, group)
+    layers_k, layers_v = build_tree_sequence_parallel(k, v, compression_rate, max_top_nodes, group, ranges=ranges)
     layers_kr = rotate_keys(layers_k, compression_rate, max_top_nodes, rope_base)   # local work on the gathered levels
     return htree_forward(q_local, k, v, compression_rate, max_top_nodes, top_k_per_layer, scale, rope_base,
                          _q_offset=t0, _layers=(layers_k, layers_v, layers_kr))

@@ -42,6 +42,20 @@ def test_query_range_grain():
         hdist.query_range(1000, 3, 0, 16, 2)
 
 
+def test_balanced_ranges_cover_the_sequence_and_even_out_the_cost():
+    import numpy as np
+    T, CR, TK, MTN = 524288, 16, 64, 512
+    for world in (2, 4, 8):
+        ranges = hdist.balanced_query_ranges(T, world, CR, TK, MTN)
+        assert ranges[0][0] == 0 and ranges[-1][1] == T
+        assert all(a[1] == b[0] for a, b in zip(ranges, ranges[1:])) and all(a % 4096 == 0 for a, _ in ranges)
+        nc, acc = configs.attend_counts(T, CR, TK, 4)
+        cost = np.where(nc[1:] > TK, nc[1:], 0).sum(0) + 2 * acc.sum(0)
+        per_rank = np.array([cost[a:b].sum() for a, b in ranges], dtype=np.float64)
+        even = np.array([cost[r * T // world:(r + 1) * T // world].sum() for r in range(world)], dtype=np.float64)
+        assert per_rank.max() / per_rank.mean() < 1.05 < even.max() / even.mean()   # block granularity 4096 tokens
+
+
 def _torch_build(k, v, cr, mtn):
     lk, lv = [k], [v]
     while lk[-1].shape[1] > mtn:
@@ -61,6 +75,9 @@ def _worker(rank, world, port, q):
         lk, lv = hdist.build_tree_sequence_parallel(k, v, 4, 10, _build=_torch_build)     # 256 -> 64 -> 16 -> 4
         rk, rv = _torch_build(k, v, 4, 10)
         ok = len(lk) == len(rk) == 4 and all(torch.allclose(a, b, atol=1e-6) for a, b in zip(lk + lv, rk + rv))
+        # uneven (work-balanced) ranges: slices are padded for the all-gather and stitched back
+        lk2, lv2 = hdist.build_tree_sequence_parallel(k, v, 4, 10, _build=_torch_build, ranges=[(0, 192), (192, 256)])
+        ok = ok and all(torch.allclose(a, b, atol=1e-6) for a, b in zip(lk2 + lv2, rk + rv))
         q.put((rank, bool(ok)))
     finally:
         tdist.destroy_process_group()

@@ -169,8 +169,13 @@ def _seq_worker(rank, world, port, ret):
         t0, t1 = hdist.query_range(T, world, rank, CR, 4)
         out_loc = hdist.htree_forward_sequence_parallel(qd[:, t0:t1].contiguous(), kd, vd, CR, MTN, TK)
         full = ht.htree_forward(qd, kd, vd, CR, MTN, TK)
+        ok = bool(torch.equal(out_loc, full[:, t0:t1]))
+        ranges = hdist.balanced_query_ranges(T, world, CR, TK, MTN)          # uneven, work-balanced split
+        a, b = ranges[rank]
+        out_bal = hdist.htree_forward_sequence_parallel(qd[:, a:b].contiguous(), kd, vd, CR, MTN, TK, ranges=ranges)
+        ok = ok and ranges[0][1] != T // 2 and bool(torch.equal(out_bal, full[:, a:b]))
         torch.cuda.synchronize()
-        ret.put((rank, bool(torch.equal(out_loc, full[:, t0:t1]))))
+        ret.put((rank, ok))
     finally:
         tdist.destroy_process_group()
 
