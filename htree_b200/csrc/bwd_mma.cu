@@ -2,8 +2,8 @@
 // all tree levels in one launch, operands gathered global/L2 -> registers -> mma.sync.
 //
 // Replaces htree_bwd_preprocess_delta_kernel, htree_bwd_dq_bottom/upper_kernel, htree_bwd_build_parent_mask_kernel and
-// htree_bwd_dkv_bottom/upper_kernel (src/backward.py:45-780) for bf16/fp16, K == V == 128, group <= 16,
-// compression_rate 16.  Arithmetic follows src/naive.py:376-386 with the forward's decomposition
+// htree_bwd_dkv_bottom/upper_kernel (src/backward.py:45-780) for bf16/fp16, K == V in {64, 128}, group <= 16,
+// compression_rate 16 or 8.  Arithmetic follows src/naive.py:376-386 with the forward's decomposition
 // S = (scale R(p-16a) q)^T K',  K' = R(node % 16) K  (see fwd_mma.cu).  For every accumulated chunk (the 16 children
 // of one parent, minus the children the next level kept):
 //   S   = q^_a K'^T                                    (score product, as in the forward)
@@ -33,9 +33,10 @@ constexpr int MWB = HTREE_BWD_WARPS;   // warps (= queries) per block
 
 __host__ __device__ inline size_t bwd_mma_smem_per_warp(int TK) { return sizeof(int32_t) * 3 * (size_t)TK; }
 
-template <typename T, int D, bool ROT16, int NR>
+template <typename T, int D, bool ROT16, int NR, int CR>
 __global__ void HTREE_BWD_BOUNDS bwd_mma_kernel(const __grid_constant__ AttnParams p) {
-    constexpr int CR = 16, HALF = D / 2, KS = D / 16, PPT = HALF / 4, NV = PPT / 8, NOT = D / 8;
+    constexpr bool T1 = CR > 8;   // CR = children per parent: 16, or 8 (then tile 1 stays empty)
+    constexpr int HALF = D / 2, KS = D / 16, PPT = HALF / 4, NV = PPT / 8, NOT = D / 8;
     using F = Frag<T>;
     using FS = Frag<__half>;
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -115,7 +116,7 @@ __global__ void HTREE_BWD_BOUNDS bwd_mma_kernel(const __grid_constant__ AttnPara
         const int rp = (np - 1) * CR + rc;
 
         for (int a = 0; a < np; ++a) {
-            const uint32_t valid = a == np - 1 ? ((2u << rc) - 1u) : 0xffffu;
+            const uint32_t valid = a == np - 1 ? ((2u << rc) - 1u) : ((1u << CR) - 1u);
             const uint32_t mask = ~keptw[a] & valid;
             if (mask == 0) continue;
             int node0 = par[a] * CR;
@@ -134,19 +135,19 @@ __global__ void HTREE_BWD_BOUNDS bwd_mma_kernel(const __grid_constant__ AttnPara
 #pragma unroll
                 for (int hf = 0; hf < 2; ++hf) {
                     ldg_vec<NV>(v0 + hf * HALF, n0 < Nl, vb[0][hf]);
-                    ldg_vec<NV>(v1 + hf * HALF, n1 < Nl, vb[1][hf]);
+                    if (T1) ldg_vec<NV>(v1 + hf * HALF, n1 < Nl, vb[1][hf]);
                 }
 #pragma unroll
                 for (int ks = 0; ks < KS; ++ks) {
                     F::mma(dP0, dOraw[0][0][ks], dOraw[1][0][ks], dOraw[0][1][ks], dOraw[1][1][ks], vb[0][0][ks], vb[0][1][ks]);
-                    F::mma(dP1, dOraw[0][0][ks], dOraw[1][0][ks], dOraw[0][1][ks], dOraw[1][1][ks], vb[1][0][ks], vb[1][1][ks]);
+                    if (T1) F::mma(dP1, dOraw[0][0][ks], dOraw[1][0][ks], dOraw[0][1][ks], dOraw[1][1][ks], vb[1][0][ks], vb[1][1][ks]);
                 }
             }
 
             // ---- S, the rotated-query fragments and the keys rotated back into q's frame ----
             float S0[4], S1[4];
             uint32_t qa[KS][4], kr[2][2][KS];
-            score_chunk<D, true, ROT16, true, NR>(p, lkr, Nl, b, hk, node0, delta, g, r, qraw, S0, S1, qa, kr);
+            score_chunk<D, true, ROT16, true, NR, CR>(p, lkr, Nl, b, hk, node0, delta, g, r, qraw, S0, S1, qa, kr);
 
             // ---- P and dS (src/naive.py:379-382), zero outside the accumulated set ----
             float P[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}}, dS[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
@@ -290,18 +291,18 @@ __global__ void __launch_bounds__(256) finalize_grads_kernel(float* dk, float* d
 
 bool bwd_mma_supported(const AttnParams& p, int dtype) {
     if (dtype != HTREE_BF16 && dtype != HTREE_F16) return false;
-    if (p.K != p.V || (p.K != 64 && p.K != 128) || p.G > 16 || p.CR != 16) return false;
+    if (p.K != p.V || (p.K != 64 && p.K != 128) || p.G > 16 || (p.CR != 16 && p.CR != 8)) return false;
     for (int l = 0; l < p.L; ++l) if (!p.lkr[l]) return false;
     return bwd_mma_smem_per_warp(p.TK) * MWB <= 200 * 1024;
 }
 
-template <typename T, int D, bool ROT16, int NR>
-static int launch_bwd_mma_nr(const AttnParams& p, cudaStream_t st) {
+template <typename T, int D, bool ROT16, int NR, int CR>
+static int launch_bwd_mma_cr(const AttnParams& p, cudaStream_t st) {
     const size_t smem = bwd_mma_smem_per_warp(p.TK) * MWB;
     dim3 grid((p.T + MWB - 1) / MWB, p.B * p.Hkv);
-    cudaError_t e = cudaFuncSetAttribute(bwd_mma_kernel<T, D, ROT16, NR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(bwd_mma_kernel<T, D, ROT16, NR, CR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    bwd_mma_kernel<T, D, ROT16, NR><<<grid, MWB * 32, smem, st>>>(p);
+    bwd_mma_kernel<T, D, ROT16, NR, CR><<<grid, MWB * 32, smem, st>>>(p);
     note_launch();
     e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
@@ -314,6 +315,11 @@ static int launch_bwd_mma_nr(const AttnParams& p, cudaStream_t st) {
         if (e != cudaSuccess) return (int)e;
     }
     return 0;
+}
+
+template <typename T, int D, bool ROT16, int NR>
+static int launch_bwd_mma_nr(const AttnParams& p, cudaStream_t st) {
+    return p.CR == 8 ? launch_bwd_mma_cr<T, D, ROT16, NR, 8>(p, st) : launch_bwd_mma_cr<T, D, ROT16, NR, 16>(p, st);
 }
 
 template <typename T, int D, bool ROT16>

@@ -3,7 +3,8 @@
 //
 // Replaces the same reference kernels as the generic forward (htree_select_accumulate_gqa_kernel,
 // htree_bottom_accumulate_gqa_kernel, htree_merge_to_global_kernel, htree_final_normalize_kernel;
-// src/parallel.py:248-867) for bf16/fp16, head_dim 64 or 128, K == V, group size <= 16, compression_rate 16.
+// src/parallel.py:248-867) for bf16/fp16, head_dim 64 or 128, K == V, group size <= 16, compression_rate 16 or 8
+// (with 8 children per parent the second score tile stays empty).
 //
 // Design notes
 //  * M = the GQA group (<= 16 query heads) maps exactly onto the M = 16 rows of mma.sync.m16n8k16; candidates are the
@@ -62,9 +63,9 @@ __host__ __device__ inline size_t mma_smem_per_warp(int TK, int CR) {
 #define HTREE_SEL_MIN_BLOCKS 4   // the selection kernel carries no accumulators: 128 registers, 16 warps per SM
 #endif
 // NR = 1: groups of at most 8 heads (rows g+8 of every fragment are padding and their ALU work is skipped).
-template <typename T, int D, bool ROT16, int MODE, int NR>
+template <typename T, int D, bool ROT16, int MODE, int NR, int CR>
 __global__ void __launch_bounds__(MW * 32, MODE == 1 ? HTREE_SEL_MIN_BLOCKS : HTREE_FWD_MIN_BLOCKS) fwd_mma_kernel(const __grid_constant__ AttnParams p) {
-    constexpr int CR = 16;
+    constexpr uint32_t kAllChildren = (1u << CR) - 1u;   // CR = children per parent: 16, or 8 (then tile 1 stays empty)
     constexpr int HALF = D / 2;
     constexpr int KS = D / 16;        // k-steps of the score product
     constexpr int PPT = HALF / 4;     // rotation pairs owned by one thread of a quad
@@ -136,8 +137,8 @@ __global__ void __launch_bounds__(MW * 32, MODE == 1 ? HTREE_SEL_MIN_BLOCKS : HT
             int node0 = par[a] * CR;
             if (node0 < 0 || node0 >= Nl) { if (p.status) atomicOr(p.status, 4); node0 = 0; }
             uint32_t unused[1][4];
-            if (rot16 && !select) score_chunk<D, false, true, false, NR>(p, lkr, Nl, b, hk, node0, rp - CR * a, g, r, qraw, S0, S1, unused);
-            else score_chunk<D, false, false, false, NR>(p, lkr, Nl, b, hk, node0, rp - CR * a, g, r, qraw, S0, S1, unused);
+            if (rot16 && !select) score_chunk<D, false, true, false, NR, CR>(p, lkr, Nl, b, hk, node0, rp - CR * a, g, r, qraw, S0, S1, unused);
+            else score_chunk<D, false, false, false, NR, CR>(p, lkr, Nl, b, hk, node0, rp - CR * a, g, r, qraw, S0, S1, unused);
         };
 
         // online-softmax accumulation of the columns in `mask` (bit c = child c of the parent at slot a)
@@ -222,8 +223,8 @@ __global__ void __launch_bounds__(MW * 32, MODE == 1 ? HTREE_SEL_MIN_BLOCKS : HT
                 }
                 __syncwarp();
                 for (int a = 0; a < np; ++a) {
-                    const uint32_t kept = (selw[a >> 1] >> (16 * (a & 1))) & 0xffffu;
-                    const uint32_t valid = a == np - 1 ? ((2u << rc) - 1u) : 0xffffu;
+                    const uint32_t kept = (selw[(a * CR) >> 5] >> ((a * CR) & 31)) & kAllChildren;
+                    const uint32_t valid = a == np - 1 ? ((2u << rc) - 1u) : kAllChildren;
                     const uint32_t mask = ~kept & valid;
                     if (mask == 0) continue;
                     float S0[4], S1[4];
@@ -241,7 +242,7 @@ __global__ void __launch_bounds__(MW * 32, MODE == 1 ? HTREE_SEL_MIN_BLOCKS : HT
                     float S0[4], S1[4];
                     score(a, S0, S1, true);
                     const int jb = a * CR;
-                    const bool cv[4] = {jb + 2 * r < nc, jb + 2 * r + 1 < nc, jb + 8 + 2 * r < nc, jb + 9 + 2 * r < nc};
+                    const bool cv[4] = {jb + 2 * r < nc, jb + 2 * r + 1 < nc, CR > 8 && jb + 8 + 2 * r < nc, CR > 8 && jb + 9 + 2 * r < nc};
                     const float NINF = -INFINITY;
                     float s[2][4];
                     s[0][0] = (cv[0] && row_ok[0]) ? S0[0] : NINF; s[0][1] = (cv[1] && row_ok[0]) ? S0[1] : NINF;
@@ -261,7 +262,7 @@ __global__ void __launch_bounds__(MW * 32, MODE == 1 ? HTREE_SEL_MIN_BLOCKS : HT
                     }
                     if (g == 0) {
                         imp[jb + 2 * r] = e[0]; imp[jb + 2 * r + 1] = e[1];
-                        imp[jb + 8 + 2 * r] = e[2]; imp[jb + 9 + 2 * r] = e[3];
+                        if (CR > 8) { imp[jb + 8 + 2 * r] = e[2]; imp[jb + 9 + 2 * r] = e[3]; }
                     }
                     if (lane == 0) cmax[a] = cm;
                 }
@@ -308,8 +309,8 @@ __global__ void __launch_bounds__(MW * 32, MODE == 1 ? HTREE_SEL_MIN_BLOCKS : HT
                 // ---- pass 2: accumulate what was not kept ----
                 if (!select_only) {
                     for (int a = 0; a < np; ++a) {
-                        const uint32_t kept = (selw[a >> 1] >> (16 * (a & 1))) & 0xffffu;
-                        const uint32_t valid = a == np - 1 ? ((2u << rc) - 1u) : 0xffffu;
+                        const uint32_t kept = (selw[(a * CR) >> 5] >> ((a * CR) & 31)) & kAllChildren;
+                        const uint32_t valid = a == np - 1 ? ((2u << rc) - 1u) : kAllChildren;
                         const uint32_t mask = ~kept & valid;
                         if (mask == 0) continue;
                         float S0[4], S1[4];
@@ -322,7 +323,7 @@ __global__ void __launch_bounds__(MW * 32, MODE == 1 ? HTREE_SEL_MIN_BLOCKS : HT
             int32_t* tmp = par; par = nxt; nxt = tmp;
         } else {
             for (int a = 0; a < np; ++a) {
-                const uint32_t valid = a == np - 1 ? ((2u << rc) - 1u) : 0xffffu;
+                const uint32_t valid = a == np - 1 ? ((2u << rc) - 1u) : kAllChildren;
                 float S0[4], S1[4];
                 score(a, S0, S1, false);
                 accumulate_chunk(a, S0, S1, valid);
@@ -359,16 +360,21 @@ __global__ void __launch_bounds__(MW * 32, MODE == 1 ? HTREE_SEL_MIN_BLOCKS : HT
     }
 }
 
-template <typename T, int D, bool ROT16, int MODE, int NR>
-static int launch_mma_mode_nr(const AttnParams& p, cudaStream_t st) {
-    const size_t smem = mma_smem_per_warp(p.TK, 16) * MW;
+template <typename T, int D, bool ROT16, int MODE, int NR, int CR>
+static int launch_mma_mode_cr(const AttnParams& p, cudaStream_t st) {
+    const size_t smem = mma_smem_per_warp(p.TK, CR) * MW;
     if (smem > 200 * 1024) return HTREE_E_UNSUPPORTED;
-    cudaError_t e = cudaFuncSetAttribute(fwd_mma_kernel<T, D, ROT16, MODE, NR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(fwd_mma_kernel<T, D, ROT16, MODE, NR, CR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     dim3 grid((p.Tq + MW - 1) / MW, p.B * p.Hkv);
-    fwd_mma_kernel<T, D, ROT16, MODE, NR><<<grid, MW * 32, smem, st>>>(p);
+    fwd_mma_kernel<T, D, ROT16, MODE, NR, CR><<<grid, MW * 32, smem, st>>>(p);
     note_launch();
     return (int)cudaGetLastError();
+}
+
+template <typename T, int D, bool ROT16, int MODE, int NR>
+static int launch_mma_mode_nr(const AttnParams& p, cudaStream_t st) {
+    return p.CR == 8 ? launch_mma_mode_cr<T, D, ROT16, MODE, NR, 8>(p, st) : launch_mma_mode_cr<T, D, ROT16, MODE, NR, 16>(p, st);
 }
 
 template <typename T, int D, bool ROT16, int MODE>
@@ -394,9 +400,9 @@ static int launch_mma_td(const AttnParams& p, cudaStream_t st) {
 bool fwd_mma_supported(const AttnParams& p, int dtype) {
     if (dtype != HTREE_BF16 && dtype != HTREE_F16) return false;
     if (p.K != p.V || (p.K != 64 && p.K != 128)) return false;
-    if (p.G > 16 || p.CR != 16) return false;
+    if (p.G > 16 || (p.CR != 16 && p.CR != 8)) return false;
     for (int l = 0; l < p.L; ++l) if (!p.lkr[l]) return false;
-    return mma_smem_per_warp(p.TK, 16) * MW <= 200 * 1024;
+    return mma_smem_per_warp(p.TK, p.CR) * MW <= 200 * 1024;
 }
 
 int launch_fwd_mma(const AttnParams& p, int dtype, cudaStream_t st) {

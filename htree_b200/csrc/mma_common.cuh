@@ -84,11 +84,13 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
 //   With KEEP_K (backward) kr receives the keys rotated back into the query's frame, scale * R(-delta) K', in the same
 //   fragment order ([tile][half][k-step]); transposed with movmatrix they are the B fragments of dq += dS K~.
 //   NR = 1 when the group has at most 8 heads: rows g+8 are padding, their rotation is skipped and their A rows are zero.
-template <int D, bool KEEP_A, bool ROT16, bool KEEP_K = false, int NR = 2>
+//   CR = children per parent (16 or 8).  With 8 the second tile (children 8-15) does not exist: no loads, no MMAs, S1 = 0.
+template <int D, bool KEEP_A, bool ROT16, bool KEEP_K = false, int NR = 2, int CR = 16>
 __device__ __forceinline__ void score_chunk(const AttnParams& p, const __half* lkr, int Nl, int b, int hk, int node0, int delta,
                                             int g, int r, const uint32_t (&qraw)[2][2][D / 16], float (&S0)[4], float (&S1)[4],
                                             uint32_t (&qa)[KEEP_A ? D / 16 : 1][4], uint32_t (*kr)[2][D / 16] = nullptr) {
     constexpr int HALF = D / 2, KS = D / 16, PPT = HALF / 4, NV = PPT / 8;
+    constexpr bool T1 = CR > 8;   // does tile 1 exist?
     using FS = Frag<__half>;
     const float* cp = p.cosc + (size_t)delta * HALF + PPT * r;
     const float* sp = p.sinc + (size_t)delta * HALF + PPT * r;
@@ -99,11 +101,15 @@ __device__ __forceinline__ void score_chunk(const AttnParams& p, const __half* l
 #pragma unroll
     for (int hf = 0; hf < 2; ++hf) {
         ldg_vec<NV>(k0 + hf * HALF, n0 < Nl, kb[0][hf]);
-        ldg_vec<NV>(k1 + hf * HALF, n1 < Nl, kb[1][hf]);
+        if (T1) ldg_vec<NV>(k1 + hf * HALF, n1 < Nl, kb[1][hf]);
+        else {
+#pragma unroll
+            for (int i = 0; i < KS; ++i) kb[1][hf][i] = 0u;
+        }
     }
     S0[0] = S0[1] = S0[2] = S0[3] = 0.f;
     S1[0] = S1[1] = S1[2] = S1[3] = 0.f;
-    float T0[4] = {0.f, 0.f, 0.f, 0.f}, T1[4] = {0.f, 0.f, 0.f, 0.f};
+    float T0[4] = {0.f, 0.f, 0.f, 0.f}, U1[4] = {0.f, 0.f, 0.f, 0.f};
     if (ROT16) {
         const __half* chp = p.cosh + (size_t)delta * HALF + PPT * r;
         const __half* shp = p.sinh + (size_t)delta * HALF + PPT * r;
@@ -112,7 +118,7 @@ __device__ __forceinline__ void score_chunk(const AttnParams& p, const __half* l
         ldg_vec<NV>(shp, true, sh);
         if (KEEP_K) {
 #pragma unroll
-            for (int tl = 0; tl < 2; ++tl)
+            for (int tl = 0; tl < (T1 ? 2 : 1); ++tl)
 #pragma unroll
                 for (int ks = 0; ks < KS; ++ks) {
                     const __half2 c2 = *reinterpret_cast<const __half2*>(&ch[ks]), s2 = *reinterpret_cast<const __half2*>(&sh[ks]);
@@ -140,14 +146,18 @@ __device__ __forceinline__ void score_chunk(const AttnParams& p, const __half* l
             if (KEEP_A) { qa[KEEP_A ? ks : 0][0] = a[0]; qa[KEEP_A ? ks : 0][1] = a[1]; qa[KEEP_A ? ks : 0][2] = a[2]; qa[KEEP_A ? ks : 0][3] = a[3]; }
             if (ks & 1) {   // two accumulation chains per tile: halves the dependent-MMA latency on the critical path
                 FS::mma(T0, a[0], a[1], a[2], a[3], kb[0][0][ks], kb[0][1][ks]);
-                FS::mma(T1, a[0], a[1], a[2], a[3], kb[1][0][ks], kb[1][1][ks]);
+                if (T1) FS::mma(U1, a[0], a[1], a[2], a[3], kb[1][0][ks], kb[1][1][ks]);
             } else {
                 FS::mma(S0, a[0], a[1], a[2], a[3], kb[0][0][ks], kb[0][1][ks]);
-                FS::mma(S1, a[0], a[1], a[2], a[3], kb[1][0][ks], kb[1][1][ks]);
+                if (T1) FS::mma(S1, a[0], a[1], a[2], a[3], kb[1][0][ks], kb[1][1][ks]);
             }
         }
 #pragma unroll
-        for (int i = 0; i < 4; ++i) { S0[i] += T0[i]; S1[i] += T1[i]; }
+        for (int i = 0; i < 4; ++i) { S0[i] += T0[i]; S1[i] += U1[i]; }
+        if (KEEP_K && !T1) {
+#pragma unroll
+            for (int ks = 0; ks < KS; ++ks) { kr[1][0][ks] = 0u; kr[1][1][ks] = 0u; }
+        }
         return;
     }
 #pragma unroll
@@ -172,6 +182,7 @@ __device__ __forceinline__ void score_chunk(const AttnParams& p, const __half* l
             if (KEEP_K) {
 #pragma unroll
                 for (int tl = 0; tl < 2; ++tl) {
+                    if (!T1 && tl == 1) { kr[1][0][ks] = 0u; kr[1][1][ks] = 0u; continue; }
                     const float2 lo = FS::unpack(kb[tl][0][ks]), hi = FS::unpack(kb[tl][1][ks]);
                     const float c0 = cs[2 * u], c1 = cs[2 * u + 1], s0 = sn[2 * u], s1 = sn[2 * u + 1];
                     kr[tl][0][ks] = FS::pack(lo.x * c0 + hi.x * s0, lo.y * c1 + hi.y * s1);
@@ -180,15 +191,15 @@ __device__ __forceinline__ void score_chunk(const AttnParams& p, const __half* l
             }
             if (u) {
                 FS::mma(T0, a[0], a[1], a[2], a[3], kb[0][0][ks], kb[0][1][ks]);
-                FS::mma(T1, a[0], a[1], a[2], a[3], kb[1][0][ks], kb[1][1][ks]);
+                if (T1) FS::mma(U1, a[0], a[1], a[2], a[3], kb[1][0][ks], kb[1][1][ks]);
             } else {
                 FS::mma(S0, a[0], a[1], a[2], a[3], kb[0][0][ks], kb[0][1][ks]);
-                FS::mma(S1, a[0], a[1], a[2], a[3], kb[1][0][ks], kb[1][1][ks]);
+                if (T1) FS::mma(S1, a[0], a[1], a[2], a[3], kb[1][0][ks], kb[1][1][ks]);
             }
         }
     }
 #pragma unroll
-    for (int i = 0; i < 4; ++i) { S0[i] += T0[i]; S1[i] += T1[i]; }
+    for (int i = 0; i < 4; ++i) { S0[i] += T0[i]; S1[i] += U1[i]; }
 }
 
 // Raw rows g and g+8 of a [heads, D] block in the fragment order used above (zero for rows beyond the group).

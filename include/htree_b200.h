@@ -111,7 +111,7 @@ int htree_b200_rotate_keys(const HtreeShape* shape, void* const* layers_k, void*
  * HTREE_FWD_SELECT_ONLY — htree_recompute_selection_kernel / _recompute_parents (src/parallel.py:1167-1399,
  * src/backward.py:881-934).
  *   layers_k_rot  NULL or the K' levels written by htree_b200_build_tree; when present (and the shape qualifies:
- *                 bf16/fp16, K == V in {64,128}, H/H_kv <= 16, compression_rate 16) the tensor-core kernel runs,
+ *                 bf16/fp16, K == V in {64,128}, H/H_kv <= 16, compression_rate 16 or 8) the tensor-core kernel runs,
  *                 otherwise the generic fp32-arithmetic kernel
  *   cos_cache, sin_cache  [n_pos, K/2] fp32 RoPE tables (src/parallel.py:983-988); n_pos >= top_k*compression_rate
  *   cos_half, sin_half    NULL, or [n_pos, K/2] IEEE half tables holding cos*scale and sin*scale: the tensor-core
@@ -132,7 +132,7 @@ int htree_b200_forward(const HtreeShape* shape, const void* q, void* const* laye
 /* Backward: replaces htree_backward and every kernel it launches (preprocess_delta, dq_bottom/upper,
  * build_parent_mask, dkv_bottom/upper, tree_backward; src/backward.py:45-841, 941-1119).
  *   layers_k_rot  NULL or the K' levels of htree_b200_build_tree: selects the tensor-core kernel where the shape
- *                 qualifies (bf16/fp16, K == V == 128, H/H_kv <= 16, compression_rate 16), else the generic kernel
+ *                 qualifies (bf16/fp16, K == V in {64,128}, H/H_kv <= 16, compression_rate 16 or 8), else the generic kernel
  *   out, dO [B,T,H,V] in `dtype`; gmax, gsum from the forward; parents[l] as written by the forward (required)
  *   dq [B,T,H,K] fp32 (written)
  *   dk_levels[l] [B,N_l,H_kv,K] fp32, dv_levels[l] [B,N_l,H_kv,V] fp32 for every level: zero-filled by this call,

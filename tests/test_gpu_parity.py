@@ -240,6 +240,8 @@ MMA_CASES = {
     "bf16_D128_G16_T2048": dict(B=2, T=2048, H=32, H_kv=2, K=128, V=128, CR=16, TK=16, MTN=256, dtype="bfloat16", seed=22),
     "f16_D128_G4_T1500": dict(B=1, T=1500, H=4, H_kv=1, K=128, V=128, CR=16, TK=32, MTN=64, dtype="float16", seed=23),
     "bf16_D128_G16_T6000_tk64": dict(B=1, T=6000, H=16, H_kv=1, K=128, V=128, CR=16, TK=64, MTN=128, dtype="bfloat16", seed=24),
+    "bf16_D64_G8_cr8_T2500": dict(B=2, T=2500, H=8, H_kv=1, K=64, V=64, CR=8, TK=16, MTN=40, dtype="bfloat16", seed=25),
+    "f16_D128_G12_cr8_T1300": dict(B=1, T=1300, H=12, H_kv=1, K=128, V=128, CR=8, TK=24, MTN=30, dtype="float16", seed=26),
 }
 
 
@@ -316,7 +318,8 @@ def _oracle_grads_with_our_forward(c, q, k, v, dO, out, ctx):
     return oracle.backward(parity.f32(q), fwd, parity.f32(dO), c["CR"], c["TK"], c["dtype"])
 
 
-@pytest.mark.parametrize("name", ["bf16_D128_G16_T2048", "f16_D128_G4_T1500", "bf16_D64_G8_T3000"])
+@pytest.mark.parametrize("name", ["bf16_D128_G16_T2048", "f16_D128_G4_T1500", "bf16_D64_G8_T3000", "bf16_D64_G8_cr8_T2500",
+                                  "f16_D128_G12_cr8_T1300"])
 def test_tensor_core_backward_against_oracle(name):
     ops = _ops()
     c = MMA_CASES[name]
@@ -394,7 +397,7 @@ def test_edge_shapes_forward_backward(c):
     L = ctx["num_layers"]
     assert L == ref["num_layers"]
     ours_parents = [ctx["per_layer_parents"][l].cpu().numpy() for l in range(L)]
-    fast = ctx["layers_k_rot"] is not None and c["K"] == c["V"] and c["K"] in (64, 128) and c["H"] // c["H_kv"] <= 16 and c["CR"] == 16
+    fast = ctx["layers_k_rot"] is not None and c["K"] == c["V"] and c["K"] in (64, 128) and c["H"] // c["H_kv"] <= 16 and c["CR"] in (8, 16)
     same, near = compare_with_oracle(c, q, k, v, ours_parents, ref, EPS_SEL_MMA if fast else EPS_SEL[c["dtype"]])
     G = c["H"] // c["H_kv"]
     rows = np.repeat(same, G).reshape(c["B"], c["T"], c["H"])
