@@ -1,4 +1,4 @@
-"""Benchmark of the htree hot path: forward + backward tokens/s at T=64K bf16 (BASELINE config 3) on N GPUs.
+"""Benchmark of the htree hot path: forward + backward tokens/s at T=64K bf16 (benchmark configuration "cfg3") on N GPUs.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload cfg3] [--t-scale S]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...

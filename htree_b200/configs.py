@@ -1,4 +1,4 @@
-"""The benchmark / parity workloads (BASELINE.json configs of this build) and their data-independent cost model.
+"""The benchmark / parity workloads (cfg1 .. cfg5: the configurations the reference is benchmarked and checked on) and their data-independent cost model.
 
 Counts follow the expansion rule of the operator (src/naive.py:108-118, 182-190 of skywong14/htree): at level l a
 query at position t scores nc_l(t) candidates and accumulates acc_l(t) of them; both depend only on t and the shape.

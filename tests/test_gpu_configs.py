@@ -1,4 +1,4 @@
-"""GPU parity at the BASELINE configuration sizes: sampled groups against the CPU oracle (the oracle evaluates single
+"""GPU parity at the benchmark configuration sizes (htree_b200.configs): sampled groups against the CPU oracle (the oracle evaluates single
 (batch, position, KV head) groups, so full-size sequences can be spot-checked), size-independent properties
 (causality, window consistency, finiteness), the near-tie stress workload, and the sequence-sharded forward."""
 import os
@@ -45,7 +45,7 @@ def compare_sampled(c, q, k, v, out, ctx, queries, eps):
 
 
 def test_config2_full_size_forward():
-    """BASELINE config 2 exactly: B=1, T=32768, H_q=32, H_kv=2, head_dim=128, bf16, CR=16, max_top_nodes=128, Top-K=64."""
+    """Configuration cfg2 exactly: B=1, T=32768, H_q=32, H_kv=2, head_dim=128, bf16, CR=16, max_top_nodes=128, Top-K=64."""
     ops = _ops()
     c = dict(B=1, T=32768, H=32, H_kv=2, K=128, V=128, CR=16, TK=64, MTN=128, dtype="bfloat16", seed=0)
     q, k, v, _ = parity.case_inputs(c)
@@ -72,7 +72,7 @@ def test_config2_full_size_forward():
 
 
 def test_config3_shapes_forward_backward():
-    """BASELINE config 3 shapes with one batch element: T=65536, H_q=64, H_kv=4, head_dim=128, bf16, CR=16,
+    """Configuration cfg3 shapes with one batch element: T=65536, H_q=64, H_kv=4, head_dim=128, bf16, CR=16,
     max_top_nodes=256, Top-K=64; forward and backward."""
     ops = _ops()
     c = dict(B=1, T=65536, H=64, H_kv=4, K=128, V=128, CR=16, TK=64, MTN=256, dtype="bfloat16", seed=1)
@@ -107,7 +107,7 @@ def test_config3_shapes_forward_backward():
 
 
 def stress_inputs(B, T, H, Hkv, D, dtype, seed):
-    """Near-tie workload of BASELINE config 5: keys = N(0,1) plus a rank-4 shared component with N(0, std 3)
+    """Near-tie workload of configuration cfg5: keys = N(0,1) plus a rank-4 shared component with N(0, std 3)
     coefficients, which clusters scores; q, v, dO ~ N(0,1)."""
     g = torch.Generator().manual_seed(seed)
     q = torch.randn(B, T, H, D, generator=g)
@@ -124,7 +124,7 @@ def stress_inputs(B, T, H, Hkv, D, dtype, seed):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("tk", [16, 32, 64, 128])
 def test_config5_near_tie_stress(dtype, tk):
-    """BASELINE config 5: B=2, T=16384, H_q=16, H_kv=2, head_dim=64, CR=8, max_top_nodes=64, Top-K swept."""
+    """Configuration cfg5: B=2, T=16384, H_q=16, H_kv=2, head_dim=64, CR=8, max_top_nodes=64, Top-K swept."""
     ops = _ops()
     c = dict(B=2, T=16384, H=16, H_kv=2, K=64, V=64, CR=8, TK=tk, MTN=64, dtype=dtype, seed=50 + tk)
     q, k, v, dO = stress_inputs(c["B"], c["T"], c["H"], c["H_kv"], 64, dtype, c["seed"])

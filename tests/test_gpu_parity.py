@@ -199,7 +199,7 @@ def test_causality_and_forced_rightmost():
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_headline_cpu_case_full(dtype):
-    """BASELINE config 1 shapes (B=1,T=2048,H=8,H_kv=2,D=64,CR=16,max_top_nodes=64,Top-K=32), every group against the oracle,
+    """Configuration cfg1 shapes (B=1,T=2048,H=8,H_kv=2,D=64,CR=16,max_top_nodes=64,Top-K=32), every group against the oracle,
     forward and backward."""
     ops = _ops()
     c = dict(B=1, T=2048, H=8, H_kv=2, K=64, V=64, CR=16, TK=32, MTN=64, dtype=dtype, seed=0)
