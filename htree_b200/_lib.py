@@ -15,6 +15,7 @@ F32, BF16, F16 = 0, 1, 2
 FWD_SELECT_ONLY = 1
 FWD_GENERIC = 2
 FWD_FUSED = 4
+FWD_TILED = 8
 
 # every exported symbol of include/htree_b200.h; tests check that the library exports all of them
 SYMBOLS = (

@@ -21,7 +21,9 @@ constexpr int NT = 256;   // threads per block
 
 struct FwdSmem {
     float* qT;      // [K][GPAD]   rotated, scaled queries, head-minor
-    float* S;       // [maxc][RS]  scores, later probabilities (RS = GPAD + 4: conflict-free 16-byte rows)
+    float* S;       // [maxc][RS]  scores, later probabilities (RS = GPAD + 4: conflict-free 16-byte rows);
+                    // tiled variant: [NT][RS], the scores of one tile of candidates
+    float* mj;      // [maxc]      tiled variant only: per-candidate score maximum of the selection pass
     uint32_t* key;  // [maxc]      importance bit patterns
     uint8_t* sel;   // [maxc]
     int32_t* par;   // [2][TK]
@@ -36,11 +38,13 @@ struct FwdSmem {
 
 __host__ __device__ inline size_t align16(size_t x) { return (x + 15) & ~size_t(15); }
 
-__host__ __device__ inline size_t fwd_smem_layout(int K, int V, int GPAD, int GP, int maxc, int TK, FwdSmem* m, unsigned char* base) {
+__host__ __device__ inline size_t fwd_smem_layout(int K, int V, int GPAD, int GP, int maxc, int TK, bool tiled, FwdSmem* m,
+                                                  unsigned char* base) {
     size_t o = 0;
     auto take = [&](size_t bytes) { size_t r = o; o = align16(o + bytes); return r; };
     size_t a_qT = take(sizeof(float) * K * GPAD);
-    size_t a_S = take(sizeof(float) * (size_t)maxc * (GPAD + 4));
+    size_t a_S = take(sizeof(float) * (size_t)(tiled ? NT : maxc) * (GPAD + 4));
+    size_t a_mj = take(tiled ? sizeof(float) * maxc : 0);
     size_t a_key = take(sizeof(uint32_t) * maxc);
     size_t a_sel = take(maxc);
     size_t a_par = take(sizeof(int32_t) * 2 * TK);
@@ -52,12 +56,43 @@ __host__ __device__ inline size_t fwd_smem_layout(int K, int V, int GPAD, int GP
     size_t a_wtot = take(sizeof(int) * (NT / 32));
     size_t a_cnt = take(sizeof(int) * 4);
     if (m) {
-        m->qT = (float*)(base + a_qT); m->S = (float*)(base + a_S); m->key = (uint32_t*)(base + a_key);
+        m->qT = (float*)(base + a_qT); m->S = (float*)(base + a_S); m->mj = (float*)(base + a_mj); m->key = (uint32_t*)(base + a_key);
         m->sel = (uint8_t*)(base + a_sel); m->par = (int32_t*)(base + a_par); m->gout = (float*)(base + a_gout);
         m->lo = (float*)(base + a_lo); m->part = (float*)(base + a_part); m->red = (float*)(base + a_red);
         m->st = (float*)(base + a_st); m->wtot = (int*)(base + a_wtot); m->cnt = (int*)(base + a_cnt);
     }
     return o;
+}
+
+// Scores of ONE candidate against GP query heads (head chunk starting at g0): rotate the key row by the candidate's
+// position, dot with the rotated queries held head-minor in shared memory (src/naive.py:193-199).
+template <typename T, int GP>
+__device__ __forceinline__ void score_row(const float* qT, int GPAD, int g0, const T* kr, const float* cj, const float* sj,
+                                          int half, float (&acc)[GP]) {
+#pragma unroll
+    for (int g = 0; g < GP; ++g) acc[g] = 0.f;
+    for (int d = 0; d < half; d += 4) {
+        float lo[4], hi[4];
+        load4<T>(kr + d, lo);
+        load4<T>(kr + d + half, hi);
+        const float4 c4 = __ldg(reinterpret_cast<const float4*>(cj + d));
+        const float4 s4 = __ldg(reinterpret_cast<const float4*>(sj + d));
+        const float cs[4] = {c4.x, c4.y, c4.z, c4.w}, sn[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const float klo = lo[u] * cs[u] - hi[u] * sn[u];
+            const float khi = lo[u] * sn[u] + hi[u] * cs[u];
+            const float* qa = qT + (d + u) * GPAD + g0;
+            const float* qb = qT + (d + u + half) * GPAD + g0;
+#pragma unroll
+            for (int g = 0; g < GP; g += 4) {
+                const float4 x = *reinterpret_cast<const float4*>(qa + g);
+                const float4 y = *reinterpret_cast<const float4*>(qb + g);
+                acc[g] += x.x * klo; acc[g + 1] += x.y * klo; acc[g + 2] += x.z * klo; acc[g + 3] += x.w * klo;
+                acc[g] += y.x * khi; acc[g + 1] += y.y * khi; acc[g + 2] += y.z * khi; acc[g + 3] += y.w * khi;
+            }
+        }
+    }
 }
 
 // Block-wide count of keys >= thr among key[0..nc).  `slot` rotates over three shared counters so that one barrier
@@ -76,13 +111,16 @@ __device__ __forceinline__ int count_ge(const uint32_t* key, int nc, uint32_t th
     return r;
 }
 
-template <typename T, int GP>
+// TILED: the level's scores do not fit into shared memory (large top_k * compression_rate * group).  The selection pass
+// then keeps only a (maximum, sum of exponentials) pair per candidate and the accumulation pass re-scores the
+// candidates tile by tile with an online softmax, instead of holding every score of the level.
+template <typename T, int GP, bool TILED>
 __global__ void __launch_bounds__(NT) fwd_generic_kernel(const __grid_constant__ AttnParams p) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int K = p.K, V = p.V, CR = p.CR, TK = p.TK, G = p.G, L = p.L, half = K >> 1;
     const int GPAD = (G + GP - 1) / GP * GP, RS = GPAD + 4, maxc = TK * CR;
     FwdSmem m;
-    fwd_smem_layout(K, V, GPAD, GP, maxc, TK, &m, smem_raw);
+    fwd_smem_layout(K, V, GPAD, GP, maxc, TK, TILED, &m, smem_raw);
     float *gm = m.st, *gs = m.st + GPAD, *lm = m.st + 2 * GPAD, *ls = m.st + 3 * GPAD, *sg = m.st + 4 * GPAD, *sc = m.st + 5 * GPAD;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -141,43 +179,36 @@ __global__ void __launch_bounds__(NT) fwd_generic_kernel(const __grid_constant__
 
         // ---- 2. scores: one candidate per thread ----
         float tmax = -INFINITY;
-        for (int j = tid; j < nc; j += NT) {
-            int node = par[j / CR] * CR + j % CR;
-            if (node < 0 || node >= Nl) { if (p.status) atomicOr(p.status, 1); node = 0; }
-            const T* kr = lk + (((int64_t)b * Nl + node) * p.Hkv + hk) * K;
-            const float* cj = p.cosc + (int64_t)j * half;
-            const float* sj = p.sinc + (int64_t)j * half;
-            for (int g0 = 0; g0 < GPAD; g0 += GP) {
-                float acc[GP];
+        const bool need_scores = !TILED || (l > 0 && nc > TK);     // the tiled variant scores the leaves while accumulating
+        if (need_scores) {
+            for (int j = tid; j < nc; j += NT) {
+                int node = par[j / CR] * CR + j % CR;
+                if (node < 0 || node >= Nl) { if (p.status) atomicOr(p.status, 1); node = 0; }
+                const T* kr = lk + (((int64_t)b * Nl + node) * p.Hkv + hk) * K;
+                const float* cj = p.cosc + (int64_t)j * half;
+                const float* sj = p.sinc + (int64_t)j * half;
+                float mrow = -INFINITY, erow = 0.f;   // tiled: running maximum and sum of exp over the head chunks
+                for (int g0 = 0; g0 < GPAD; g0 += GP) {
+                    float acc[GP];
+                    score_row<T, GP>(m.qT, GPAD, g0, kr, cj, sj, half, acc);
+                    if (!TILED) {
 #pragma unroll
-                for (int g = 0; g < GP; ++g) acc[g] = 0.f;
-                for (int d = 0; d < half; d += 4) {
-                    float lo[4], hi[4];
-                    load4<T>(kr + d, lo);
-                    load4<T>(kr + d + half, hi);
-                    const float4 c4 = __ldg(reinterpret_cast<const float4*>(cj + d));
-                    const float4 s4 = __ldg(reinterpret_cast<const float4*>(sj + d));
-                    const float cs[4] = {c4.x, c4.y, c4.z, c4.w}, sn[4] = {s4.x, s4.y, s4.z, s4.w};
+                        for (int g = 0; g < GP; g += 4)
+                            *reinterpret_cast<float4*>(m.S + (size_t)j * RS + g0 + g) = make_float4(acc[g], acc[g + 1], acc[g + 2], acc[g + 3]);
 #pragma unroll
-                    for (int u = 0; u < 4; ++u) {
-                        const float klo = lo[u] * cs[u] - hi[u] * sn[u];
-                        const float khi = lo[u] * sn[u] + hi[u] * cs[u];
-                        const float* qa = m.qT + (d + u) * GPAD + g0;
-                        const float* qb = m.qT + (d + u + half) * GPAD + g0;
+                        for (int g = 0; g < GP; ++g) if (g0 + g < G) tmax = fmaxf(tmax, acc[g]);
+                    } else {
+                        float cmx = -INFINITY;
 #pragma unroll
-                        for (int g = 0; g < GP; g += 4) {
-                            const float4 x = *reinterpret_cast<const float4*>(qa + g);
-                            const float4 y = *reinterpret_cast<const float4*>(qb + g);
-                            acc[g] += x.x * klo; acc[g + 1] += x.y * klo; acc[g + 2] += x.z * klo; acc[g + 3] += x.w * klo;
-                            acc[g] += y.x * khi; acc[g + 1] += y.y * khi; acc[g + 2] += y.z * khi; acc[g + 3] += y.w * khi;
-                        }
+                        for (int g = 0; g < GP; ++g) if (g0 + g < G) cmx = fmaxf(cmx, acc[g]);
+                        const float mn = fmaxf(mrow, cmx);
+                        float e = erow * expf(mrow - mn);
+#pragma unroll
+                        for (int g = 0; g < GP; ++g) if (g0 + g < G) e += expf(acc[g] - mn);
+                        mrow = mn; erow = e;
                     }
                 }
-#pragma unroll
-                for (int g = 0; g < GP; g += 4)
-                    *reinterpret_cast<float4*>(m.S + (size_t)j * RS + g0 + g) = make_float4(acc[g], acc[g + 1], acc[g + 2], acc[g + 3]);
-#pragma unroll
-                for (int g = 0; g < GP; ++g) if (g0 + g < G) tmax = fmaxf(tmax, acc[g]);
+                if (TILED) { m.mj[j] = mrow; m.key[j] = __float_as_uint(erow); tmax = fmaxf(tmax, mrow); }
             }
         }
 
@@ -190,11 +221,14 @@ __global__ void __launch_bounds__(NT) fwd_generic_kernel(const __grid_constant__
             float M = m.red[0];
 #pragma unroll
             for (int i = 1; i < NT / 32; ++i) M = fmaxf(M, m.red[i]);
-            for (int j = tid; j < nc; j += NT) {
-                float s = 0.f;
-                for (int g = 0; g < G; ++g) s += expf(m.S[(size_t)j * RS + g] - M);
-                if (j == rp) s = kForcedImportance;
-                m.key[j] = __float_as_uint(s);   // s >= 0, so the bit pattern orders like the value
+            if (need_scores) {
+                for (int j = tid; j < nc; j += NT) {
+                    float s = 0.f;
+                    if (!TILED) { for (int g = 0; g < G; ++g) s += expf(m.S[(size_t)j * RS + g] - M); }
+                    else s = __uint_as_float(m.key[j]) * expf(m.mj[j] - M);
+                    if (j == rp) s = kForcedImportance;
+                    m.key[j] = __float_as_uint(s);   // s >= 0, so the bit pattern orders like the value
+                }
             }
             __syncthreads();
             if (nc <= TK) {
@@ -232,7 +266,97 @@ __global__ void __launch_bounds__(NT) fwd_generic_kernel(const __grid_constant__
 
         if (!select_only) {
             // ---- 4. accumulate the candidates that were not kept ----
-            if (accumulate) {
+            if (TILED && accumulate) {
+                float* al = sg;   // per-head rescale factor of the running level state (sg is free until the merge)
+                for (int g = tid; g < GPAD; g += NT) { lm[g] = kNegInf; ls[g] = 0.f; }
+                for (int i = tid; i < GPAD * V; i += NT) m.lo[i] = 0.f;
+                __syncthreads();
+                const int vcols = V < NT ? V : NT;
+                const int nsl = NT / vcols;
+                const int slice = tid / vcols, dcol = tid - slice * vcols;
+                for (int j0 = 0; j0 < nc; j0 += NT) {
+                    const int j = j0 + tid;
+                    const bool act = j < nc && !m.sel[j];
+                    // scores of this thread's candidate -> tile row tid (-inf when there is nothing to accumulate)
+                    {
+                        int node = act ? par[j / CR] * CR + j % CR : 0;
+                        if (node < 0 || node >= Nl) { if (p.status) atomicOr(p.status, 1); node = 0; }
+                        const T* kr = lk + (((int64_t)b * Nl + node) * p.Hkv + hk) * K;
+                        const float* cj = p.cosc + (int64_t)(act ? j : 0) * half;
+                        const float* sj = p.sinc + (int64_t)(act ? j : 0) * half;
+                        for (int g0 = 0; g0 < GPAD; g0 += GP) {
+                            float acc[GP];
+                            if (act) score_row<T, GP>(m.qT, GPAD, g0, kr, cj, sj, half, acc);
+#pragma unroll
+                            for (int g = 0; g < GP; ++g) {
+                                const float sv = act ? acc[g] : -INFINITY;
+                                m.S[(size_t)tid * RS + g0 + g] = sv;
+                                const float w = warp_max(sv);
+                                if (lane == 0) m.red[warp * GPAD + g0 + g] = w;
+                            }
+                        }
+                    }
+                    __syncthreads();
+                    for (int g = tid; g < GPAD; g += NT) {
+                        float w = m.red[g];
+                        for (int i = 1; i < NT / 32; ++i) w = fmaxf(w, m.red[i * GPAD + g]);
+                        const float mn = fmaxf(lm[g], w);
+                        al[g] = expf(lm[g] - mn);
+                        lm[g] = mn;
+                    }
+                    __syncthreads();
+                    for (int g = 0; g < GPAD; ++g) {   // probabilities in place, tile sums
+                        float* sp = m.S + (size_t)tid * RS + g;
+                        const float pr = act ? expf(*sp - lm[g]) : 0.f;
+                        *sp = pr;
+                        const float w = warp_sum(pr);
+                        if (lane == 0) m.red[warp * GPAD + g] = w;
+                    }
+                    __syncthreads();
+                    for (int g = tid; g < GPAD; g += NT) {
+                        float w = 0.f;
+                        for (int i = 0; i < NT / 32; ++i) w += m.red[i * GPAD + g];
+                        ls[g] = ls[g] * al[g] + w;
+                    }
+                    const int rows = min(NT, nc - j0);
+                    for (int g0 = 0; g0 < GPAD; g0 += GP) {
+                        for (int d0 = 0; d0 < V; d0 += vcols) {
+                            const int d = d0 + dcol;
+                            float acc[GP];
+#pragma unroll
+                            for (int g = 0; g < GP; ++g) acc[g] = 0.f;
+                            if (slice < nsl && d < V) {
+                                for (int u = slice; u < rows; u += nsl) {
+                                    const int ju = j0 + u;
+                                    if (m.sel[ju]) continue;
+                                    int node = par[ju / CR] * CR + ju % CR;
+                                    if (node < 0 || node >= Nl) node = 0;
+                                    const float vv = to_f(lv[(((int64_t)b * Nl + node) * p.Hkv + hk) * V + d]);
+                                    const float* pr = m.S + (size_t)u * RS + g0;
+#pragma unroll
+                                    for (int g = 0; g < GP; g += 4) {
+                                        const float4 x = *reinterpret_cast<const float4*>(pr + g);
+                                        acc[g] += x.x * vv; acc[g + 1] += x.y * vv; acc[g + 2] += x.z * vv; acc[g + 3] += x.w * vv;
+                                    }
+                                }
+                            }
+#pragma unroll
+                            for (int g = 0; g < GP; ++g) m.part[tid * GP + g] = acc[g];
+                            __syncthreads();
+                            for (int i = tid; i < GP * vcols; i += NT) {
+                                const int g = i / vcols, dc = i - g * vcols;
+                                if (d0 + dc < V) {
+                                    float w = 0.f;
+                                    for (int s2 = 0; s2 < nsl; ++s2) w += m.part[(s2 * vcols + dc) * GP + g];
+                                    float* o = m.lo + (g0 + g) * V + d0 + dc;
+                                    *o = *o * al[g0 + g] + w;
+                                }
+                            }
+                            __syncthreads();
+                        }
+                    }
+                }
+            } else if (accumulate) {
                 for (int g0 = 0; g0 < GPAD; g0 += GP) {   // row maxima over the accumulated set
                     float mx[GP];
 #pragma unroll
@@ -364,23 +488,31 @@ __global__ void __launch_bounds__(NT) fwd_generic_kernel(const __grid_constant__
     }
 }
 
+template <typename T, bool TILED>
+static int launch_tt(const AttnParams& p, size_t smem, int GP, cudaStream_t st) {
+    dim3 grid(p.Tq, p.B * p.Hkv);
+    cudaError_t e;
+#define HT_LAUNCH(GPV)                                                                                                     \
+    e = cudaFuncSetAttribute(fwd_generic_kernel<T, GPV, TILED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
+    if (e != cudaSuccess) return (int)e;                                                                                   \
+    fwd_generic_kernel<T, GPV, TILED><<<grid, NT, smem, st>>>(p);
+    if (GP == 4) { HT_LAUNCH(4) } else if (GP == 8) { HT_LAUNCH(8) } else { HT_LAUNCH(16) }
+#undef HT_LAUNCH
+    note_launch();
+    return (int)cudaGetLastError();
+}
+
 template <typename T>
 static int launch_t(const AttnParams& p, cudaStream_t st) {
     const int G = p.G;
     const int GP = G <= 4 ? 4 : (G <= 8 ? 8 : 16);
     const int GPAD = (G + GP - 1) / GP * GP;
-    const size_t smem = fwd_smem_layout(p.K, p.V, GPAD, GP, p.TK * p.CR, p.TK, nullptr, nullptr);
-    if (smem > 227 * 1024) return HTREE_E_UNSUPPORTED;
-    dim3 grid(p.Tq, p.B * p.Hkv);
-    cudaError_t e;
-#define HT_LAUNCH(GPV)                                                                                              \
-    e = cudaFuncSetAttribute(fwd_generic_kernel<T, GPV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
-    if (e != cudaSuccess) return (int)e;                                                                            \
-    fwd_generic_kernel<T, GPV><<<grid, NT, smem, st>>>(p);
-    if (GP == 4) { HT_LAUNCH(4) } else if (GP == 8) { HT_LAUNCH(8) } else { HT_LAUNCH(16) }
-#undef HT_LAUNCH
-    note_launch();
-    return (int)cudaGetLastError();
+    const size_t limit = 227 * 1024;
+    const size_t full = fwd_smem_layout(p.K, p.V, GPAD, GP, p.TK * p.CR, p.TK, false, nullptr, nullptr);
+    if (full <= limit && !(p.flags & HTREE_FWD_TILED)) return launch_tt<T, false>(p, full, GP, st);
+    const size_t tiled = fwd_smem_layout(p.K, p.V, GPAD, GP, p.TK * p.CR, p.TK, true, nullptr, nullptr);
+    if (tiled > limit) return HTREE_E_UNSUPPORTED;
+    return launch_tt<T, true>(p, tiled, GP, st);
 }
 
 int launch_fwd_generic(const AttnParams& p, int dtype, cudaStream_t st) {

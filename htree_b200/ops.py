@@ -198,7 +198,7 @@ def htree_forward(
     scale: Optional[float] = None, rope_base: float = 10000.0,
     _save_for_backward: bool = False, _save_parents: bool = True,
     return_trace: bool = False, _force_generic: bool = False, _q_offset: Optional[int] = None, _layers=None,
-    _fused: bool = False,
+    _fused: bool = False, _tiled: bool = False,
 ):
     """htree forward.  q [B,T,H,K], k [B,T,H_kv,K], v [B,T,H_kv,V] -> out [B,T,H,V] in q's dtype.
 
@@ -238,6 +238,8 @@ def htree_forward(
               torch.empty(L, B, T, H, V, dtype=torch.float32, device=dev))
         trace = _lib.HtreeTrace(tr[0].data_ptr(), tr[1].data_ptr(), tr[2].data_ptr())
     flags = _lib.FWD_GENERIC if (_force_generic or return_trace) else (_lib.FWD_FUSED if _fused else 0)
+    if _tiled:
+        flags |= _lib.FWD_TILED
     half_tables = rope_cache_half(K, cos_cache.shape[0], rope_base, scale, dev) if layers_kr is not None else None
     _run_forward(shape, q, layers_k, layers_v, cos_cache, sin_cache, scale, out, gmax, gsum, parents, trace, flags,
                  layers_kr, half_tables)

@@ -47,6 +47,8 @@ extern "C" {
 #define HTREE_FWD_SELECT_ONLY 1u /* rebuild the selections only: no V reads, no accumulation, out/gmax/gsum untouched */
 #define HTREE_FWD_GENERIC 2u     /* force the dtype-generic fp32-arithmetic kernel even where a tensor-core kernel exists
                                     (also honoured by the backward) */
+#define HTREE_FWD_TILED 8u       /* generic forward: use the tiled variant (scores not held for a whole level) even when the
+                                    untiled one fits into shared memory; it is chosen automatically when it does not */
 #define HTREE_FWD_FUSED 4u       /* tensor-core forward: keep selection and accumulation in ONE kernel even when parent
                                     buffers are provided (default then: a selection kernel followed by an accumulation kernel) */
 

@@ -425,3 +425,42 @@ def test_split_and_fused_tensor_core_forward_agree():
     assert torch.equal(ctx_a["global_max"], ctx_b["global_max"]) and torch.equal(ctx_a["global_sum"], ctx_b["global_sum"])
     for l in range(ctx_a["num_layers"]):
         assert torch.equal(ctx_a["per_layer_parents"][l], ctx_b["per_layer_parents"][l])
+
+
+@pytest.mark.parametrize("name", ["f32_T300_cr4_tk8", "bf16_T512_cr8_tk16", "f32_T1024_cr16_tk32"])
+def test_tiled_generic_forward_matches_untiled(name):
+    """The tiled variant of the generic forward (scores re-computed tile by tile, online softmax) against the untiled one."""
+    ops = _ops()
+    c = CASES[name]
+    q, k, v, _ = (x.to(DEV) for x in parity.case_inputs(c))
+    a, ctx_a = ops.htree_forward(q, k, v, c["CR"], c["MTN"], c["TK"], _save_for_backward=True, _force_generic=True)
+    b, ctx_b = ops.htree_forward(q, k, v, c["CR"], c["MTN"], c["TK"], _save_for_backward=True, _force_generic=True, _tiled=True)
+    torch.cuda.synchronize(); ops.check_status()
+    for l in range(ctx_a["num_layers"]):
+        assert torch.equal(ctx_a["per_layer_parents"][l], ctx_b["per_layer_parents"][l])
+    tol = 2e-6 if c["dtype"] == "float32" else 8e-3
+    assert float((a.float() - b.float()).abs().max()) <= tol
+    assert torch.allclose(ctx_a["global_max"], ctx_b["global_max"], rtol=1e-6, atol=1e-6)
+    assert torch.allclose(ctx_a["global_sum"], ctx_b["global_sum"], rtol=1e-5, atol=1e-7)
+
+
+@pytest.mark.parametrize("dtype,H,H_kv", [("float16", 16, 4), ("float32", 16, 1)])
+def test_reference_default_parameters(dtype, H, H_kv):
+    """The reference's own default arguments (compression_rate 16, max_top_nodes 8192, top_k_per_layer 512, head_dim 32;
+    correctness_test.py:612-624, speed_test.py:315-328): 8192 candidates per level, served by the tiled generic forward."""
+    ops = _ops()
+    c = dict(B=1, T=12000, H=H, H_kv=H_kv, K=32, V=32, CR=16, TK=512, MTN=8192, dtype=dtype, seed=81)
+    q, k, v, dO = parity.case_inputs(c)
+    qd, kd, vd, dOd = (x.to(DEV) for x in (q, k, v, dO))
+    out = ops.htree_forward_triton_autograd(qd.requires_grad_(True), kd.requires_grad_(True), vd.requires_grad_(True))
+    out.backward(dOd)
+    torch.cuda.synchronize(); ops.check_status()
+    rng = np.random.default_rng(5)
+    n = 96
+    queries = np.stack([np.zeros(n, np.int64), np.sort(rng.integers(0, c["T"], n)), rng.integers(0, H_kv, n)], 1).astype(np.int32)
+    ref = oracle.forward(parity.f32(q), parity.f32(k), parity.f32(v), 16, 8192, 512, dtype=dtype, queries=queries)
+    G = H // H_kv
+    o = out.detach().float().cpu().numpy().reshape(1, c["T"], H_kv, G, -1)[0, queries[:, 1], queries[:, 2]]
+    assert_out_close(o, ref["out_rounded"], dtype)
+    for gname, t in (("dq", qd.grad), ("dk", kd.grad), ("dv", vd.grad)):
+        assert bool(torch.isfinite(t.float()).all()), gname
