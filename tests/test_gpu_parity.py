@@ -464,3 +464,33 @@ def test_reference_default_parameters(dtype, H, H_kv):
     assert_out_close(o, ref["out_rounded"], dtype)
     for gname, t in (("dq", qd.grad), ("dk", kd.grad), ("dv", vd.grad)):
         assert bool(torch.isfinite(t.float()).all()), gname
+
+
+def test_tensor_core_kernels_with_reference_sized_top_k():
+    """top_k_per_layer = 512, max_top_nodes = 8192 (the reference's defaults) on the tensor-core kernels: 8192 leaf
+    candidates per query, 32 KB of importances per warp."""
+    ops = _ops()
+    c = dict(B=1, T=20000, H=16, H_kv=1, K=128, V=128, CR=16, TK=512, MTN=8192, dtype="bfloat16", seed=91)
+    q, k, v, dO = parity.case_inputs(c)
+    qd, kd, vd, dOd = (x.to(DEV) for x in (q, k, v, dO))
+    out, ctx = ops.htree_forward(qd, kd, vd, 16, 8192, 512, _save_for_backward=True)
+    dq, dk, dv = ops.htree_backward(dOd, qd, out, ctx)
+    torch.cuda.synchronize(); ops.check_status()
+    assert ctx["layers_k_rot"] is not None and ctx["num_layers"] == 2
+    rng = np.random.default_rng(6)
+    n = 64
+    queries = np.stack([np.zeros(n, np.int64), np.sort(rng.integers(9000, c["T"], n)), np.zeros(n, np.int64)], 1).astype(np.int32)
+    ref = oracle.forward(parity.f32(q), parity.f32(k), parity.f32(v), 16, 8192, 512, dtype="bfloat16", queries=queries,
+                         return_importance=True)
+    ti = queries[:, 1]
+    ours = ctx["per_layer_parents"][0][0, ti, 0].cpu().numpy()
+    ex, near, bad = parity.compare_selections(ours, ref["parents"][0], ref["importance"][1], ref["parents"][1], 16, EPS_SEL_MMA)
+    assert bad == 0 and ex + near == n
+    same = (ours == ref["parents"][0]).all(-1)
+    o = out.float().cpu().numpy()[0, ti]
+    assert float(np.abs(o - ref["out_rounded"])[same].max()) <= 2e-2
+    dq_g, dk_g, dv_g = ops.htree_backward(dOd, qd, out, ctx, _force_generic=True)
+    for nm, a, b in (("dq", dq, dq_g), ("dk", dk, dk_g), ("dv", dv, dv_g)):
+        st = parity.err_stats(parity.f32(a), parity.f32(b))
+        scale = max(1.0, float(b.abs().max()))
+        assert st["max"] <= 2e-2 * scale and st["p99"] <= 5e-3 * scale, (nm, st)
