@@ -24,7 +24,8 @@ def sample_queries(B, T, Hkv, n, seed):
 def compare_sampled(c, q, k, v, out, ctx, queries, eps):
     """Selections (near-tie rule, level by level) and outputs of the sampled groups.  Returns (fraction of sampled
     groups identical at every level, max |out - oracle| over those groups)."""
-    ref = oracle.forward(parity.f32(q), parity.f32(k), parity.f32(v), c["CR"], c["MTN"], c["TK"], dtype=c["dtype"],
+    as_f32 = lambda x: x if isinstance(x, np.ndarray) else parity.f32(x)
+    ref = oracle.forward(as_f32(q), as_f32(k), as_f32(v), c["CR"], c["MTN"], c["TK"], dtype=c["dtype"],
                          queries=queries, return_importance=True)
     L, TK, G = ctx["num_layers"], c["TK"], c["H"] // c["H_kv"]
     assert L == ref["num_layers"]
@@ -209,3 +210,41 @@ def test_sequence_sharded_forward_two_gpus():
     for p in procs:
         p.join(60)
     assert results == [(0, True), (1, True)]
+
+
+def test_config4_length_forward():
+    """The long-context length of configuration cfg4 (T = 524288, four tree levels, groups of 8 heads) with one KV head:
+    sampled groups against the oracle, causality of the last quarter, and the query window used for sequence sharding.
+    Only the sampled query rows come from the CPU generator (the others are device-random: a group's result depends on
+    its own query rows and on k, v only)."""
+    ops = _ops()
+    c = dict(B=1, T=524288, H=8, H_kv=1, K=128, V=128, CR=16, TK=64, MTN=512, dtype="bfloat16", seed=7)
+    g = torch.Generator().manual_seed(c["seed"])
+    k = torch.randn(1, c["T"], 1, 128, generator=g).bfloat16()
+    v = torch.randn(1, c["T"], 1, 128, generator=g).bfloat16()
+    n = 96
+    ts = np.sort(np.random.default_rng(8).choice(c["T"], n, replace=False))
+    ts[-1] = c["T"] - 1; ts[0] = 0
+    q_rows = torch.randn(n, 8, 128, generator=g).bfloat16()
+    qd = torch.randn(1, c["T"], 8, 128, device=DEV, generator=torch.Generator(device=DEV).manual_seed(1)).bfloat16()
+    qd[0, torch.from_numpy(ts).to(DEV)] = q_rows.to(DEV)
+    kd, vd = k.to(DEV), v.to(DEV)
+    out, ctx = ops.htree_forward(qd, kd, vd, 16, 512, 64, _save_for_backward=True)
+    torch.cuda.synchronize(); ops.check_status()
+    assert ctx["num_layers"] == 4 and [x.shape[1] for x in ctx["layers_k"]] == [524288, 32768, 2048, 128]
+    assert bool(torch.isfinite(out.float()).all())
+    q_sparse = np.zeros((1, c["T"], 8, 128), np.float32)
+    q_sparse[0, ts] = q_rows.float().numpy()
+    queries = np.stack([np.zeros(n, np.int64), ts, np.zeros(n, np.int64)], 1).astype(np.int32)
+    frac, err, _, _ = compare_sampled(c, q_sparse, k, v, out, ctx, queries, EPS_SEL_MMA)
+    print(f"\n[cfg4 length] sampled groups identical at every level: {frac:.4f}; max|out-oracle| on them {err:.3e}")
+    assert frac > 0.93 and err <= 2e-2
+    t0 = 400000
+    k2, v2 = kd.clone(), vd.clone()
+    k2[:, t0 + 1:] += 1.0; v2[:, t0 + 1:] -= 1.0
+    out2 = ops.htree_forward(qd, k2, v2, 16, 512, 64)
+    assert torch.equal(out[:, : t0 + 1], out2[:, : t0 + 1])
+    a, b = 458752, 524288          # the last eighth, as one of 8 sequence-sharded ranks would compute it
+    layers = (ctx["layers_k"], ctx["layers_v"], ctx["layers_k_rot"])
+    out_w = ops.htree_forward(qd[:, a:b].contiguous(), kd, vd, 16, 512, 64, _q_offset=a, _layers=layers)
+    assert torch.equal(out_w, out[:, a:b])
