@@ -180,6 +180,53 @@ int htree_b200_forward(const HtreeShape* shape, const void* q, void* const* laye
     return launch_fwd_generic(p, shape->dtype, (cudaStream_t)stream);
 }
 
+int htree_b200_level_forward(const HtreeShape* s, int32_t level, int32_t n_level, const void* q, const void* layer_k,
+                             const void* layer_v, const int32_t* prev_parents, const float* cos_cache,
+                             const float* sin_cache, int32_t n_pos, float scale, float* layer_max, float* layer_sum,
+                             float* layer_out, int32_t* next_parents, int32_t* status, void* stream) {
+    if (!s || !q || !layer_k || !layer_v || !prev_parents || !cos_cache || !sin_cache || !layer_max || !layer_sum || !layer_out)
+        return HTREE_E_NULL;
+    if (s->B <= 0 || s->T <= 0 || s->H <= 0 || s->H_kv <= 0 || s->K <= 0 || s->V <= 0 || s->top_k <= 0 || n_level <= 0 ||
+        s->compression_rate < 2 || s->H % s->H_kv != 0 || (s->K & 1))
+        return HTREE_E_SHAPE;
+    if (level < 0 || level >= HTREE_MAX_LEVELS) return HTREE_E_LEVELS;
+    if (level > 0 && !next_parents) return HTREE_E_NULL;
+    if (s->dtype != HTREE_F32 && s->dtype != HTREE_BF16 && s->dtype != HTREE_F16) return HTREE_E_DTYPE;
+    if (s->K % 8 != 0 || s->V % 8 != 0 || !aligned16(q) || !aligned16(layer_k) || !aligned16(layer_v) || !aligned16(cos_cache) ||
+        !aligned16(sin_cache))
+        return HTREE_E_ALIGN;
+    if ((int64_t)n_pos < (int64_t)s->top_k * s->compression_rate) return HTREE_E_ROPE;
+    if ((int64_t)s->B * s->H_kv > 65535) return HTREE_E_UNSUPPORTED;
+    AttnParams p;
+    std::memset(&p, 0, sizeof(p));
+    p.q = q; p.lk[level] = layer_k; p.lv[level] = layer_v; p.ln[level] = n_level;
+    int64_t pw = 1;
+    for (int l = 0; l < level; ++l) pw *= s->compression_rate;
+    p.lpow[level] = pw;
+    p.cosc = cos_cache; p.sinc = sin_cache; p.status = status;
+    p.B = s->B; p.T = s->T; p.H = s->H; p.Hkv = s->H_kv; p.K = s->K; p.V = s->V;
+    p.CR = s->compression_rate; p.TK = s->top_k; p.L = level + 1; p.G = s->H / s->H_kv; p.n_pos = n_pos;
+    p.Tq = s->T; p.t0 = 0; p.scale = scale; p.flags = 0;
+    p.level_mode = 1; p.level_index = level; p.parents_in = prev_parents; p.next_out = next_parents;
+    p.tr_max = layer_max; p.tr_sum = layer_sum; p.tr_out = layer_out;
+    return launch_fwd_generic(p, s->dtype, (cudaStream_t)stream);
+}
+
+int htree_b200_merge_to_global(const float* layer_max, const float* layer_sum, const float* layer_out, float* global_max,
+                               float* global_sum, float* global_out, int64_t rows, int32_t V, void* stream) {
+    if (!layer_max || !layer_sum || !layer_out || !global_max || !global_sum || !global_out) return HTREE_E_NULL;
+    if (rows <= 0 || V <= 0) return HTREE_E_SHAPE;
+    return launch_merge_to_global(layer_max, layer_sum, layer_out, global_max, global_sum, global_out, rows, V, (cudaStream_t)stream);
+}
+
+int htree_b200_final_normalize(const float* global_out, const float* global_sum, void* out, int32_t dtype, int64_t rows,
+                               int32_t V, void* stream) {
+    if (!global_out || !global_sum || !out) return HTREE_E_NULL;
+    if (rows <= 0 || V <= 0) return HTREE_E_SHAPE;
+    if (dtype != HTREE_F32 && dtype != HTREE_BF16 && dtype != HTREE_F16) return HTREE_E_DTYPE;
+    return launch_final_normalize(global_out, global_sum, out, dtype, rows, V, (cudaStream_t)stream);
+}
+
 int htree_b200_backward(const HtreeShape* shape, const void* q, void* const* layers_k, void* const* layers_v,
                         void* const* layers_k_rot, const float* cos_cache, const float* sin_cache, const void* cos_half,
                         const void* sin_half, int32_t n_pos, float scale, const void* out,

@@ -40,6 +40,11 @@ struct AttnParams {
     float* dk[HTREE_MAX_LEVELS];
     float* dv[HTREE_MAX_LEVELS];
     int32_t B, T, H, Hkv, K, V, CR, TK, L, G, n_pos;
+    // single-level mode of the generic forward (per-kernel compatibility surface): only level `level_index` runs, its
+    // parent lists come from parents_in and the kept nodes go to next_out; the per-level state goes to tr_* slot 0
+    const int32_t* parents_in;
+    int32_t* next_out;
+    int32_t level_mode, level_index;
     int32_t Tq, t0;   // query window: rows 0..Tq-1 of q/out are sequence positions t0..t0+Tq-1
     float scale;
     uint32_t flags;
@@ -112,6 +117,9 @@ int launch_tree_backward(const HtreeShape& s, int L, const int32_t* ln, float* c
 int launch_rotate_keys(const HtreeShape& s, int L, const int32_t* ln, void* const* lk, void* const* lkr, const float* cosc,
                        const float* sinc, cudaStream_t st);
 int launch_fwd_generic(const AttnParams& p, int dtype, cudaStream_t st);
+int launch_merge_to_global(const float* lmax, const float* lsum, const float* lout, float* gmax, float* gsum, float* gout,
+                           int64_t rows, int V, cudaStream_t st);
+int launch_final_normalize(const float* gout, const float* gsum, void* out, int dtype, int64_t rows, int V, cudaStream_t st);
 bool fwd_mma_supported(const AttnParams& p, int dtype);
 int launch_fwd_mma(const AttnParams& p, int dtype, cudaStream_t st);
 bool bwd_mma_supported(const AttnParams& p, int dtype);

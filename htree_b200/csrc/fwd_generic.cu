@@ -137,7 +137,9 @@ __global__ void __launch_bounds__(NT) fwd_generic_kernel(const __grid_constant__
     if (tid < 4) m.cnt[tid] = 0;
     int32_t* par = m.par;
     int32_t* nxt = m.par + TK;
-    {
+    if (p.level_mode) {
+        for (int i = tid; i < TK; i += NT) par[i] = p.parents_in[qidx * TK + i];
+    } else {
         int np0 = (int)(((int64_t)t / p.lpow[L - 1]) / CR) + 1;
         if (np0 > TK) np0 = TK;
         for (int i = tid; i < TK; i += NT) par[i] = i < np0 ? i : -1;
@@ -145,8 +147,10 @@ __global__ void __launch_bounds__(NT) fwd_generic_kernel(const __grid_constant__
     int slot = 0;
     __syncthreads();
 
-    for (int l = L - 1; l >= 0; --l) {
+    const int l_hi = p.level_mode ? p.level_index : L - 1, l_lo = p.level_mode ? p.level_index : 0;
+    for (int l = l_hi; l >= l_lo; --l) {
         const int Nl = p.ln[l];
+        const int64_t tslot = p.level_mode ? 0 : l;   // slot of this level in the trace arrays
         const T* lk = reinterpret_cast<const T*>(p.lk[l]);
         const T* lv = reinterpret_cast<const T*>(p.lv[l]);
         if (p.parents[l]) for (int i = tid; i < TK; i += NT) p.parents[l][qidx * TK + i] = par[i];
@@ -450,11 +454,11 @@ __global__ void __launch_bounds__(NT) fwd_generic_kernel(const __grid_constant__
             }
 
             // ---- trace + 5. merge into the running state (src/naive.py:215-223) ----
-            if (p.tr_max) for (int g = tid; g < G; g += NT) p.tr_max[(int64_t)l * p.B * p.Tq * p.H + hbase + g] = lm[g];
-            if (p.tr_sum) for (int g = tid; g < G; g += NT) p.tr_sum[(int64_t)l * p.B * p.Tq * p.H + hbase + g] = ls[g];
+            if (p.tr_max) for (int g = tid; g < G; g += NT) p.tr_max[tslot * p.B * p.Tq * p.H + hbase + g] = lm[g];
+            if (p.tr_sum) for (int g = tid; g < G; g += NT) p.tr_sum[tslot * p.B * p.Tq * p.H + hbase + g] = ls[g];
             if (p.tr_out)
                 for (int i = tid; i < G * V; i += NT)
-                    p.tr_out[((int64_t)l * p.B * p.Tq * p.H + hbase) * V + i] = m.lo[i];
+                    p.tr_out[(tslot * p.B * p.Tq * p.H + hbase) * V + i] = m.lo[i];
             for (int g = tid; g < GPAD; g += NT) {
                 const bool ch = ls[g] > kHasMass, gh = gs[g] > kHasMass;
                 const float nm = fmaxf(gm[g], lm[g]);
@@ -477,11 +481,12 @@ __global__ void __launch_bounds__(NT) fwd_generic_kernel(const __grid_constant__
             }
         }
         __syncthreads();
+        if (p.level_mode && l > 0 && p.next_out) for (int i = tid; i < TK; i += NT) p.next_out[qidx * TK + i] = nxt[i];
         int32_t* tmp = par; par = nxt; nxt = tmp;   // the kept nodes are the next level's parents
         if (l == 0) { tmp = par; par = nxt; nxt = tmp; }
     }
 
-    if (!select_only) {
+    if (!select_only && !p.level_mode) {
         T* og = reinterpret_cast<T*>(p.out) + hbase * V;
         for (int i = tid; i < G * V; i += NT) og[i] = from_f<T>(m.gout[i] / gs[i / V]);   // src/parallel.py:321-363
         for (int g = tid; g < G; g += NT) { p.gmax[hbase + g] = gm[g]; p.gsum[hbase + g] = gs[g]; }
@@ -513,6 +518,50 @@ static int launch_t(const AttnParams& p, cudaStream_t st) {
     const size_t tiled = fwd_smem_layout(p.K, p.V, GPAD, GP, p.TK * p.CR, p.TK, true, nullptr, nullptr);
     if (tiled > limit) return HTREE_E_UNSUPPORTED;
     return launch_tt<T, true>(p, tiled, GP, st);
+}
+
+// Stand-alone level merge and final normalisation: the reference's htree_merge_to_global_kernel and
+// htree_final_normalize_kernel (src/parallel.py:248-363), kept for callers that drive the levels one by one.  One warp
+// per (b, t, h) row.  The fused kernels do this on chip.
+__global__ void __launch_bounds__(256) merge_to_global_kernel(const float* lmax, const float* lsum, const float* lout, float* gmax,
+                                                              float* gsum, float* gout, int64_t rows, int V) {
+    const int64_t row = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    const float lm = lmax[row], ls = lsum[row], gm = gmax[row], gs = gsum[row];
+    const bool ch = ls > kHasMass, gh = gs > kHasMass;
+    if (!ch) return;
+    const float nm = fmaxf(gm, lm);
+    const float sg = gh ? expf(gm - nm) : 0.f, sc = expf(lm - nm);
+    for (int d = lane; d < V; d += 32) {
+        const float o = lout[row * V + d];
+        gout[row * V + d] = gh ? gout[row * V + d] * sg + o * sc : o;
+    }
+    __syncwarp();
+    if (lane == 0) { gmax[row] = gh ? nm : lm; gsum[row] = gh ? gs * sg + ls * sc : ls; }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) final_normalize_kernel(const float* gout, const float* gsum, T* out, int64_t rows, int V) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= rows * V) return;
+    out[i] = from_f<T>(gout[i] / gsum[i / V]);
+}
+
+int launch_merge_to_global(const float* lmax, const float* lsum, const float* lout, float* gmax, float* gsum, float* gout,
+                           int64_t rows, int V, cudaStream_t st) {
+    merge_to_global_kernel<<<(unsigned)((rows * 32 + 255) / 256), 256, 0, st>>>(lmax, lsum, lout, gmax, gsum, gout, rows, V);
+    note_launch();
+    return (int)cudaGetLastError();
+}
+
+int launch_final_normalize(const float* gout, const float* gsum, void* out, int dtype, int64_t rows, int V, cudaStream_t st) {
+    const unsigned blocks = (unsigned)((rows * V + 255) / 256);
+    if (dtype == HTREE_F32) final_normalize_kernel<float><<<blocks, 256, 0, st>>>(gout, gsum, (float*)out, rows, V);
+    else if (dtype == HTREE_BF16) final_normalize_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(gout, gsum, (__nv_bfloat16*)out, rows, V);
+    else final_normalize_kernel<__half><<<blocks, 256, 0, st>>>(gout, gsum, (__half*)out, rows, V);
+    note_launch();
+    return (int)cudaGetLastError();
 }
 
 int launch_fwd_generic(const AttnParams& p, int dtype, cudaStream_t st) {

@@ -131,6 +131,23 @@ int htree_b200_forward(const HtreeShape* shape, const void* q, void* const* laye
                        float* gmax, float* gsum, int32_t* const* parents, const HtreeTrace* trace, int32_t* status,
                        uint32_t flags, void* stream);
 
+/* One tree level at a time (the call surface the reference's parity harness uses, correctness_test.py:168-347):
+ * htree_b200_level_forward replaces one launch of htree_select_accumulate_gqa_kernel (level > 0; src/parallel.py:537-867)
+ * or of htree_bottom_accumulate_gqa_kernel (level 0; src/parallel.py:369-530): given the parent lists consumed at this
+ * level it writes the level's accumulator state (layer_max/layer_sum [B,T,H], layer_out [B,T,H,V], fp32) and, above the
+ * leaves, the kept nodes (next_parents [B,T,H_kv,top_k], ascending, -1 padded).  layer_k/layer_v are this level's
+ * tensors [B,n_level,H_kv,*]; shape->T is the query length, shape->max_top_nodes is ignored.  fp32-arithmetic kernel.
+ * htree_b200_merge_to_global / htree_b200_final_normalize replace htree_merge_to_global_kernel and
+ * htree_final_normalize_kernel (src/parallel.py:248-363); rows = B*T*H. */
+int htree_b200_level_forward(const HtreeShape* shape, int32_t level, int32_t n_level, const void* q, const void* layer_k,
+                             const void* layer_v, const int32_t* prev_parents, const float* cos_cache,
+                             const float* sin_cache, int32_t n_pos, float scale, float* layer_max, float* layer_sum,
+                             float* layer_out, int32_t* next_parents, int32_t* status, void* stream);
+int htree_b200_merge_to_global(const float* layer_max, const float* layer_sum, const float* layer_out, float* global_max,
+                               float* global_sum, float* global_out, int64_t rows, int32_t V, void* stream);
+int htree_b200_final_normalize(const float* global_out, const float* global_sum, void* out, int32_t dtype, int64_t rows,
+                               int32_t V, void* stream);
+
 /* Backward: replaces htree_backward and every kernel it launches (preprocess_delta, dq_bottom/upper,
  * build_parent_mask, dkv_bottom/upper, tree_backward; src/backward.py:45-841, 941-1119).
  *   layers_k_rot  NULL or the K' levels of htree_b200_build_tree: selects the tensor-core kernel where the shape
