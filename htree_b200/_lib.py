@@ -16,6 +16,7 @@ FWD_SELECT_ONLY = 1
 FWD_GENERIC = 2
 FWD_FUSED = 4
 FWD_TILED = 8
+PARENTS_U16 = 16
 
 # every exported symbol of include/htree_b200.h; tests check that the library exports all of them
 SYMBOLS = (

@@ -47,6 +47,10 @@ static int fill_params(AttnParams& p, const HtreeShape* s, int L, const int32_t*
     if (!q || !lk || !lv || !cosc || !sinc) return HTREE_E_NULL;
     if ((int64_t)n_pos < (int64_t)s->top_k * s->compression_rate) return HTREE_E_ROPE;
     if (!aligned16(q) || !aligned16(cosc) || !aligned16(sinc)) return HTREE_E_ALIGN;
+    if ((flags & HTREE_PARENTS_U16) && parents) {   // ids of level l+1 (or of the virtual parents) must fit, 0xFFFF = none
+        if (s->top_k > 65535) return HTREE_E_UNSUPPORTED;
+        for (int l = 1; l < L; ++l) if (ln[l] > 65535) return HTREE_E_UNSUPPORTED;
+    }
     p.q = q;
     int64_t pw = 1;
     for (int l = 0; l < L; ++l) {

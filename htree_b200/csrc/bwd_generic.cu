@@ -100,8 +100,8 @@ __global__ void __launch_bounds__(NTB) bwd_generic_kernel(const __grid_constant_
         float* dkl = p.dk[l];
         float* dvl = p.dv[l];
         for (int i = tid; i < TK; i += NTB) {
-            m.par[i] = p.parents[l][qidx * TK + i];
-            m.nsel[i] = l > 0 ? p.parents[l - 1][qidx * TK + i] : -1;
+            m.par[i] = load_parent(p, l, qidx * TK + i);
+            m.nsel[i] = l > 0 ? load_parent(p, l - 1, qidx * TK + i) : -1;
         }
         __syncthreads();
         int np = 0, nsv = 0;

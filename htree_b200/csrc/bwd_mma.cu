@@ -93,8 +93,8 @@ __global__ void HTREE_BWD_BOUNDS bwd_mma_kernel(const __grid_constant__ AttnPara
         float* dvl = p.dv[l];
         __syncwarp();
         for (int i = lane; i < TK; i += 32) {
-            par[i] = p.parents[l][qidx * TK + i];
-            nsel[i] = l > 0 ? p.parents[l - 1][qidx * TK + i] : -1;
+            par[i] = load_parent(p, l, qidx * TK + i);
+            nsel[i] = l > 0 ? load_parent(p, l - 1, qidx * TK + i) : -1;
             keptw[i] = 0u;
         }
         __syncwarp();

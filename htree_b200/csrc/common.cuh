@@ -111,6 +111,19 @@ __device__ __forceinline__ int block_scan_flag(bool f, int* wtot, int* total) {
 
 void note_launch(int n = 1);   // diagnostic launch counter (api.cu)
 
+// Parent lists: int32 with -1 for "none" (the reference's layout), or uint16 with 0xFFFF under HTREE_PARENTS_U16.
+__device__ __forceinline__ int load_parent(const AttnParams& p, int l, int64_t idx) {
+    if (p.flags & HTREE_PARENTS_U16) {
+        const uint16_t v = reinterpret_cast<const uint16_t*>(p.parents[l])[idx];
+        return v == 0xFFFFu ? -1 : (int)v;
+    }
+    return p.parents[l][idx];
+}
+__device__ __forceinline__ void store_parent(const AttnParams& p, int l, int64_t idx, int v) {
+    if (p.flags & HTREE_PARENTS_U16) reinterpret_cast<uint16_t*>(p.parents[l])[idx] = v < 0 ? (uint16_t)0xFFFFu : (uint16_t)v;
+    else p.parents[l][idx] = v;
+}
+
 // launchers implemented in the .cu files (return cudaError_t as int)
 int launch_tree_build(const HtreeShape& s, int L, const int32_t* ln, void* const* lk, void* const* lv, cudaStream_t st);
 int launch_tree_backward(const HtreeShape& s, int L, const int32_t* ln, float* const* dk, float* const* dv, cudaStream_t st);

@@ -153,7 +153,7 @@ __global__ void __launch_bounds__(NT) fwd_generic_kernel(const __grid_constant__
         const int64_t tslot = p.level_mode ? 0 : l;   // slot of this level in the trace arrays
         const T* lk = reinterpret_cast<const T*>(p.lk[l]);
         const T* lv = reinterpret_cast<const T*>(p.lv[l]);
-        if (p.parents[l]) for (int i = tid; i < TK; i += NT) p.parents[l][qidx * TK + i] = par[i];
+        if (p.parents[l]) for (int i = tid; i < TK; i += NT) store_parent(p, l, qidx * TK + i, par[i]);
         if (select_only && l == 0) break;   // the leaf level selects nothing
         int np = 0;   // parents are a dense prefix followed by -1 padding
         for (int i = tid; i < TK; i += NT) np += par[i] >= 0;

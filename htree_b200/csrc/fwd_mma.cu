@@ -119,10 +119,10 @@ __global__ void __launch_bounds__(MW * 32, MODE == 1 ? HTREE_SEL_MIN_BLOCKS : HT
         const T* lv = reinterpret_cast<const T*>(p.lv[l]);
         if (kAccumulateKernel) {
             __syncwarp();
-            for (int i = lane; i < TK; i += 32) par[i] = p.parents[l][qidx * TK + i];
+            for (int i = lane; i < TK; i += 32) par[i] = load_parent(p, l, qidx * TK + i);
             __syncwarp();
         } else if (p.parents[l]) {
-            for (int i = lane; i < TK; i += 32) p.parents[l][qidx * TK + i] = par[i];
+            for (int i = lane; i < TK; i += 32) store_parent(p, l, qidx * TK + i, par[i]);
         }
         if (select_only && l == 0) break;
         int np = 0;
@@ -208,7 +208,7 @@ __global__ void __launch_bounds__(MW * 32, MODE == 1 ? HTREE_SEL_MIN_BLOCKS : HT
             if (nc > TK) {
                 // kept-candidate bit mask from the two sorted lists: the level's parents and the next level's parents
                 for (int i = lane; i < (nc + 31) / 32; i += 32) selw[i] = 0u;
-                for (int i = lane; i < TK; i += 32) nxt[i] = p.parents[l - 1][qidx * TK + i];
+                for (int i = lane; i < TK; i += 32) nxt[i] = load_parent(p, l - 1, qidx * TK + i);
                 __syncwarp();
                 for (int i = lane; i < TK; i += 32) {
                     const int node = nxt[i];

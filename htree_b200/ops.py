@@ -34,6 +34,34 @@ _DTYPES = {torch.float32: _lib.F32, torch.bfloat16: _lib.BF16, torch.float16: _l
 # in the backward with the selection-only pass like the reference does (False; saves L*B*T*H_kv*top_k*4 bytes).
 SAVE_SELECTIONS_FOR_BACKWARD = True
 
+# Storage of the per-level selections (bwd_ctx["per_layer_parents"]): "int32" is the reference's layout
+# (src/parallel.py:1044, -1 = none); "uint16" halves that memory (torch.int16 tensors holding the unsigned bit
+# pattern, 0xFFFF = none; decode_parents() converts) and needs every pooled level to have at most 65535 nodes.
+SELECTION_STORAGE = "int32"
+
+
+def _parents_dtype(layers_k, top_k: int):
+    if SELECTION_STORAGE == "int32":
+        return torch.int32
+    if SELECTION_STORAGE != "uint16":
+        raise ValueError(f"SELECTION_STORAGE must be 'int32' or 'uint16', not {SELECTION_STORAGE!r}")
+    if top_k > 65535 or any(x.shape[1] > 65535 for x in layers_k[1:]):
+        raise ValueError("SELECTION_STORAGE='uint16' needs pooled levels of at most 65535 nodes")
+    return torch.int16
+
+
+def _parents_flag(parents) -> int:
+    first = parents[0] if parents is not None else None
+    return _lib.PARENTS_U16 if first is not None and first.dtype == torch.int16 else 0
+
+
+def decode_parents(t: torch.Tensor) -> torch.Tensor:
+    """Selections in the reference's layout (int32, -1 = none) from either storage format."""
+    if t.dtype == torch.int32:
+        return t
+    x = t.to(torch.int32) & 0xFFFF
+    return torch.where(x == 0xFFFF, torch.full_like(x, -1), x)
+
 
 @dataclass
 class LayerTrace:
@@ -229,7 +257,8 @@ def htree_forward(
     # the tensor-core forward is faster as selection kernel + accumulation kernel, which hand the selections over in
     # these buffers; so they are allocated there even when the caller does not keep them
     split_forward = layers_kr is not None and not (_force_generic or return_trace or _fused)
-    parents = [torch.empty(B, q.shape[1], H_kv, top_k_per_layer, dtype=torch.int32, device=dev) for _ in range(L)] \
+    pdt = _parents_dtype(layers_k, top_k_per_layer)
+    parents = [torch.empty(B, q.shape[1], H_kv, top_k_per_layer, dtype=pdt, device=dev) for _ in range(L)] \
         if (want_parents or split_forward) else None
     trace = tr = None
     if return_trace:
@@ -240,6 +269,7 @@ def htree_forward(
     flags = _lib.FWD_GENERIC if (_force_generic or return_trace) else (_lib.FWD_FUSED if _fused else 0)
     if _tiled:
         flags |= _lib.FWD_TILED
+    flags |= _parents_flag(parents)
     half_tables = rope_cache_half(K, cos_cache.shape[0], rope_base, scale, dev) if layers_kr is not None else None
     _run_forward(shape, q, layers_k, layers_v, cos_cache, sin_cache, scale, out, gmax, gsum, parents, trace, flags,
                  layers_kr, half_tables)
@@ -261,7 +291,8 @@ def htree_forward(
         ))
     if return_trace:
         check_status(dev)
-        layers = {l: LayerTrace(l, parents[l - 1] if l > 0 else None, tr[0][l], tr[1][l], tr[2][l]) for l in range(L)}
+        layers = {l: LayerTrace(l, decode_parents(parents[l - 1]) if l > 0 else None, tr[0][l], tr[1][l], tr[2][l])
+                  for l in range(L)}
         result.append({"num_layers": L, "num_groups": H // H_kv, "selection_mode": "parallel_importance",
                        "layers": layers})
     return tuple(result)
@@ -275,9 +306,11 @@ def recompute_parents(q, layers_k, layers_v, cos_cache, sin_cache, compression_r
     shape = _lib.HtreeShape(B, T, H, H_kv, K, V, int(compression_rate), int(top_k_per_layer), int(max_top_nodes),
                             _DTYPES[q.dtype])
     L = len(layers_k)
-    parents = [torch.empty(B, T, H_kv, top_k_per_layer, dtype=torch.int32, device=q.device) for _ in range(L)]
+    parents = [torch.empty(B, T, H_kv, top_k_per_layer, dtype=_parents_dtype(layers_k, top_k_per_layer), device=q.device)
+               for _ in range(L)]
     _run_forward(shape, q.contiguous(), layers_k, layers_v, cos_cache, sin_cache, scale, None, None, None, parents,
-                 None, _lib.FWD_SELECT_ONLY | (_lib.FWD_GENERIC if _force_generic else 0), layers_k_rot)
+                 None, _lib.FWD_SELECT_ONLY | (_lib.FWD_GENERIC if _force_generic else 0) | _parents_flag(parents),
+                 layers_k_rot)
     return {l: parents[l] for l in range(L)}
 
 
@@ -313,7 +346,8 @@ def htree_backward(dO: torch.Tensor, q: torch.Tensor, output: torch.Tensor, bwd_
             cos_cache.shape[0], float(scale), output.data_ptr(), dO.data_ptr(),
             bwd_ctx["global_max"].data_ptr(), bwd_ctx["global_sum"].data_ptr(),
             _ptrs([parents[l] for l in range(L)]), dq.data_ptr(), _ptrs(dk_levels), _ptrs(dv_levels),
-            _status(dev).data_ptr(), _lib.FWD_GENERIC if _force_generic else 0, _stream())
+            _status(dev).data_ptr(),
+            (_lib.FWD_GENERIC if _force_generic else 0) | _parents_flag([parents[l] for l in range(L)]), _stream())
     _lib.check(rc, "backward")
     return dq, dk_levels[0], dv_levels[0]
 
@@ -359,7 +393,7 @@ def htree_forward_autograd(q, k, v, compression_rate: int = 16, max_top_nodes: i
 htree_forward_triton_autograd = htree_forward_autograd   # drop-in name of the reference
 
 __all__ = [
-    "HTREE_SCORE_NEG_INF", "HTREE_SCORE_VALID_THRESHOLD", "LayerTrace", "build_tree", "rope_cache",
+    "decode_parents", "HTREE_SCORE_NEG_INF", "HTREE_SCORE_VALID_THRESHOLD", "LayerTrace", "build_tree", "rope_cache",
     "htree_forward", "htree_backward", "recompute_parents", "HTreeFunction", "HTreeTritonFunction",
     "htree_forward_autograd", "htree_forward_triton_autograd", "check_status",
 ]

@@ -49,6 +49,10 @@ extern "C" {
                                     (also honoured by the backward) */
 #define HTREE_FWD_TILED 8u       /* generic forward: use the tiled variant (scores not held for a whole level) even when the
                                     untiled one fits into shared memory; it is chosen automatically when it does not */
+#define HTREE_PARENTS_U16 16u     /* forward and backward: the parent-list buffers hold uint16 node ids (0xFFFF = none) instead of
+                                    int32 (-1 = none): half the saved-selection memory.  Needs every pooled level to have at
+                                    most 65535 nodes (else HTREE_E_UNSUPPORTED).  The reference keeps int32
+                                    (src/parallel.py:1044; docs/backward_derivation.md:355-372 names the cost). */
 #define HTREE_FWD_FUSED 4u       /* tensor-core forward: keep selection and accumulation in ONE kernel even when parent
                                     buffers are provided (default then: a selection kernel followed by an accumulation kernel) */
 

@@ -76,3 +76,26 @@ def test_python_entry_points_refuse_cpu_tensors():
         htree_forward(q, k, v, 4, 8, 2)
     with pytest.raises(ValueError):
         htree_forward(q[0], k, v, 4, 8, 2)
+
+
+def test_compact_selection_storage_host_rules():
+    """uint16 selections: refused when a pooled level has more than 65535 nodes; decoding restores the int32 layout."""
+    import torch
+    from htree_b200 import ops
+    small = [torch.empty(1, 70000, 1, 8), torch.empty(1, 4375, 1, 8)]
+    large = [torch.empty(1, 1, 1, 8).expand(1, 2 ** 21, 1, 8), torch.empty(1, 1, 1, 8).expand(1, 2 ** 17, 1, 8)]   # no memory behind them
+    assert ops._parents_dtype(small, 64) is torch.int32
+    ops.SELECTION_STORAGE = "uint16"
+    try:
+        assert ops._parents_dtype(small, 64) is torch.int16
+        with pytest.raises(ValueError):
+            ops._parents_dtype(large, 64)
+        ops.SELECTION_STORAGE = "int8"
+        with pytest.raises(ValueError):
+            ops._parents_dtype(small, 64)
+    finally:
+        ops.SELECTION_STORAGE = "int32"
+    stored = torch.tensor([0, 5, 40000, 65534, 65535], dtype=torch.int32).to(torch.int16)
+    assert ops.decode_parents(stored).tolist() == [0, 5, 40000, 65534, -1]
+    same = torch.tensor([3, -1], dtype=torch.int32)
+    assert ops.decode_parents(same) is same

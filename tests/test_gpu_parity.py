@@ -149,6 +149,35 @@ def test_selection_only_replay_and_autograd_recompute():
     assert float((grads[0][0].cpu() - torch.from_numpy(g["dq"])).abs().max()) < 1e-4
 
 
+@pytest.mark.parametrize("name", ["f32_T300_cr4_tk8", "bf16_D128_G16_T2048", "bf16_D64_G8_cr8_T2500"])
+def test_compact_selection_storage(name):
+    """uint16 parent lists: same outputs bit for bit, same selections after decoding, same gradients up to the order of
+    the floating-point reductions; through the separate selection pass, the forward and the backward."""
+    ops = _ops()
+    c = CASES[name] if name in CASES else MMA_CASES[name]
+    q, k, v, dO = (x.to(DEV) for x in parity.case_inputs(c))
+    res = {}
+    for fmt in ("int32", "uint16"):
+        ops.ops.SELECTION_STORAGE = fmt
+        try:
+            out, ctx = ops.htree_forward(q, k, v, c["CR"], c["MTN"], c["TK"], _save_for_backward=True)
+            again = ops.recompute_parents(q, ctx["layers_k"], ctx["layers_v"], ctx["cos_cache"], ctx["sin_cache"], c["CR"],
+                                          c["TK"], c["MTN"], ctx["scale"], ctx.get("layers_k_rot"))
+            grads = ops.htree_backward(dO, q, out, ctx)
+            res[fmt] = (out, ctx["per_layer_parents"], again, grads)
+        finally:
+            ops.ops.SELECTION_STORAGE = "int32"
+    (o32, p32, a32, g32), (o16, p16, a16, g16) = res["int32"], res["uint16"]
+    assert torch.equal(o32, o16)
+    for l in p32:
+        assert p32[l].dtype == torch.int32 and p16[l].dtype == torch.int16
+        assert p16[l].numel() * p16[l].element_size() * 2 == p32[l].numel() * p32[l].element_size()
+        assert torch.equal(ops.decode_parents(p16[l]), p32[l])
+        assert torch.equal(ops.decode_parents(a16[l]), a32[l])
+    for a, b in zip(g32, g16):
+        assert torch.allclose(a, b, rtol=1e-4, atol=1e-4 * float(a.abs().max()))
+
+
 def _dense_reference(q, k, v, rope_base=10000.0):
     """Plain PyTorch fp32 causal attention with half-split RoPE at absolute positions, GQA-broadcast."""
     B, T, H, K = q.shape
