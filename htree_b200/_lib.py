@@ -31,6 +31,7 @@ SYMBOLS = (
     "htree_b200_level_forward",
     "htree_b200_merge_to_global",
     "htree_b200_final_normalize",
+    "htree_b200_topk",
     "htree_b200_backward",
     "htree_b200_static_scratch_bytes",
     "htree_b200_backward_static_scratch",
@@ -88,6 +89,8 @@ def lib() -> ctypes.CDLL:
         L.htree_b200_merge_to_global.argtypes = [vp, vp, vp, vp, vp, vp, ctypes.c_int64, i32, vp]
         L.htree_b200_final_normalize.restype = ctypes.c_int
         L.htree_b200_final_normalize.argtypes = [vp, vp, vp, i32, ctypes.c_int64, i32, vp]
+        L.htree_b200_topk.restype = ctypes.c_int
+        L.htree_b200_topk.argtypes = [vp, vp, vp, i32, i32, i32, i32, vp, vp, vp, vp, vp]
         L.htree_b200_backward.restype = ctypes.c_int
         L.htree_b200_backward.argtypes = [ctypes.POINTER(HtreeShape), vp, vp, vp, vp, vp, vp, vp, vp, i32, f32, vp, vp, vp, vp, vp,
                                           vp, vp, vp, vp, u32, vp]

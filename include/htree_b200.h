@@ -152,6 +152,14 @@ int htree_b200_merge_to_global(const float* layer_max, const float* layer_sum, c
 int htree_b200_final_normalize(const float* global_out, const float* global_sum, void* out, int32_t dtype, int64_t rows,
                                int32_t V, void* stream);
 
+/* Selector micro-benchmark (no counterpart on the operator path; the experiment of topk_test/benchmark.py:34-46):
+ * `batch` independent problems, the k largest of n <= 8192 fp32 values each; pay1 [batch,n] and pay8 [batch,n,8] are
+ * optional int32 payloads gathered for the winners.  method 0 = threshold search (the attention kernels' selector),
+ * 1 = radix select, 2 = bitonic (n and k powers of two).  Methods 0 and 1 return the winners by ascending index,
+ * method 2 by descending value; ties go to the smaller index. */
+int htree_b200_topk(const float* values, const int32_t* pay1, const int32_t* pay8, int32_t batch, int32_t n, int32_t k,
+                    int32_t method, float* out_val, int32_t* out_idx, int32_t* out_pay1, int32_t* out_pay8, void* stream);
+
 /* Backward: replaces htree_backward and every kernel it launches (preprocess_delta, dq_bottom/upper,
  * build_parent_mask, dkv_bottom/upper, tree_backward; src/backward.py:45-841, 941-1119).
  *   layers_k_rot  NULL or the K' levels of htree_b200_build_tree: selects the tensor-core kernel where the shape
