@@ -91,6 +91,11 @@ __global__ void HTREE_BWD_BOUNDS bwd_mma_kernel(const __grid_constant__ AttnPara
         const T* lv = reinterpret_cast<const T*>(p.lv[l]);
         float* dkl = p.dk[l];
         float* dvl = p.dv[l];
+        // per-lane bases into this level: only node * rstride is left to add per chunk
+        const int rstride = p.Hkv * D;
+        const __half* kq = lkr + ((int64_t)b * Nl * p.Hkv + hk) * D + (D / 8) * r;
+        const T* vq = lv + ((int64_t)b * Nl * p.Hkv + hk) * D + (D / 8) * r;
+        const int64_t gbase = ((int64_t)b * Nl * p.Hkv + hk) * D + ((g & 1) ? 16 : 0) + 4 * r;
         __syncwarp();
         for (int i = lane; i < TK; i += 32) {
             par[i] = load_parent(p, l, qidx * TK + i);
@@ -128,14 +133,15 @@ __global__ void HTREE_BWD_BOUNDS bwd_mma_kernel(const __grid_constant__ AttnPara
             // ---- dP = dO V^T: value rows in the same (column n = child, permuted contraction) fragment order ----
             float dP0[4] = {0.f, 0.f, 0.f, 0.f}, dP1[4] = {0.f, 0.f, 0.f, 0.f};
             {
-                const int n0 = node0 + g, n1 = node0 + 8 + g;
-                const T* v0 = lv + (((int64_t)b * Nl + n0) * p.Hkv + hk) * D + PPT * r;
-                const T* v1 = lv + (((int64_t)b * Nl + n1) * p.Hkv + hk) * D + PPT * r;
+                // rows beyond the end of the level are read from the last row: their columns are masked below
+                const int n0 = min(node0 + g, Nl - 1), n1 = min(node0 + 8 + g, Nl - 1);
+                const T* v0 = vq + (int64_t)n0 * rstride;
+                const T* v1 = vq + (int64_t)n1 * rstride;
                 uint32_t vb[2][2][KS];
 #pragma unroll
                 for (int hf = 0; hf < 2; ++hf) {
-                    ldg_vec<NV>(v0 + hf * HALF, n0 < Nl, vb[0][hf]);
-                    if (T1) ldg_vec<NV>(v1 + hf * HALF, n1 < Nl, vb[1][hf]);
+                    ldg_vec<NV>(v0 + hf * HALF, true, vb[0][hf]);
+                    if (T1) ldg_vec<NV>(v1 + hf * HALF, true, vb[1][hf]);
                 }
 #pragma unroll
                 for (int ks = 0; ks < KS; ++ks) {
@@ -147,7 +153,7 @@ __global__ void HTREE_BWD_BOUNDS bwd_mma_kernel(const __grid_constant__ AttnPara
             // ---- S, the rotated-query fragments and the keys rotated back into q's frame ----
             float S0[4], S1[4];
             uint32_t qa[KS][4], kr[2][2][KS];
-            score_chunk<D, true, ROT16, true, NR, CR>(p, lkr, Nl, b, hk, node0, delta, g, r, qraw, S0, S1, qa, kr);
+            score_chunk<D, true, ROT16, true, NR, CR>(p, kq, rstride, Nl, node0, delta, g, r, qraw, S0, S1, qa, kr);
 
             // ---- P and dS (src/naive.py:379-382), zero outside the accumulated set ----
             float P[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}}, dS[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
@@ -192,8 +198,8 @@ __global__ void HTREE_BWD_BOUNDS bwd_mma_kernel(const __grid_constant__ AttnPara
             for (int rr = 0; rr < 2; ++rr) {
                 rowa[rr] = (mask >> (ge + 8 * rr) & 1) != 0;          // even row of the pair
                 rowb[rr] = (mask >> (ge + 1 + 8 * rr) & 1) != 0;      // odd row of the pair
-                const int64_t offa = (((int64_t)b * Nl + node0 + ge + 8 * rr) * p.Hkv + hk) * D + (odd ? 16 : 0) + 4 * r;
-                const int64_t offb = offa + (int64_t)p.Hkv * D;
+                const int64_t offa = gbase + (int64_t)(node0 + ge + 8 * rr) * rstride;
+                const int64_t offb = offa + rstride;
                 dka[rr] = dkl + offa; dkb[rr] = dkl + offb;
                 dva[rr] = dvl + offa; dvb[rr] = dvl + offb;
             }

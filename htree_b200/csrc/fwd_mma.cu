@@ -104,7 +104,12 @@ __global__ void __launch_bounds__(MW * 32, MODE == 1 ? HTREE_SEL_MIN_BLOCKS : HT
     float O[NOT][4];
 #pragma unroll
     for (int i = 0; i < NOT; ++i) { O[i][0] = O[i][1] = O[i][2] = O[i][3] = 0.f; }
-    float m_run[2] = {-1.0e30f, -1.0e30f}, s_run[2] = {0.f, 0.f};
+    // Online softmax with a lazily updated reference: probabilities are taken relative to m_run, which is only moved (and
+    // the accumulators rescaled) when a row maximum exceeds it by more than kLazyMax, so exp(s - m_run) <= e^kLazyMax; the
+    // true running maximum is tracked separately for the (gmax, gsum) the backward reads.  With 16 heads sharing a warp
+    // an exact running maximum would move in most chunks and cost 64 multiplies each time.
+    constexpr float kLazyMax = 8.f;
+    float m_run[2] = {-1.0e30f, -1.0e30f}, m_true[2] = {-1.0e30f, -1.0e30f}, s_run[2] = {0.f, 0.f};
 
     {   // virtual parents of the top level (src/parallel.py:1026-1038)
         int np0 = (int)(((int64_t)t / p.lpow[L - 1]) / CR) + 1;
@@ -133,12 +138,16 @@ __global__ void __launch_bounds__(MW * 32, MODE == 1 ? HTREE_SEL_MIN_BLOCKS : HT
 
         // S0/S1 = scores of the 16 children of parent slot `a` against the 16 query rows.  `select` = this pass
         // decides the Top-K: the query is then always rotated in fp32.
+        // per-lane bases into this level: only node * rstride is left to add per chunk
+        const int rstride = p.Hkv * D;
+        const __half* kq = lkr + ((int64_t)b * Nl * p.Hkv + hk) * D + (D / 8) * r;
+        const T* vq = lv + ((int64_t)b * Nl * p.Hkv + hk) * D + 8 * g;
         auto score = [&](int a, float (&S0)[4], float (&S1)[4], bool select) {
             int node0 = par[a] * CR;
             if (node0 < 0 || node0 >= Nl) { if (p.status) atomicOr(p.status, 4); node0 = 0; }
             uint32_t unused[1][4];
-            if (rot16 && !select) score_chunk<D, false, true, false, NR, CR>(p, lkr, Nl, b, hk, node0, rp - CR * a, g, r, qraw, S0, S1, unused);
-            else score_chunk<D, false, false, false, NR, CR>(p, lkr, Nl, b, hk, node0, rp - CR * a, g, r, qraw, S0, S1, unused);
+            if (rot16 && !select) score_chunk<D, false, true, false, NR, CR>(p, kq, rstride, Nl, node0, rp - CR * a, g, r, qraw, S0, S1, unused);
+            else score_chunk<D, false, false, false, NR, CR>(p, kq, rstride, Nl, node0, rp - CR * a, g, r, qraw, S0, S1, unused);
         };
 
         // online-softmax accumulation of the columns in `mask` (bit c = child c of the parent at slot a)
@@ -151,7 +160,7 @@ __global__ void __launch_bounds__(MW * 32, MODE == 1 ? HTREE_SEL_MIN_BLOCKS : HT
             uint4 vr[4][NHH];
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
-                const T* vrow = lv + (((int64_t)b * Nl + node0 + col[c]) * p.Hkv + hk) * D + 8 * g;
+                const T* vrow = vq + (int64_t)(node0 + col[c]) * rstride;
 #pragma unroll
                 for (int hh = 0; hh < NHH; ++hh) {
                     vr[c][hh] = make_uint4(0, 0, 0, 0);
@@ -172,7 +181,8 @@ __global__ void __launch_bounds__(MW * 32, MODE == 1 ? HTREE_SEL_MIN_BLOCKS : HT
                 m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
                 mr[rr] = m;
             }
-            if (__any_sync(0xffffffffu, mr[0] > m_run[0] || mr[1] > m_run[1])) {
+            m_true[0] = fmaxf(m_true[0], mr[0]); m_true[1] = fmaxf(m_true[1], mr[1]);
+            if (__any_sync(0xffffffffu, mr[0] > m_run[0] + kLazyMax || mr[1] > m_run[1] + kLazyMax)) {
                 const float n0 = fmaxf(m_run[0], mr[0]), n1 = fmaxf(m_run[1], mr[1]);
                 const float a0 = __expf(m_run[0] - n0), a1 = __expf(m_run[1] - n1);
                 m_run[0] = n0; m_run[1] = n1;
@@ -356,7 +366,7 @@ __global__ void __launch_bounds__(MW * 32, MODE == 1 ? HTREE_SEL_MIN_BLOCKS : HT
             dst[0] = make_uint4(w0[0], w0[1], w0[2], w0[3]);
             dst[1] = make_uint4(w1[0], w1[1], w1[2], w1[3]);
         }
-        if (r == 0) { p.gmax[hbase + g + 8 * rr] = m_run[rr]; p.gsum[hbase + g + 8 * rr] = s_run[rr]; }
+        if (r == 0) { p.gmax[hbase + g + 8 * rr] = m_true[rr]; p.gsum[hbase + g + 8 * rr] = s_run[rr] * __expf(m_run[rr] - m_true[rr]); }
     }
 }
 

@@ -86,22 +86,25 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
 //   NR = 1 when the group has at most 8 heads: rows g+8 are padding, their rotation is skipped and their A rows are zero.
 //   CR = children per parent (16 or 8).  With 8 the second tile (children 8-15) does not exist: no loads, no MMAs, S1 = 0.
 template <int D, bool KEEP_A, bool ROT16, bool KEEP_K = false, int NR = 2, int CR = 16>
-__device__ __forceinline__ void score_chunk(const AttnParams& p, const __half* lkr, int Nl, int b, int hk, int node0, int delta,
+__device__ __forceinline__ void score_chunk(const AttnParams& p, const __half* kq, int rstride, int Nl, int node0, int delta,
                                             int g, int r, const uint32_t (&qraw)[2][2][D / 16], float (&S0)[4], float (&S1)[4],
                                             uint32_t (&qa)[KEEP_A ? D / 16 : 1][4], uint32_t (*kr)[2][D / 16] = nullptr) {
     constexpr int HALF = D / 2, KS = D / 16, PPT = HALF / 4, NV = PPT / 8;
     constexpr bool T1 = CR > 8;   // does tile 1 exist?
+    constexpr bool POST_SCALE = !KEEP_A && !KEEP_K && !ROT16;
     using FS = Frag<__half>;
     const float* cp = p.cosc + (size_t)delta * HALF + PPT * r;
     const float* sp = p.sinc + (size_t)delta * HALF + PPT * r;
-    const int n0 = node0 + g, n1 = node0 + 8 + g;
-    const __half* k0 = lkr + (((int64_t)b * Nl + n0) * p.Hkv + hk) * D + PPT * r;
-    const __half* k1 = lkr + (((int64_t)b * Nl + n1) * p.Hkv + hk) * D + PPT * r;
+    // kq = this lane's base into the level (row 0, the group's KV head, column PPT*r), rstride = elements per row.
+    // Children beyond the end of the level are read from the last row instead: callers mask those columns.
+    const int n0 = min(node0 + g, Nl - 1), n1 = min(node0 + 8 + g, Nl - 1);
+    const __half* k0 = kq + (int64_t)n0 * rstride;
+    const __half* k1 = kq + (int64_t)n1 * rstride;
     uint32_t kb[2][2][KS];   // [tile][half][k-step]
 #pragma unroll
     for (int hf = 0; hf < 2; ++hf) {
-        ldg_vec<NV>(k0 + hf * HALF, n0 < Nl, kb[0][hf]);
-        if (T1) ldg_vec<NV>(k1 + hf * HALF, n1 < Nl, kb[1][hf]);
+        ldg_vec<NV>(k0 + hf * HALF, true, kb[0][hf]);
+        if (T1) ldg_vec<NV>(k1 + hf * HALF, true, kb[1][hf]);
         else {
 #pragma unroll
             for (int i = 0; i < KS; ++i) kb[1][hf][i] = 0u;
@@ -164,8 +167,10 @@ __device__ __forceinline__ void score_chunk(const AttnParams& p, const __half* l
     for (int ks2 = 0; ks2 < KS; ks2 += 2) {
         const float4 c4 = __ldg(reinterpret_cast<const float4*>(cp + 2 * ks2));
         const float4 s4 = __ldg(reinterpret_cast<const float4*>(sp + 2 * ks2));
-        const float cs[4] = {c4.x * p.scale, c4.y * p.scale, c4.z * p.scale, c4.w * p.scale};
-        const float sn[4] = {s4.x * p.scale, s4.y * p.scale, s4.z * p.scale, s4.w * p.scale};
+        // the softmax scale goes into the tables, or, when only the scores are wanted, onto the 8 scores at the end
+        const float tsc = POST_SCALE ? 1.f : p.scale;
+        const float cs[4] = {c4.x * tsc, c4.y * tsc, c4.z * tsc, c4.w * tsc};
+        const float sn[4] = {s4.x * tsc, s4.y * tsc, s4.z * tsc, s4.w * tsc};
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
             const int ks = ks2 + u;
@@ -199,7 +204,10 @@ __device__ __forceinline__ void score_chunk(const AttnParams& p, const __half* l
         }
     }
 #pragma unroll
-    for (int i = 0; i < 4; ++i) { S0[i] += T0[i]; S1[i] += U1[i]; }
+    for (int i = 0; i < 4; ++i) {
+        S0[i] += T0[i]; S1[i] += U1[i];
+        if (POST_SCALE) { S0[i] *= p.scale; S1[i] *= p.scale; }
+    }
 }
 
 // Raw rows g and g+8 of a [heads, D] block in the fragment order used above (zero for rows beyond the group).
