@@ -11,6 +11,8 @@ void note_launch(int n) { g_launches.fetch_add((unsigned long long)n, std::memor
 
 static int esize(int dtype) { return dtype == HTREE_F32 ? 4 : 2; }
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+// the tensor-core kernels move 32-byte pieces with 256-bit loads
+static bool aligned32(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 31u) == 0; }
 
 static int level_sizes(int T, int CR, int MTN, int32_t* ln) {
     if (T <= 0 || CR < 2 || MTN < 1) return HTREE_E_SHAPE;
@@ -169,16 +171,17 @@ int htree_b200_forward(const HtreeShape* shape, const void* q, void* const* laye
         if (!aligned16(out)) return HTREE_E_ALIGN;
     }
     p.out = out; p.gmax = gmax; p.gsum = gsum;
-    if (cos_half && sin_half && aligned16(cos_half) && aligned16(sin_half)) {
+    if (cos_half && sin_half && aligned32(cos_half) && aligned32(sin_half)) {
         p.cosh = static_cast<const __half*>(cos_half); p.sinh = static_cast<const __half*>(sin_half);
     }
     if (trace) { p.tr_max = trace->layer_max; p.tr_sum = trace->layer_sum; p.tr_out = trace->layer_out; }
     if (layers_k_rot && !trace && !(flags & HTREE_FWD_GENERIC)) {
         bool all = true;
         for (int l = 0; l < L; ++l) {
-            if (!layers_k_rot[l] || !aligned16(layers_k_rot[l])) all = false;
+            if (!layers_k_rot[l] || !aligned32(layers_k_rot[l]) || !aligned32(layers_v[l])) all = false;
             p.lkr[l] = layers_k_rot[l];
         }
+        all = all && aligned32(q) && aligned32(cos_cache) && aligned32(sin_cache);
         if (all && fwd_mma_supported(p, shape->dtype)) return launch_fwd_mma(p, shape->dtype, (cudaStream_t)stream);
     }
     return launch_fwd_generic(p, shape->dtype, (cudaStream_t)stream);
@@ -259,16 +262,17 @@ int htree_b200_backward(const HtreeShape* shape, const void* q, void* const* lay
     }
     p.out = const_cast<void*>(out); p.dO = dO; p.gmax = const_cast<float*>(gmax); p.gsum = const_cast<float*>(gsum);
     p.dq = dq;
-    if (cos_half && sin_half && aligned16(cos_half) && aligned16(sin_half)) {
+    if (cos_half && sin_half && aligned32(cos_half) && aligned32(sin_half)) {
         p.cosh = static_cast<const __half*>(cos_half); p.sinh = static_cast<const __half*>(sin_half);
     }
     bool fast = layers_k_rot != nullptr && !(flags & HTREE_FWD_GENERIC);
     if (fast) {
         for (int l = 0; l < L; ++l) {
-            if (!layers_k_rot[l] || !aligned16(layers_k_rot[l])) fast = false;
+            if (!layers_k_rot[l] || !aligned32(layers_k_rot[l]) || !aligned32(layers_v[l])) fast = false;
             p.lkr[l] = layers_k_rot[l];
         }
-        fast = fast && aligned16(dO) && aligned16(out) && aligned16(dq) && bwd_mma_supported(p, shape->dtype);
+        fast = fast && aligned32(q) && aligned32(dO) && aligned32(out) && aligned16(dq) && aligned32(cos_cache) &&
+               aligned32(sin_cache) && bwd_mma_supported(p, shape->dtype);
     }
     rc = fast ? launch_bwd_mma(p, shape->dtype, st) : launch_bwd_generic(p, shape->dtype, st);
     if (rc) return rc;

@@ -70,7 +70,7 @@ __global__ void __launch_bounds__(MW * 32, MODE == 1 ? HTREE_SEL_MIN_BLOCKS : HT
     constexpr int KS = D / 16;        // k-steps of the score product
     constexpr int PPT = HALF / 4;     // rotation pairs owned by one thread of a quad
     constexpr int NV = PPT / 8;       // 16-byte loads per (row, half): 2 for D=128, 1 for D=64
-    constexpr int NHH = D / 64;       // 64-wide value column groups
+    constexpr int VB = D / 8;         // value columns one thread loads per row: one 32-byte (D=128) or 16-byte (D=64) piece
     constexpr int NOT = D / 8;        // n8 output tiles
     using F = Frag<T>;          // P.V product: values stay in their storage type
     using FS = Frag<__half>;    // score product: rotated queries and K' are IEEE half for every storage type
@@ -141,7 +141,7 @@ __global__ void __launch_bounds__(MW * 32, MODE == 1 ? HTREE_SEL_MIN_BLOCKS : HT
         // per-lane bases into this level: only node * rstride is left to add per chunk
         const int rstride = p.Hkv * D;
         const __half* kq = lkr + ((int64_t)b * Nl * p.Hkv + hk) * D + (D / 8) * r;
-        const T* vq = lv + ((int64_t)b * Nl * p.Hkv + hk) * D + 8 * g;
+        const T* vq = lv + ((int64_t)b * Nl * p.Hkv + hk) * D + VB * g;
         auto score = [&](int a, float (&S0)[4], float (&S1)[4], bool select) {
             int node0 = par[a] * CR;
             if (node0 < 0 || node0 >= Nl) { if (p.status) atomicOr(p.status, 4); node0 = 0; }
@@ -156,17 +156,12 @@ __global__ void __launch_bounds__(MW * 32, MODE == 1 ? HTREE_SEL_MIN_BLOCKS : HT
             if (node0 < 0 || node0 >= Nl) node0 = 0;
             const int col[4] = {2 * r, 2 * r + 1, 8 + 2 * r, 9 + 2 * r};
             const bool cv[4] = {(mask >> col[0] & 1) != 0, (mask >> col[1] & 1) != 0, (mask >> col[2] & 1) != 0, (mask >> col[3] & 1) != 0};
-            // value rows first (longest latency): 16-byte chunk g of every 64-wide column group
-            uint4 vr[4][NHH];
+            // value rows first (longest latency): piece g (VB columns) of the rows of this thread's four candidates, one
+            // load each; 32-byte loads keep the L1 data pipe at a quarter of the cycles that 16-byte loads of the same
+            // bytes take
+            uint32_t vr[4][VB / 2];
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                const T* vrow = vq + (int64_t)(node0 + col[c]) * rstride;
-#pragma unroll
-                for (int hh = 0; hh < NHH; ++hh) {
-                    vr[c][hh] = make_uint4(0, 0, 0, 0);
-                    if (cv[c]) vr[c][hh] = ldg16(vrow + 64 * hh);
-                }
-            }
+            for (int c = 0; c < 4; ++c) ldg_vec<VB / 8>(vq + (int64_t)(node0 + col[c]) * rstride, cv[c], vr[c]);
             const float NINF = -INFINITY;
             float s[2][4];   // [row][tile0 c0, tile0 c1, tile1 c0, tile1 c1]
             s[0][0] = (cv[0] && row_ok[0]) ? S0[0] : NINF; s[0][1] = (cv[1] && row_ok[0]) ? S0[1] : NINF;
@@ -203,15 +198,14 @@ __global__ void __launch_bounds__(MW * 32, MODE == 1 ? HTREE_SEL_MIN_BLOCKS : HT
                 }
             const uint32_t pa0 = F::pack(pr[0][0], pr[0][1]), pa1 = F::pack(pr[1][0], pr[1][1]);
             const uint32_t pa2 = F::pack(pr[0][2], pr[0][3]), pa3 = F::pack(pr[1][2], pr[1][3]);
+            // output tile w, column c <-> value column VB*c + w: the w-th element of every thread's piece
 #pragma unroll
-            for (int hh = 0; hh < NHH; ++hh)
-#pragma unroll
-                for (int w = 0; w < 8; ++w) {
-                    const uint32_t sel = (w & 1) ? 0x7632u : 0x5410u;
-                    const uint32_t b0 = __byte_perm(word(vr[0][hh], w >> 1), word(vr[1][hh], w >> 1), sel);
-                    const uint32_t b1 = __byte_perm(word(vr[2][hh], w >> 1), word(vr[3][hh], w >> 1), sel);
-                    F::mma(O[hh * 8 + w], pa0, pa1, pa2, pa3, b0, b1);
-                }
+            for (int w = 0; w < VB; ++w) {
+                const uint32_t sel = (w & 1) ? 0x7632u : 0x5410u;
+                const uint32_t b0 = __byte_perm(vr[0][w >> 1], vr[1][w >> 1], sel);
+                const uint32_t b1 = __byte_perm(vr[2][w >> 1], vr[3][w >> 1], sel);
+                F::mma(O[w], pa0, pa1, pa2, pa3, b0, b1);
+            }
         };
 
         if (l > 0 && kAccumulateKernel) {
@@ -353,18 +347,18 @@ __global__ void __launch_bounds__(MW * 32, MODE == 1 ? HTREE_SEL_MIN_BLOCKS : HT
         if (!row_ok[rr]) continue;
         const float inv = 1.f / s_run[rr];
         T* orow = reinterpret_cast<T*>(p.out) + (hbase + g + 8 * rr) * D;
+        // this thread owns columns 2*VB*r + [0, VB) (element 2rr of tiles 0..VB-1) and the VB after them (element 2rr+1)
+        uint32_t wlo[VB / 2], whi[VB / 2];
 #pragma unroll
-        for (int hh = 0; hh < NHH; ++hh) {
-            // this thread owns columns 64*hh + 16*r + [0,16): c0 of tiles w=0..7, then c1 of tiles w=0..7
-            uint32_t w0[4], w1[4];
+        for (int i = 0; i < VB / 2; ++i) {
+            wlo[i] = F::pack(O[2 * i][2 * rr] * inv, O[2 * i + 1][2 * rr] * inv);
+            whi[i] = F::pack(O[2 * i][2 * rr + 1] * inv, O[2 * i + 1][2 * rr + 1] * inv);
+        }
+        uint4* dst = reinterpret_cast<uint4*>(orow + 2 * VB * r);
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                w0[i] = F::pack(O[hh * 8 + 2 * i][2 * rr] * inv, O[hh * 8 + 2 * i + 1][2 * rr] * inv);
-                w1[i] = F::pack(O[hh * 8 + 2 * i][2 * rr + 1] * inv, O[hh * 8 + 2 * i + 1][2 * rr + 1] * inv);
-            }
-            uint4* dst = reinterpret_cast<uint4*>(orow + 64 * hh + 16 * r);
-            dst[0] = make_uint4(w0[0], w0[1], w0[2], w0[3]);
-            dst[1] = make_uint4(w1[0], w1[1], w1[2], w1[3]);
+        for (int i = 0; i < VB / 8; ++i) {
+            dst[i] = make_uint4(wlo[4 * i], wlo[4 * i + 1], wlo[4 * i + 2], wlo[4 * i + 3]);
+            dst[VB / 8 + i] = make_uint4(whi[4 * i], whi[4 * i + 1], whi[4 * i + 2], whi[4 * i + 3]);
         }
         if (r == 0) { p.gmax[hbase + g + 8 * rr] = m_true[rr]; p.gsum[hbase + g + 8 * rr] = s_run[rr] * __expf(m_run[rr] - m_true[rr]); }
     }
