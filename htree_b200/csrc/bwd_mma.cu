@@ -93,6 +93,7 @@ __global__ void HTREE_BWD_BOUNDS bwd_mma_kernel(const __grid_constant__ AttnPara
         float* dvl = p.dv[l];
         // per-lane bases into this level: only node * rstride is left to add per chunk
         const int rstride = p.Hkv * D;
+        constexpr bool stream_rows = true;   // gathered rows are used once: not allocated in L1
         const __half* kq = lkr + ((int64_t)b * Nl * p.Hkv + hk) * D + (D / 8) * r;
         const T* vq = lv + ((int64_t)b * Nl * p.Hkv + hk) * D + (D / 8) * r;
         const int64_t gbase = ((int64_t)b * Nl * p.Hkv + hk) * D + ((g & 1) ? 16 : 0) + 4 * r;
@@ -140,8 +141,8 @@ __global__ void HTREE_BWD_BOUNDS bwd_mma_kernel(const __grid_constant__ AttnPara
                 uint32_t vb[2][2][KS];
 #pragma unroll
                 for (int hf = 0; hf < 2; ++hf) {
-                    ldg_vec<NV>(v0 + hf * HALF, true, vb[0][hf]);
-                    if (T1) ldg_vec<NV>(v1 + hf * HALF, true, vb[1][hf]);
+                    ldg_vec<NV>(v0 + hf * HALF, true, vb[0][hf], stream_rows);
+                    if (T1) ldg_vec<NV>(v1 + hf * HALF, true, vb[1][hf], stream_rows);
                 }
 #pragma unroll
                 for (int ks = 0; ks < KS; ++ks) {
@@ -153,7 +154,7 @@ __global__ void HTREE_BWD_BOUNDS bwd_mma_kernel(const __grid_constant__ AttnPara
             // ---- S, the rotated-query fragments and the keys rotated back into q's frame ----
             float S0[4], S1[4];
             uint32_t qa[KS][4], kr[2][2][KS];
-            score_chunk<D, true, ROT16, true, NR, CR>(p, kq, rstride, Nl, node0, delta, g, r, qraw, S0, S1, qa, kr);
+            score_chunk<D, true, ROT16, true, NR, CR>(p, kq, rstride, Nl, node0, delta, g, r, qraw, S0, S1, qa, kr, stream_rows);
 
             // ---- P and dS (src/naive.py:379-382), zero outside the accumulated set ----
             float P[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}}, dS[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};

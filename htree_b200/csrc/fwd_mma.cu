@@ -140,14 +140,17 @@ __global__ void __launch_bounds__(MW * 32, MODE == 1 ? HTREE_SEL_MIN_BLOCKS : HT
         // decides the Top-K: the query is then always rotated in fp32.
         // per-lane bases into this level: only node * rstride is left to add per chunk
         const int rstride = p.Hkv * D;
+        // a gathered row is used once and is not allocated in L1; the selection kernel, where the top level is a larger
+        // share of the rows, keeps that level (shared by neighbouring queries, small enough to live in L1) cached
+        const bool stream_rows = kSelectKernel ? l < L - 1 : true;
         const __half* kq = lkr + ((int64_t)b * Nl * p.Hkv + hk) * D + (D / 8) * r;
         const T* vq = lv + ((int64_t)b * Nl * p.Hkv + hk) * D + VB * g;
         auto score = [&](int a, float (&S0)[4], float (&S1)[4], bool select) {
             int node0 = par[a] * CR;
             if (node0 < 0 || node0 >= Nl) { if (p.status) atomicOr(p.status, 4); node0 = 0; }
             uint32_t unused[1][4];
-            if (rot16 && !select) score_chunk<D, false, true, false, NR, CR>(p, kq, rstride, Nl, node0, rp - CR * a, g, r, qraw, S0, S1, unused);
-            else score_chunk<D, false, false, false, NR, CR>(p, kq, rstride, Nl, node0, rp - CR * a, g, r, qraw, S0, S1, unused);
+            if (rot16 && !select) score_chunk<D, false, true, false, NR, CR>(p, kq, rstride, Nl, node0, rp - CR * a, g, r, qraw, S0, S1, unused, nullptr, stream_rows);
+            else score_chunk<D, false, false, false, NR, CR>(p, kq, rstride, Nl, node0, rp - CR * a, g, r, qraw, S0, S1, unused, nullptr, stream_rows);
         };
 
         // online-softmax accumulation of the columns in `mask` (bit c = child c of the parent at slot a)
@@ -161,7 +164,7 @@ __global__ void __launch_bounds__(MW * 32, MODE == 1 ? HTREE_SEL_MIN_BLOCKS : HT
             // bytes take
             uint32_t vr[4][VB / 2];
 #pragma unroll
-            for (int c = 0; c < 4; ++c) ldg_vec<VB / 8>(vq + (int64_t)(node0 + col[c]) * rstride, cv[c], vr[c]);
+            for (int c = 0; c < 4; ++c) ldg_vec<VB / 8>(vq + (int64_t)(node0 + col[c]) * rstride, cv[c], vr[c], stream_rows);
             const float NINF = -INFINITY;
             float s[2][4];   // [row][tile0 c0, tile0 c1, tile1 c0, tile1 c1]
             s[0][0] = (cv[0] && row_ok[0]) ? S0[0] : NINF; s[0][1] = (cv[1] && row_ok[0]) ? S0[1] : NINF;

@@ -46,17 +46,38 @@ __device__ __forceinline__ void ldg32(const void* p, uint32_t (&o)[8]) {
                  : "=r"(o[0]), "=r"(o[1]), "=r"(o[2]), "=r"(o[3]), "=r"(o[4]), "=r"(o[5]), "=r"(o[6]), "=r"(o[7])
                  : "l"(p));
 }
-// n16 consecutive 16-byte pieces (n16 = 1 or 2) into o[0 .. 4*n16), using one 256-bit load when n16 == 2
+// The same for gathered rows that are used once: not allocated in L1.  A row that misses L1 otherwise crosses the L1
+// data pipe twice (fill, then read), and that pipe is the busiest unit of the attention kernels.
+__device__ __forceinline__ void ldg32_stream(const void* p, uint32_t (&o)[8]) {
+#ifdef HTREE_LDG_ALLOC
+    ldg32(p, o);
+#else
+    asm volatile("ld.global.nc.L1::no_allocate.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];\n"
+                 : "=r"(o[0]), "=r"(o[1]), "=r"(o[2]), "=r"(o[3]), "=r"(o[4]), "=r"(o[5]), "=r"(o[6]), "=r"(o[7])
+                 : "l"(p));
+#endif
+}
+__device__ __forceinline__ uint4 ldg16_stream(const void* p) {
+#ifdef HTREE_LDG_ALLOC
+    return ldg16(p);
+#else
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.b32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+#endif
+}
+// n16 consecutive 16-byte pieces (n16 = 1 or 2) into o[0 .. 4*n16), using one 256-bit load when n16 == 2.
+// STREAM: the data is a gathered row (see ldg32_stream).
 template <int N16>
-__device__ __forceinline__ void ldg_vec(const void* p, bool on, uint32_t* o) {
+__device__ __forceinline__ void ldg_vec(const void* p, bool on, uint32_t* o, bool stream = false) {
     if (N16 == 2) {
         uint32_t t[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        if (on) ldg32(p, t);
+        if (on) { if (stream) ldg32_stream(p, t); else ldg32(p, t); }
 #pragma unroll
         for (int i = 0; i < 8; ++i) o[i] = t[i];
     } else {
         uint4 x = make_uint4(0, 0, 0, 0);
-        if (on) x = ldg16(p);
+        if (on) x = stream ? ldg16_stream(p) : ldg16(p);
         o[0] = x.x; o[1] = x.y; o[2] = x.z; o[3] = x.w;
     }
 }
@@ -88,7 +109,7 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
 template <int D, bool KEEP_A, bool ROT16, bool KEEP_K = false, int NR = 2, int CR = 16>
 __device__ __forceinline__ void score_chunk(const AttnParams& p, const __half* kq, int rstride, int Nl, int node0, int delta,
                                             int g, int r, const uint32_t (&qraw)[2][2][D / 16], float (&S0)[4], float (&S1)[4],
-                                            uint32_t (&qa)[KEEP_A ? D / 16 : 1][4], uint32_t (*kr)[2][D / 16] = nullptr) {
+                                            uint32_t (&qa)[KEEP_A ? D / 16 : 1][4], uint32_t (*kr)[2][D / 16] = nullptr, bool stream = true) {
     constexpr int HALF = D / 2, KS = D / 16, PPT = HALF / 4, NV = PPT / 8;
     constexpr bool T1 = CR > 8;   // does tile 1 exist?
     constexpr bool POST_SCALE = !KEEP_A && !KEEP_K && !ROT16;
@@ -103,8 +124,8 @@ __device__ __forceinline__ void score_chunk(const AttnParams& p, const __half* k
     uint32_t kb[2][2][KS];   // [tile][half][k-step]
 #pragma unroll
     for (int hf = 0; hf < 2; ++hf) {
-        ldg_vec<NV>(k0 + hf * HALF, true, kb[0][hf]);
-        if (T1) ldg_vec<NV>(k1 + hf * HALF, true, kb[1][hf]);
+        ldg_vec<NV>(k0 + hf * HALF, true, kb[0][hf], stream);
+        if (T1) ldg_vec<NV>(k1 + hf * HALF, true, kb[1][hf], stream);
         else {
 #pragma unroll
             for (int i = 0; i < KS; ++i) kb[1][hf][i] = 0u;
