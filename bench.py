@@ -101,6 +101,24 @@ class ClockSampler:
 
 # --------------------------------------------------------------------------------------------- CPU oracle leg
 
+def measure_limits(device) -> dict:
+    """Ceilings of the two on-chip memory paths the attention kernels live on, measured live with the kernels' own access
+    patterns (htree_b200_probe_gather / _probe_reduction): random 256-byte rows read from, and fp32 reductions into
+    random 512-byte rows of, a 64 MiB buffer (L2-resident)."""
+    import ctypes
+    from htree_b200 import _lib
+    buf = torch.zeros(64 << 20, dtype=torch.uint8, device=device)
+    out = {}
+    val = ctypes.c_float()
+    st = torch.cuda.current_stream().cuda_stream
+    _lib.check(_lib.lib().htree_b200_probe_gather(buf.data_ptr(), buf.numel(), 5, ctypes.byref(val), st), "probe_gather")
+    out["l2_gather_gbs"] = float(val.value)
+    _lib.check(_lib.lib().htree_b200_probe_reduction(buf.data_ptr(), buf.numel(), 5, ctypes.byref(val), st), "probe_reduction")
+    out["l2_reduction_gbs"] = float(val.value)
+    del buf
+    return out
+
+
 def cpu_oracle_leg(c: dict, seconds: float, steps: int = 1, warmup: int = 0):
     """Time the CPU oracle (port of the reference's naive path) forward(+backward) on a bounded sample of the workload:
     groups (t, kv head 0, batch 0) with t uniform over the sequence, all host threads.  Returns (tokens/s, info)."""
@@ -381,6 +399,15 @@ def main():
                 "backward_tflops": (cm["flops_bwd"] / world / (bwd_ms * 1e-3) / 1e12) if bwd else None,
                 "forward_requested_gather_gbs": cm["gather_bytes_fwd"] / world / (fwd_ms * 1e-3) / 1e9,
                 "forward_compulsory_hbm_frac": cm["bytes_fwd"] / world / (fwd_ms * 1e-3) / 1e9 / pk["hbm_gbs"]}
+    # what actually bounds the two attention kernels: gathered rows per second (forward) and bytes of fp32 reductions
+    # into the dK/dV level buffers per second (backward: 2 * D floats per accumulated row), against ceilings measured now
+    limits = measure_limits(dev)
+    limits["forward_gather_gbs"] = roofline["forward_requested_gather_gbs"]
+    limits["forward_gather_frac"] = limits["forward_gather_gbs"] / limits["l2_gather_gbs"]
+    if bwd:
+        red_bytes = cm["accumulated_rows"] * 2 * D * 4 / world
+        limits["backward_reduction_gbs"] = red_bytes / (bwd_ms * 1e-3) / 1e9
+        limits["backward_reduction_frac"] = limits["backward_reduction_gbs"] / limits["l2_reduction_gbs"]
     es = 4 if c["dtype"] == "float32" else 2
     lv_sizes = cm["levels"]
     n_rows = B * Hkv if seq_mode else U
@@ -395,7 +422,7 @@ def main():
             "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16" if c["dtype"] == "bfloat16" else c["dtype"],
             "data": "synthetic", "config": cfg_desc,
-            "fwd_tokens_per_s": B * T / (fwd_ms * 1e-3), "roofline": roofline, "streaming": streaming, "e2e": e2e,
+            "fwd_tokens_per_s": B * T / (fwd_ms * 1e-3), "roofline": roofline, "limits": limits, "streaming": streaming, "e2e": e2e,
             "gpu_launches": int(launches), "clocks": clocks}
     if not args.no_cpu_baseline and world == 1:
         tps, info = cpu_oracle_leg(c, args.cpu_seconds)

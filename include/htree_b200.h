@@ -152,6 +152,14 @@ int htree_b200_merge_to_global(const float* layer_max, const float* layer_sum, c
 int htree_b200_final_normalize(const float* global_out, const float* global_sum, void* out, int32_t dtype, int64_t rows,
                                int32_t V, void* stream);
 
+/* Measured ceilings of the two memory paths the attention kernels depend on (measurement aids, no reference counterpart).
+ * gather: GB/s of random 256-byte rows read from `table` (table_bytes, 32-byte aligned) with the kernels' 32-byte loads;
+ * reduction: GB/s of fp32 red.global.add.v4 into random 512-byte rows of `buffer` (its contents are overwritten).
+ * A buffer well below the L2 size measures the L2 path, a much larger one the HBM path.  Both calls time `reps` launches
+ * with CUDA events on `stream` and wait for them. */
+int htree_b200_probe_gather(void* table, int64_t table_bytes, int32_t reps, float* gbs, void* stream);
+int htree_b200_probe_reduction(float* buffer, int64_t buffer_bytes, int32_t reps, float* gbs, void* stream);
+
 /* Selector micro-benchmark (no counterpart on the operator path; the experiment of topk_test/benchmark.py:34-46):
  * `batch` independent problems, the k largest of n <= 8192 fp32 values each; pay1 [batch,n] and pay8 [batch,n,8] are
  * optional int32 payloads gathered for the winners.  method 0 = threshold search (the attention kernels' selector),
