@@ -340,7 +340,7 @@ def main():
         del outs
 
         from htree_b200 import host as hhost
-        e2e_chunk = 1                   # units resident per pipeline stage (two stages in flight); small head/tail
+        e2e_chunk = "unit"              # one (batch, KV head) unit per pipeline stage (two in flight): small head/tail
 
         def e2e_step():
             if seq_mode:      # a single long sequence cannot be cut along the batch: plain copies around the call
@@ -371,8 +371,8 @@ def main():
         e2e = {"value": B * T / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": n_e2e,
                "api": ("htree_forward_sequence_parallel with pinned host tensors copied in and out around the call" if seq_mode
-                       else "htree_b200.host.forward_backward_host: pinned host tensors in and out, batch chunks "
-                            "pipelined over three streams (H2D | kernels | D2H)")}
+                       else "htree_b200.host.forward_backward_host: pinned host tensors in and out, (batch, KV head) "
+                            "units pipelined over three streams (H2D | kernels | D2H)")}
         del host_in, host_out
 
     if rank != 0:

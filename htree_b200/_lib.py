@@ -32,6 +32,7 @@ SYMBOLS = (
     "htree_b200_merge_to_global",
     "htree_b200_final_normalize",
     "htree_b200_topk",
+    "htree_b200_copy_rows",
     "htree_b200_probe_gather",
     "htree_b200_probe_reduction",
     "htree_b200_backward",
@@ -95,6 +96,8 @@ def lib() -> ctypes.CDLL:
         L.htree_b200_probe_gather.argtypes = [vp, ctypes.c_int64, i32, ctypes.POINTER(ctypes.c_float), vp]
         L.htree_b200_probe_reduction.restype = ctypes.c_int
         L.htree_b200_probe_reduction.argtypes = [vp, ctypes.c_int64, i32, ctypes.POINTER(ctypes.c_float), vp]
+        L.htree_b200_copy_rows.restype = ctypes.c_int
+        L.htree_b200_copy_rows.argtypes = [vp, ctypes.c_int64, vp, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, vp]
         L.htree_b200_topk.restype = ctypes.c_int
         L.htree_b200_topk.argtypes = [vp, vp, vp, i32, i32, i32, i32, vp, vp, vp, vp, vp]
         L.htree_b200_backward.restype = ctypes.c_int

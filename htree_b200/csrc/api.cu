@@ -234,6 +234,14 @@ int htree_b200_final_normalize(const float* global_out, const float* global_sum,
     return launch_final_normalize(global_out, global_sum, out, dtype, rows, V, (cudaStream_t)stream);
 }
 
+int htree_b200_copy_rows(void* dst, int64_t dpitch, const void* src, int64_t spitch, int64_t width, int64_t height,
+                         void* stream) {
+    if (!dst || !src) return HTREE_E_NULL;
+    if (width <= 0 || height <= 0 || dpitch < width || spitch < width) return HTREE_E_SHAPE;
+    return (int)cudaMemcpy2DAsync(dst, (size_t)dpitch, src, (size_t)spitch, (size_t)width, (size_t)height, cudaMemcpyDefault,
+                                  (cudaStream_t)stream);
+}
+
 int htree_b200_backward(const HtreeShape* shape, const void* q, void* const* layers_k, void* const* layers_v,
                         void* const* layers_k_rot, const float* cos_cache, const float* sin_cache, const void* cos_half,
                         const void* sin_half, int32_t n_pos, float scale, const void* out,

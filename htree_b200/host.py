@@ -10,7 +10,7 @@ from typing import Optional, Tuple
 
 import torch
 
-from . import ops
+from . import _lib, ops
 
 
 _stream_cache = {}
@@ -25,6 +25,18 @@ def _streams(dev):
     return _stream_cache[key]
 
 
+def _copy_unit(dst: torch.Tensor, src: torch.Tensor, stream) -> None:
+    """dst <- src for two views of shape [1, T, heads, D] whose rows (one position: heads * D elements) are contiguous;
+    either side may be a slice of a larger [B, T, H, D] tensor (rows a fixed pitch apart) in pinned host memory."""
+    assert dst.shape == src.shape and dst.dtype == src.dtype
+    T, es = dst.shape[1], dst.element_size()
+    width = dst.shape[2] * dst.shape[3] * es
+    for x in (dst, src):
+        assert x.stride(3) == 1 and x.stride(2) == x.shape[3], "rows must be contiguous"
+    _lib.check(_lib.lib().htree_b200_copy_rows(dst.data_ptr(), dst.stride(1) * es, src.data_ptr(), src.stride(1) * es, width, T,
+                                               stream.cuda_stream), "copy_rows")
+
+
 def forward_backward_host(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, dO: Optional[torch.Tensor],
                           compression_rate: int = 16, max_top_nodes: int = 8192, top_k_per_layer: int = 512,
                           scale: Optional[float] = None, rope_base: float = 10000.0, chunk: int = 1,
@@ -33,7 +45,9 @@ def forward_backward_host(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, dO:
 
     Returns host tensors (out,) or (out, dq, dk, dv) in the input dtype; pass `outputs` (pinned, same shapes) to reuse
     buffers.  `chunk` batch elements are resident on the device at a time (two chunks in flight).  The call returns
-    after everything has arrived in host memory."""
+    after everything has arrived in host memory.  chunk="unit" moves and computes one (batch, KV head) unit at a time
+    (strided copies of that head group's slices): the units are independent too, and the smaller the piece the less of
+    the first upload and the last download is left outside the overlap."""
     dev = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
     B = q.shape[0]
     bwd = dO is not None
@@ -47,6 +61,9 @@ def forward_backward_host(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, dO:
         outs = list(outputs)
     s_in, s_run, s_out = _streams(dev)
     s_in.wait_stream(torch.cuda.current_stream(dev))
+    if chunk == "unit":
+        return _by_units(q, k, v, dO, outs, dev, (s_in, s_run, s_out), compression_rate, max_top_nodes, top_k_per_layer, scale,
+                         rope_base)
     keep = []                      # device tensors stay referenced until the final synchronisation
     prev_done = None               # compute of the previous chunk (its inputs may be overwritten two chunks later)
     for b0 in range(0, B, chunk):
@@ -76,5 +93,52 @@ def forward_backward_host(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, dO:
         if len(keep) > 2:
             keep.pop(0)
         prev_done = done
+    s_out.synchronize(); s_run.synchronize(); s_in.synchronize()
+    return tuple(outs)
+
+
+def _by_units(q, k, v, dO, outs, dev, streams, compression_rate, max_top_nodes, top_k_per_layer, scale, rope_base):
+    """One (batch, KV head) unit at a time: q/dO/out/dq slices [1,T,G,D] and k/v/dk/dv slices [1,T,1,D]."""
+    s_in, s_run, s_out = streams
+    B, T, H, K = q.shape
+    H_kv, V = k.shape[2], v.shape[-1]
+    G = H // H_kv
+    bwd = dO is not None
+    if scale is None:
+        scale = K ** -0.5
+    keep = []
+    with torch.cuda.device(dev):
+        for b in range(B):
+            for hk in range(H_kv):
+                hs = slice(hk * G, (hk + 1) * G)
+                srcs = [q[b:b + 1, :, hs], k[b:b + 1, :, hk:hk + 1], v[b:b + 1, :, hk:hk + 1]] + ([dO[b:b + 1, :, hs]] if bwd else [])
+                with torch.cuda.stream(s_in):
+                    dev_in = [torch.empty(x.shape, dtype=x.dtype, device=dev) for x in srcs]
+                    for d, x in zip(dev_in, srcs):
+                        _copy_unit(d, x, s_in)
+                    ready = torch.cuda.Event(); ready.record(s_in)
+                with torch.cuda.stream(s_run):
+                    s_run.wait_event(ready)
+                    if bwd:
+                        o, ctx = ops.htree_forward(dev_in[0], dev_in[1], dev_in[2], compression_rate, max_top_nodes,
+                                                   top_k_per_layer, scale, rope_base, _save_for_backward=True)
+                        dq, dk, dv = ops.htree_backward(dev_in[3], dev_in[0], o, ctx)
+                        res = [o, dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype)]
+                        del ctx
+                    else:
+                        res = [ops.htree_forward(dev_in[0], dev_in[1], dev_in[2], compression_rate, max_top_nodes,
+                                                 top_k_per_layer, scale, rope_base)]
+                    done = torch.cuda.Event(); done.record(s_run)
+                dsts = [outs[0][b:b + 1, :, hs]] + ([outs[1][b:b + 1, :, hs], outs[2][b:b + 1, :, hk:hk + 1],
+                                                     outs[3][b:b + 1, :, hk:hk + 1]] if bwd else [])
+                with torch.cuda.stream(s_out):
+                    s_out.wait_event(done)
+                    for h, r in zip(dsts, res):
+                        _copy_unit(h, r, s_out)
+                for t in dev_in + res:
+                    t.record_stream(s_run); t.record_stream(s_out)
+                keep.append((dev_in, res))
+                if len(keep) > 2:
+                    keep.pop(0)
     s_out.synchronize(); s_run.synchronize(); s_in.synchronize()
     return tuple(outs)

@@ -152,6 +152,12 @@ int htree_b200_merge_to_global(const float* layer_max, const float* layer_sum, c
 int htree_b200_final_normalize(const float* global_out, const float* global_sum, void* out, int32_t dtype, int64_t rows,
                                int32_t V, void* stream);
 
+/* Strided copy for callers whose tensors live in host memory (no reference counterpart): `height` rows of `width` bytes,
+ * consecutive rows dpitch / spitch bytes apart, direction inferred from the pointers (pinned host memory for an
+ * asynchronous copy).  htree_b200.host uses it to move one (batch, KV head) unit of q, k, v, dO and of the results. */
+int htree_b200_copy_rows(void* dst, int64_t dpitch, const void* src, int64_t spitch, int64_t width, int64_t height,
+                         void* stream);
+
 /* Measured ceilings of the two memory paths the attention kernels depend on (measurement aids, no reference counterpart).
  * gather: GB/s of random 256-byte rows read from `table` (table_bytes, 32-byte aligned) with the kernels' 32-byte loads;
  * reduction: GB/s of fp32 red.global.add.v4 into random 512-byte rows of `buffer` (its contents are overwritten).

@@ -402,6 +402,23 @@ def test_host_buffer_pipeline_matches_device_calls():
     assert torch.equal(o2, out.cpu())
 
 
+def test_host_buffer_pipeline_by_units():
+    """chunk="unit": one (batch, KV head) unit at a time through strided copies; same results as the device calls."""
+    ops = _ops()
+    from htree_b200 import host
+    c = dict(B=2, T=1500, H=16, H_kv=4, K=128, V=128, CR=16, TK=16, MTN=64, dtype="bfloat16", seed=62)
+    q, k, v, dO = parity.case_inputs(c)
+    hq, hk, hv, hd = (x.pin_memory() for x in (q, k, v, dO))
+    out_h, dq_h, dk_h, dv_h = host.forward_backward_host(hq, hk, hv, hd, c["CR"], c["MTN"], c["TK"], chunk="unit")
+    out, ctx = ops.htree_forward(q.to(DEV), k.to(DEV), v.to(DEV), c["CR"], c["MTN"], c["TK"], _save_for_backward=True)
+    dq, dk, dv = ops.htree_backward(dO.to(DEV), q.to(DEV), out, ctx)
+    assert torch.equal(out_h, out.cpu())
+    for a, b in ((dq_h, dq), (dk_h, dk), (dv_h, dv)):
+        assert torch.allclose(a.float(), b.to(torch.bfloat16).float().cpu(), rtol=2e-2, atol=2e-3)   # reduction order
+    (o2,) = host.forward_backward_host(hq, hk, hv, None, c["CR"], c["MTN"], c["TK"], chunk="unit")
+    assert torch.equal(o2, out.cpu())
+
+
 @pytest.mark.parametrize("c", [
     # group of 32 heads per KV head: outside the tensor-core kernel (<= 16), generic kernel processes heads in chunks
     dict(B=1, T=600, H=32, H_kv=1, K=64, V=64, CR=16, TK=8, MTN=40, dtype="bfloat16", seed=71),
