@@ -243,7 +243,9 @@ __global__ void __launch_bounds__(NT) fwd_generic_kernel(const __grid_constant__
                 uint32_t tau = 0;   // becomes the TK-th largest key
                 for (int bit = 30; bit >= 0; --bit) {
                     const uint32_t cand = tau | (1u << bit);
-                    if (count_ge(m.key, nc, cand, m.cnt, slot) >= TK) tau = cand;
+                    const int c_ge = count_ge(m.key, nc, cand, m.cnt, slot);
+                    if (c_ge >= TK) tau = cand;
+                    if (c_ge == TK) break;   // the kept set is decided: lower bits cannot change it (uniform across the block)
                 }
                 const int c_gt = tau == 0xffffffffu ? 0 : count_ge(m.key, nc, tau + 1u, m.cnt, slot);
                 const int need = TK - c_gt;   // keys equal to tau that are kept: the `need` smallest positions

@@ -287,15 +287,34 @@ __global__ void __launch_bounds__(MW * 32, MODE == 1 ? HTREE_SEL_MIN_BLOCKS : HT
                 // ---- exact Top-K: bitwise search for the TK-th largest key (keys are non-negative floats) ----
                 const uint32_t* key = reinterpret_cast<const uint32_t*>(imp);
                 uint32_t tau = 0;
-                for (int bit = 30; bit >= 0; --bit) {
-                    const uint32_t cand = tau | (1u << bit);
-                    int c = 0;
-                    for (int j = lane; j < nc; j += 32) c += key[j] >= cand;
-                    c = __reduce_add_sync(0xffffffffu, c);
-                    if (c >= TK) tau = cand;
-                }
                 int c_gt = 0;
-                for (int j = lane; j < nc; j += 32) c_gt += key[j] > tau;
+                if (maxc <= 1024) {
+                    // at most 32 keys per lane: they stay in registers for the whole search (padding 0 is below every threshold)
+                    uint32_t kreg[32];
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) { const int j = lane + 32 * i; kreg[i] = j < nc ? key[j] : 0u; }
+                    for (int bit = 30; bit >= 0; --bit) {
+                        const uint32_t cand = tau | (1u << bit);
+                        int c = 0;
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) c += kreg[i] >= cand;
+                        c = __reduce_add_sync(0xffffffffu, c);
+                        if (c >= TK) tau = cand;
+                        if (c == TK) break;   // exactly TK keys reach this threshold: the kept set is decided, lower bits cannot change it
+                    }
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) c_gt += kreg[i] > tau;
+                } else {
+                    for (int bit = 30; bit >= 0; --bit) {
+                        const uint32_t cand = tau | (1u << bit);
+                        int c = 0;
+                        for (int j = lane; j < nc; j += 32) c += key[j] >= cand;
+                        c = __reduce_add_sync(0xffffffffu, c);
+                        if (c >= TK) tau = cand;
+                        if (c == TK) break;
+                    }
+                    for (int j = lane; j < nc; j += 32) c_gt += key[j] > tau;
+                }
                 c_gt = __reduce_add_sync(0xffffffffu, c_gt);
                 const int need = TK - c_gt;     // keys equal to tau that are kept: the smallest positions
                 int base_eq = 0, base_out = 0;

@@ -96,7 +96,9 @@ __global__ void __launch_bounds__(TKN) topk_threshold_kernel(const TopkArgs a) {
         const uint32_t cand = thr | (1u << bit);
         int c = 0;
         for (int j = threadIdx.x; j < a.n; j += TKN) c += key[j] >= cand;
-        if (block_sum(c, red) >= a.k) thr = cand;
+        const int n_ge = block_sum(c, red);
+        if (n_ge >= a.k) thr = cand;
+        if (n_ge == a.k) break;   // the winner set is decided: lower bits cannot change it
     }
     int c = 0;
     for (int j = threadIdx.x; j < a.n; j += TKN) c += key[j] > thr;
