@@ -20,7 +20,8 @@
 //    significand keeps the score noise 8x below bf16's and with it the rate of Top-K near-tie swaps.
 //  * Fragments are loaded so that no data movement is needed: the contraction index of the score product is
 //    permuted (thread r of a quad owns rotation pairs [P*r, P*(r+1)) of both halves), applied consistently to A and
-//    B; the value rows are loaded as 16-byte chunks and byte-permuted into k-major B fragments.
+//    B; the value rows are loaded as one 32-byte (D = 128) or 16-byte (D = 64) piece per row and thread and byte-permuted
+//    into k-major B fragments.  Gathered rows are used once and are not allocated in L1.
 //  * Upper levels run two passes over the candidates: pass 1 scores and stores only the shared importance
 //    (4 bytes per candidate in shared memory), an exact Top-K (bitwise search for the K-th largest key, ties to the
 //    smaller position, right-most forced) picks the kept set, pass 2 re-scores and accumulates the others.

@@ -81,7 +81,6 @@ __device__ __forceinline__ void ldg_vec(const void* p, bool on, uint32_t* o, boo
         o[0] = x.x; o[1] = x.y; o[2] = x.z; o[3] = x.w;
     }
 }
-__device__ __forceinline__ uint32_t word(const uint4& v, int i) { return i == 0 ? v.x : (i == 1 ? v.y : (i == 2 ? v.z : v.w)); }
 
 __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
     uint32_t d;
