@@ -94,7 +94,7 @@ __global__ void HTREE_BWD_BOUNDS bwd_mma_kernel(const __grid_constant__ AttnPara
         // per-lane bases into this level: only node * rstride is left to add per chunk
         const int rstride = p.Hkv * D;
         constexpr bool stream_rows = true;   // gathered rows are used once: not allocated in L1
-        const __half* kq = lkr + ((int64_t)b * Nl * p.Hkv + hk) * D + (D / 8) * r;
+        const __half* kq = lkr + ((int64_t)b * Nl * p.Hkv + hk) * D + (D == 64 ? D / 4 : D / 8) * r;
         const T* vq = lv + ((int64_t)b * Nl * p.Hkv + hk) * D + (D / 8) * r;
         const int64_t gbase = ((int64_t)b * Nl * p.Hkv + hk) * D + ((g & 1) ? 16 : 0) + 4 * r;
         __syncwarp();

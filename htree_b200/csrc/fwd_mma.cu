@@ -144,7 +144,7 @@ __global__ void __launch_bounds__(MW * 32, MODE == 1 ? HTREE_SEL_MIN_BLOCKS : HT
         // a gathered row is used once and is not allocated in L1; the selection kernel, where the top level is a larger
         // share of the rows, keeps that level (shared by neighbouring queries, small enough to live in L1) cached
         const bool stream_rows = kSelectKernel ? l < L - 1 : true;
-        const __half* kq = lkr + ((int64_t)b * Nl * p.Hkv + hk) * D + (D / 8) * r;
+        const __half* kq = lkr + ((int64_t)b * Nl * p.Hkv + hk) * D + (D == 64 ? D / 4 : D / 8) * r;
         const T* vq = lv + ((int64_t)b * Nl * p.Hkv + hk) * D + VB * g;
         auto score = [&](int a, float (&S0)[4], float (&S1)[4], bool select) {
             int node0 = par[a] * CR;

@@ -115,19 +115,29 @@ __device__ __forceinline__ void score_chunk(const AttnParams& p, const __half* k
     using FS = Frag<__half>;
     const float* cp = p.cosc + (size_t)delta * HALF + PPT * r;
     const float* sp = p.sinc + (size_t)delta * HALF + PPT * r;
-    // kq = this lane's base into the level (row 0, the group's KV head, column PPT*r), rstride = elements per row.
+    // kq = this lane's base into the level (row 0, the group's KV head, column PPT*r; 2*PPT*r for 64-wide rows),
+    // rstride = elements per row.
     // Children beyond the end of the level are read from the last row instead: callers mask those columns.
     const int n0 = min(node0 + g, Nl - 1), n1 = min(node0 + 8 + g, Nl - 1);
     const __half* k0 = kq + (int64_t)n0 * rstride;
     const __half* k1 = kq + (int64_t)n1 * rstride;
     uint32_t kb[2][2][KS];   // [tile][half][k-step]
+    if (D == 64) {
+        // 64-wide rows keep this thread's low and high 8 pairs side by side (rotate_keys_kernel): one 32-byte load per row
+        uint32_t t0[8], t1[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+        ldg_vec<2>(k0, true, t0, stream);
+        if (T1) ldg_vec<2>(k1, true, t1, stream);
 #pragma unroll
-    for (int hf = 0; hf < 2; ++hf) {
-        ldg_vec<NV>(k0 + hf * HALF, true, kb[0][hf], stream);
-        if (T1) ldg_vec<NV>(k1 + hf * HALF, true, kb[1][hf], stream);
-        else {
+        for (int i = 0; i < KS; ++i) { kb[0][0][i] = t0[i]; kb[0][1][i] = t0[4 + i]; kb[1][0][i] = t1[i]; kb[1][1][i] = t1[4 + i]; }
+    } else {
 #pragma unroll
-            for (int i = 0; i < KS; ++i) kb[1][hf][i] = 0u;
+        for (int hf = 0; hf < 2; ++hf) {
+            ldg_vec<NV>(k0 + hf * HALF, true, kb[0][hf], stream);
+            if (T1) ldg_vec<NV>(k1 + hf * HALF, true, kb[1][hf], stream);
+            else {
+#pragma unroll
+                for (int i = 0; i < KS; ++i) kb[1][hf][i] = 0u;
+            }
         }
     }
     S0[0] = S0[1] = S0[2] = S0[3] = 0.f;

@@ -172,8 +172,16 @@ __global__ void __launch_bounds__(256) rotate_keys_kernel(const __grid_constant_
         olo[i] = fminf(fmaxf(lo[i] * cs[i] - hi[i] * sn[i], -65504.f), 65504.f);
         ohi[i] = fminf(fmaxf(lo[i] * sn[i] + hi[i] * cs[i], -65504.f), 65504.f);
     }
-    *reinterpret_cast<uint4*>(dst) = pack16<__half>(olo);
-    *reinterpret_cast<uint4*>(dst + half) = pack16<__half>(ohi);
+    if (a.K == 64) {
+        // 64-wide rows: the low and the high 8 pairs that one thread of the tensor-core kernels owns are stored side by
+        // side (chunk ch at [16 ch, 16 ch + 16)), so that it fetches both with a single 32-byte load
+        __half* row0 = reinterpret_cast<__half*>(a.dst) + row * a.K;
+        *reinterpret_cast<uint4*>(row0 + 16 * ch) = pack16<__half>(olo);
+        *reinterpret_cast<uint4*>(row0 + 16 * ch + 8) = pack16<__half>(ohi);
+    } else {
+        *reinterpret_cast<uint4*>(dst) = pack16<__half>(olo);
+        *reinterpret_cast<uint4*>(dst + half) = pack16<__half>(ohi);
+    }
 }
 
 int launch_rotate_keys(const HtreeShape& s, int L, const int32_t* ln, void* const* lk, void* const* lkr, const float* cosc,

@@ -99,7 +99,8 @@ int htree_b200_level_sizes(int32_t T, int32_t compression_rate, int32_t max_top_
  *   layers_k_rot  NULL, or L pointers to buffers shaped like layers_k (level 0 included) that receive
  *                 K'[node] = R(node % compression_rate) K[node], the keys rotated by their child index with the
  *                 half-split RoPE of src/parallel.py:687-692, stored as IEEE half for bf16 and fp16 inputs alike
- *                 (clamped to the finite half range).  The tensor-core forward reads K' (16-bit storage
+ *                 (clamped to the finite half range).  The column order inside a K' row is private to the library
+ *                 (rows of 64 columns interleave 8-column pieces of the two halves).  The tensor-core forward reads K' (16-bit storage
  *                 types only; needs cos_cache/sin_cache with at least compression_rate rows, and K % 16 == 0).
  *                 Pass NULL for fp32 or when only the generic kernels are wanted. */
 int htree_b200_build_tree(const HtreeShape* shape, void* const* layers_k, void* const* layers_v,

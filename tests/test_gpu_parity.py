@@ -328,7 +328,10 @@ def test_prerotated_keys_match_direct_rotation():
         c = np.arange(x.shape[1]) % 16
         lo, hi = x[..., :32], x[..., 32:]
         co, si = cs[c][None, :, None, :], sn[c][None, :, None, :]
-        want = oracle.round_storage(np.concatenate([lo * co - hi * si, lo * si + hi * co], -1), "float16")
+        rlo, rhi = lo * co - hi * si, lo * si + hi * co
+        # 64-wide rows are stored with the low and the high 8 pairs of each of the four 8-pair chunks side by side
+        want = oracle.round_storage(np.concatenate([np.concatenate([rlo[..., 8 * ch:8 * ch + 8], rhi[..., 8 * ch:8 * ch + 8]], -1)
+                                                    for ch in range(4)], -1), "float16")
         assert b.dtype == torch.float16
         assert np.abs(parity.f32(b) - want).max() <= 4e-3      # at most one half ulp from contraction differences
         assert (parity.f32(b) != want).mean() < 0.02
