@@ -65,7 +65,6 @@ def forward_backward_host(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, dO:
         return _by_units(q, k, v, dO, outs, dev, (s_in, s_run, s_out), compression_rate, max_top_nodes, top_k_per_layer, scale,
                          rope_base)
     keep = []                      # device tensors stay referenced until the final synchronisation
-    prev_done = None               # compute of the previous chunk (its inputs may be overwritten two chunks later)
     for b0 in range(0, B, chunk):
         b1 = min(B, b0 + chunk)
         with torch.cuda.stream(s_in):
@@ -92,7 +91,6 @@ def forward_backward_host(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, dO:
         keep.append((dev_in, res))
         if len(keep) > 2:
             keep.pop(0)
-        prev_done = done
     s_out.synchronize(); s_run.synchronize(); s_in.synchronize()
     return tuple(outs)
 

@@ -99,3 +99,27 @@ def test_compact_selection_storage_host_rules():
     assert ops.decode_parents(stored).tolist() == [0, 5, 40000, 65534, -1]
     same = torch.tensor([3, -1], dtype=torch.int32)
     assert ops.decode_parents(same) is same
+
+
+def test_per_kernel_shims_check_their_arguments_without_a_gpu():
+    """htree_b200.compat: level index from layer_power, and CPU tensors are refused before anything is launched."""
+    import torch
+    from htree_b200 import compat
+    assert compat._level_of(1, 16) == 0 and compat._level_of(256, 16) == 2 and compat._level_of(8, 8) == 1
+    with pytest.raises(ValueError):
+        compat._level_of(24, 16)
+    x = torch.zeros(1, 16, 1, 8)
+    with pytest.raises(RuntimeError):
+        compat.htree_build_kernel[(1, 1)](x, x, x[:, :4], x[:, :4], N_child=16, N_parent=4, B=1, H_kv=1, K=8, V=8,
+                                          COMPRESSION_RATE=4, BLOCK_SIZE=8)
+    with pytest.raises(RuntimeError):
+        compat.htree_merge_to_global_kernel[(16, 1)](x[..., 0], x[..., 0], x, x[..., 0], x[..., 0], x, B=1, T=16, H=1, V=8)
+    assert "htree_select_accumulate_gqa_kernel" in repr(compat.htree_select_accumulate_gqa_kernel)
+
+
+def test_topk_runner_refuses_cpu_tensors():
+    import torch
+    from htree_b200 import topk_bench
+    with pytest.raises(ValueError):
+        topk_bench.topk(torch.zeros(2, 64), 8)
+    assert set(topk_bench.METHODS) == {"threshold_search", "radix_select", "bitonic"}
