@@ -110,29 +110,39 @@ def _by_units(q, k, v, dO, outs, dev, streams, compression_rate, max_top_nodes, 
             for hk in range(H_kv):
                 hs = slice(hk * G, (hk + 1) * G)
                 srcs = [q[b:b + 1, :, hs], k[b:b + 1, :, hk:hk + 1], v[b:b + 1, :, hk:hk + 1]] + ([dO[b:b + 1, :, hs]] if bwd else [])
+                dsts = [outs[0][b:b + 1, :, hs]] + ([outs[1][b:b + 1, :, hs], outs[2][b:b + 1, :, hk:hk + 1],
+                                                     outs[3][b:b + 1, :, hk:hk + 1]] if bwd else [])
+                # the forward starts as soon as q, k, v are there (dO follows), and its output leaves while the backward runs
                 with torch.cuda.stream(s_in):
                     dev_in = [torch.empty(x.shape, dtype=x.dtype, device=dev) for x in srcs]
-                    for d, x in zip(dev_in, srcs):
+                    for d, x in zip(dev_in[:3], srcs[:3]):
                         _copy_unit(d, x, s_in)
                     ready = torch.cuda.Event(); ready.record(s_in)
+                    if bwd:
+                        _copy_unit(dev_in[3], srcs[3], s_in)
+                        ready_bwd = torch.cuda.Event(); ready_bwd.record(s_in)
                 with torch.cuda.stream(s_run):
                     s_run.wait_event(ready)
                     if bwd:
                         o, ctx = ops.htree_forward(dev_in[0], dev_in[1], dev_in[2], compression_rate, max_top_nodes,
                                                    top_k_per_layer, scale, rope_base, _save_for_backward=True)
+                        fwd_done = torch.cuda.Event(); fwd_done.record(s_run)
+                        s_run.wait_event(ready_bwd)
                         dq, dk, dv = ops.htree_backward(dev_in[3], dev_in[0], o, ctx)
                         res = [o, dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype)]
                         del ctx
                     else:
                         res = [ops.htree_forward(dev_in[0], dev_in[1], dev_in[2], compression_rate, max_top_nodes,
                                                  top_k_per_layer, scale, rope_base)]
+                        fwd_done = torch.cuda.Event(); fwd_done.record(s_run)
                     done = torch.cuda.Event(); done.record(s_run)
-                dsts = [outs[0][b:b + 1, :, hs]] + ([outs[1][b:b + 1, :, hs], outs[2][b:b + 1, :, hk:hk + 1],
-                                                     outs[3][b:b + 1, :, hk:hk + 1]] if bwd else [])
                 with torch.cuda.stream(s_out):
-                    s_out.wait_event(done)
-                    for h, r in zip(dsts, res):
-                        _copy_unit(h, r, s_out)
+                    s_out.wait_event(fwd_done)
+                    _copy_unit(dsts[0], res[0], s_out)
+                    if bwd:
+                        s_out.wait_event(done)
+                        for h, r in zip(dsts[1:], res[1:]):
+                            _copy_unit(h, r, s_out)
                 for t in dev_in + res:
                     t.record_stream(s_run); t.record_stream(s_out)
                 keep.append((dev_in, res))
