@@ -405,6 +405,36 @@ def test_host_buffer_pipeline_matches_device_calls():
     assert torch.equal(o2, out.cpu())
 
 
+def test_operands_aligned_to_16_but_not_32_bytes_take_the_generic_kernels():
+    """The tensor-core kernels move 32-byte pieces; tensors that start on an odd multiple of 16 bytes (views into a larger
+    allocation) must be routed to the fp32-arithmetic kernels instead, with the same results up to their arithmetic."""
+    ops = _ops()
+    c = dict(B=1, T=1200, H=16, H_kv=1, K=128, V=128, CR=16, TK=16, MTN=64, dtype="bfloat16", seed=63)
+    q, k, v, dO = (x.to(DEV) for x in parity.case_inputs(c))
+
+    def shifted(x):   # same values, storage offset of 8 elements = 16 bytes
+        buf = torch.empty(x.numel() + 8, dtype=x.dtype, device=x.device)
+        y = buf[8:].view(x.shape)
+        y.copy_(x)
+        assert y.data_ptr() % 32 == 16 and y.is_contiguous()
+        return y
+
+    out_a, ctx_a = ops.htree_forward(q, k, v, c["CR"], c["MTN"], c["TK"], _save_for_backward=True)
+    ga = ops.htree_backward(dO, q, out_a, ctx_a)
+    for which in ("q", "v"):
+        q2, v2 = (shifted(q) if which == "q" else q), (shifted(v) if which == "v" else v)
+        out_b, ctx_b = ops.htree_forward(q2, k, v2, c["CR"], c["MTN"], c["TK"], _save_for_backward=True)
+        gb = ops.htree_backward(dO, q2, out_b, ctx_b)
+        torch.cuda.synchronize()
+        ops.check_status()
+        same = (ctx_a["per_layer_parents"][0] == ctx_b["per_layer_parents"][0]).all(dim=-1)
+        assert same.float().mean() > 0.97
+        rows = same[0, :, 0]
+        assert float((out_a.float() - out_b.float())[0, rows].abs().max()) <= 2e-2
+        for a, b in zip(ga, gb):   # a few rows select differently between the two arithmetic paths: compare in the norm
+            assert float((a - b).norm() / a.norm()) <= 5e-2
+
+
 def test_host_buffer_pipeline_by_units():
     """chunk="unit": one (batch, KV head) unit at a time through strided copies; same results as the device calls."""
     ops = _ops()
