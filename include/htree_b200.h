@@ -118,8 +118,9 @@ int htree_b200_rotate_keys(const HtreeShape* shape, void* const* layers_k, void*
  * HTREE_FWD_SELECT_ONLY — htree_recompute_selection_kernel / _recompute_parents (src/parallel.py:1167-1399,
  * src/backward.py:881-934).
  *   layers_k_rot  NULL or the K' levels written by htree_b200_build_tree; when present (and the shape qualifies:
- *                 bf16/fp16, K == V in {64,128}, H/H_kv <= 16, compression_rate 16 or 8) the tensor-core kernel runs,
- *                 otherwise the generic fp32-arithmetic kernel
+ *                 bf16/fp16, K == V in {64,128}, H/H_kv <= 16, compression_rate 16 or 8, and q, every level of
+ *                 layers_v and layers_k_rot and the tables 32-byte aligned; the backward also wants out and dO so)
+ *                 the tensor-core kernel runs, otherwise the generic fp32-arithmetic kernel (16-byte alignment)
  *   cos_cache, sin_cache  [n_pos, K/2] fp32 RoPE tables (src/parallel.py:983-988); n_pos >= top_k*compression_rate
  *   cos_half, sin_half    NULL, or [n_pos, K/2] IEEE half tables holding cos*scale and sin*scale: the tensor-core
  *                         kernels then rotate queries with packed half arithmetic where that does not touch the
