@@ -27,14 +27,13 @@ SYMBOLS = (
     "htree_b200_level_sizes",
     "htree_b200_build_tree",
     "htree_b200_rotate_keys",
+    "htree_b200_block_values",
     "htree_b200_forward",
     "htree_b200_level_forward",
     "htree_b200_merge_to_global",
     "htree_b200_final_normalize",
     "htree_b200_topk",
     "htree_b200_copy_rows",
-    "htree_b200_probe_gather",
-    "htree_b200_probe_reduction",
     "htree_b200_backward",
     "htree_b200_static_scratch_bytes",
     "htree_b200_backward_static_scratch",
@@ -45,6 +44,10 @@ class HtreeShape(ctypes.Structure):
     _fields_ = [(n, ctypes.c_int32) for n in
                 ("B", "T", "H", "H_kv", "K", "V", "compression_rate", "top_k", "max_top_nodes", "dtype", "T_q",
                  "t_offset")]
+
+
+class HtreeTypedGrads(ctypes.Structure):
+    _fields_ = [("dq", ctypes.c_void_p), ("dk", ctypes.c_void_p), ("dv", ctypes.c_void_p)]
 
 
 class HtreeTrace(ctypes.Structure):
@@ -79,11 +82,13 @@ def lib() -> ctypes.CDLL:
         L.htree_b200_level_sizes.restype = ctypes.c_int
         L.htree_b200_level_sizes.argtypes = [i32, i32, i32, ctypes.POINTER(i32), i32]
         L.htree_b200_build_tree.restype = ctypes.c_int
-        L.htree_b200_build_tree.argtypes = [ctypes.POINTER(HtreeShape), vp, vp, vp, vp, vp, vp]
+        L.htree_b200_build_tree.argtypes = [ctypes.POINTER(HtreeShape), vp, vp, vp, vp, vp, vp, vp]
         L.htree_b200_rotate_keys.restype = ctypes.c_int
         L.htree_b200_rotate_keys.argtypes = [ctypes.POINTER(HtreeShape), vp, vp, vp, vp, vp]
+        L.htree_b200_block_values.restype = ctypes.c_int
+        L.htree_b200_block_values.argtypes = [ctypes.POINTER(HtreeShape), vp, vp, vp]
         L.htree_b200_forward.restype = ctypes.c_int
-        L.htree_b200_forward.argtypes = [ctypes.POINTER(HtreeShape), vp, vp, vp, vp, vp, vp, vp, vp, i32, f32, vp, vp, vp, vp,
+        L.htree_b200_forward.argtypes = [ctypes.POINTER(HtreeShape), vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, f32, vp, vp, vp, vp,
                                          ctypes.POINTER(HtreeTrace), vp, u32, vp]
         L.htree_b200_level_forward.restype = ctypes.c_int
         L.htree_b200_level_forward.argtypes = [ctypes.POINTER(HtreeShape), i32, i32, vp, vp, vp, vp, vp, vp, i32, f32, vp, vp, vp, vp,
@@ -92,17 +97,13 @@ def lib() -> ctypes.CDLL:
         L.htree_b200_merge_to_global.argtypes = [vp, vp, vp, vp, vp, vp, ctypes.c_int64, i32, vp]
         L.htree_b200_final_normalize.restype = ctypes.c_int
         L.htree_b200_final_normalize.argtypes = [vp, vp, vp, i32, ctypes.c_int64, i32, vp]
-        L.htree_b200_probe_gather.restype = ctypes.c_int
-        L.htree_b200_probe_gather.argtypes = [vp, ctypes.c_int64, i32, ctypes.POINTER(ctypes.c_float), vp]
-        L.htree_b200_probe_reduction.restype = ctypes.c_int
-        L.htree_b200_probe_reduction.argtypes = [vp, ctypes.c_int64, i32, ctypes.POINTER(ctypes.c_float), vp]
         L.htree_b200_copy_rows.restype = ctypes.c_int
         L.htree_b200_copy_rows.argtypes = [vp, ctypes.c_int64, vp, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, vp]
         L.htree_b200_topk.restype = ctypes.c_int
         L.htree_b200_topk.argtypes = [vp, vp, vp, i32, i32, i32, i32, vp, vp, vp, vp, vp]
         L.htree_b200_backward.restype = ctypes.c_int
         L.htree_b200_backward.argtypes = [ctypes.POINTER(HtreeShape), vp, vp, vp, vp, vp, vp, vp, vp, i32, f32, vp, vp, vp, vp, vp,
-                                          vp, vp, vp, vp, u32, vp]
+                                          vp, vp, vp, ctypes.POINTER(HtreeTypedGrads), vp, u32, vp]
         L.htree_b200_static_scratch_bytes.restype = ctypes.c_size_t
         L.htree_b200_backward_static_scratch.restype = ctypes.c_int
         L.htree_b200_backward_static_scratch.argtypes = [ctypes.POINTER(HtreeShape), vp, vp, vp, vp, vp, vp, vp, vp, i32, f32, vp,

@@ -15,6 +15,7 @@ from concurrent.futures import ThreadPoolExecutor
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libhtree_b200.so")
+PROBES_LIB = os.path.join(HERE, "libhtree_b200_probes.so")    # measurement aids of the benchmark (csrc/bench/), not the operator
 OBJ_DIR = os.path.join(HERE, "build")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr", "-Xptxas", "-v"]
@@ -69,7 +70,20 @@ def build(force: bool = False, verbose: bool = False, defines=(), out: str = LIB
         r = subprocess.run([nvcc, *ARCH, "-shared", "-o", LIB_, *objs, "-lcudart"], capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
+    if out == LIB:
+        build_probes(force)
     return LIB_
+
+
+def build_probes(force: bool = False) -> str:
+    """The benchmark's ceiling probes (csrc/bench/probes.cu) as a shared library of their own."""
+    src = os.path.join(CSRC, "bench", "probes.cu")
+    deps = [src, os.path.join(CSRC, "mma_common.cuh"), os.path.join(CSRC, "common.cuh")]
+    if force or _stale(PROBES_LIB, deps):
+        r = subprocess.run([_nvcc(), *ARCH, *FLAGS, "-shared", "-o", PROBES_LIB, src, "-lcudart"], capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"nvcc failed on {src}:\n{r.stdout}\n{r.stderr}")
+    return PROBES_LIB
 
 
 if __name__ == "__main__":

@@ -16,8 +16,31 @@ CONFIGS: Dict[str, dict] = {
     "cfg2": dict(B=1, T=32768, H=32, H_kv=2, D=128, dtype="bfloat16", CR=16, MTN=128, TK=64, mode="fwd"),
     "cfg3": dict(B=4, T=65536, H=64, H_kv=4, D=128, dtype="bfloat16", CR=16, MTN=256, TK=64, mode="fwd+bwd"),
     "cfg4": dict(B=1, T=524288, H=32, H_kv=4, D=128, dtype="bfloat16", CR=16, MTN=512, TK=64, mode="fwd"),
-    "cfg5": dict(B=2, T=16384, H=16, H_kv=2, D=64, dtype="bfloat16", CR=8, MTN=64, TK=64, mode="fwd+bwd"),
+    "cfg5": dict(B=2, T=16384, H=16, H_kv=2, D=64, dtype="bfloat16", CR=8, MTN=64, TK=64, mode="fwd+bwd", keys="clustered"),
+    "cfg5_f32": dict(B=2, T=16384, H=16, H_kv=2, D=64, dtype="float32", CR=8, MTN=64, TK=64, mode="fwd+bwd", keys="clustered"),
 }
+
+
+def make_inputs(c: dict, device, seed: int = 42, want_dO: bool = True):
+    """Seeded synthetic q, k, v (and dO) of a workload on `device`, in the operator's layouts [B,T,H,D] / [B,T,H_kv,D].
+    All N(0,1) like the reference's benchmarks (speed_test.py:66-69); with keys="clustered" (the near-tie stress
+    workload) the keys are N(0,1) plus a rank-4 component shared by all positions with N(0, std 3) coefficients."""
+    import torch
+    tdt = {"float32": torch.float32, "bfloat16": torch.bfloat16, "float16": torch.float16}[c["dtype"]]
+    g = torch.Generator(device=device).manual_seed(seed)
+    B, T, H, Hkv, D = c["B"], c["T"], c["H"], c["H_kv"], c["D"]
+
+    def randn(*shape):
+        return torch.randn(*shape, generator=g, device=device, dtype=torch.float32)
+
+    q = randn(B, T, H, D).to(tdt)
+    k = randn(B, T, Hkv, D)
+    if c.get("keys") == "clustered":
+        k = k + (3.0 * randn(B, T, Hkv, 4)) @ randn(4, D)
+    k = k.to(tdt)
+    v = randn(B, T, Hkv, D).to(tdt)
+    dO = randn(B, T, H, D).to(tdt) if want_dO else None
+    return q, k, v, dO
 
 
 def describe(c: dict) -> str:

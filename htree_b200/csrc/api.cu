@@ -113,7 +113,8 @@ int htree_b200_level_sizes(int32_t T, int32_t CR, int32_t MTN, int32_t* sizes, i
 }
 
 int htree_b200_build_tree(const HtreeShape* shape, void* const* layers_k, void* const* layers_v,
-                          void* const* layers_k_rot, const float* cos_cache, const float* sin_cache, void* stream) {
+                          void* const* layers_k_rot, void* const* layers_v_blk, const float* cos_cache,
+                          const float* sin_cache, void* stream) {
     int32_t ln[HTREE_MAX_LEVELS];
     const int L = check_shape(shape, ln, false);   // top_k plays no role in the tree
     if (L < 0) return L;
@@ -132,10 +133,36 @@ int htree_b200_build_tree(const HtreeShape* shape, void* const* layers_k, void* 
             if (!aligned16(layers_k_rot[l])) return HTREE_E_ALIGN;
         }
     }
+    if (layers_v_blk) {
+        if (shape->dtype == HTREE_F32 || (shape->V != 64 && shape->V != 128) ||
+            (shape->compression_rate != 8 && shape->compression_rate != 16))
+            return HTREE_E_UNSUPPORTED;
+        for (int l = 0; l < L; ++l) {
+            if (!layers_v_blk[l]) return HTREE_E_NULL;
+            if (!aligned32(layers_v_blk[l])) return HTREE_E_ALIGN;
+        }
+    }
     int rc = launch_tree_build(*shape, L, ln, layers_k, layers_v, (cudaStream_t)stream);
     if (rc == 0 && layers_k_rot)
         rc = launch_rotate_keys(*shape, L, ln, layers_k, layers_k_rot, cos_cache, sin_cache, (cudaStream_t)stream);
+    if (rc == 0 && layers_v_blk)
+        rc = launch_block_values(*shape, L, ln, layers_v, layers_v_blk, (cudaStream_t)stream);
     return rc;
+}
+
+int htree_b200_block_values(const HtreeShape* shape, void* const* layers_v, void* const* layers_v_blk, void* stream) {
+    int32_t ln[HTREE_MAX_LEVELS];
+    const int L = check_shape(shape, ln, false);
+    if (L < 0) return L;
+    if (!layers_v || !layers_v_blk) return HTREE_E_NULL;
+    if (shape->dtype == HTREE_F32 || (shape->V != 64 && shape->V != 128) ||
+        (shape->compression_rate != 8 && shape->compression_rate != 16))
+        return HTREE_E_UNSUPPORTED;
+    for (int l = 0; l < L; ++l) {
+        if (!layers_v[l] || !layers_v_blk[l]) return HTREE_E_NULL;
+        if (!aligned16(layers_v[l]) || !aligned32(layers_v_blk[l])) return HTREE_E_ALIGN;
+    }
+    return launch_block_values(*shape, L, ln, layers_v, layers_v_blk, (cudaStream_t)stream);
 }
 
 int htree_b200_rotate_keys(const HtreeShape* shape, void* const* layers_k, void* const* layers_k_rot,
@@ -153,7 +180,7 @@ int htree_b200_rotate_keys(const HtreeShape* shape, void* const* layers_k, void*
 }
 
 int htree_b200_forward(const HtreeShape* shape, const void* q, void* const* layers_k, void* const* layers_v,
-                       void* const* layers_k_rot, const float* cos_cache, const float* sin_cache, const void* cos_half,
+                       void* const* layers_k_rot, void* const* layers_v_blk, const float* cos_cache, const float* sin_cache, const void* cos_half,
                        const void* sin_half, int32_t n_pos, float scale, void* out,
                        float* gmax, float* gsum, int32_t* const* parents, const HtreeTrace* trace, int32_t* status,
                        uint32_t flags, void* stream) {
@@ -178,8 +205,12 @@ int htree_b200_forward(const HtreeShape* shape, const void* q, void* const* laye
     if (layers_k_rot && !trace && !(flags & HTREE_FWD_GENERIC)) {
         bool all = true;
         for (int l = 0; l < L; ++l) {
-            if (!layers_k_rot[l] || !aligned32(layers_k_rot[l]) || !aligned32(layers_v[l])) all = false;
+            if (!layers_k_rot[l] || !aligned32(layers_k_rot[l])) all = false;
             p.lkr[l] = layers_k_rot[l];
+            if (!select_only) {   // the accumulating passes read the blocked values
+                if (!layers_v_blk || !layers_v_blk[l] || !aligned32(layers_v_blk[l])) all = false;
+                else p.lvb[l] = layers_v_blk[l];
+            }
         }
         all = all && aligned32(q) && aligned32(cos_cache) && aligned32(sin_cache);
         if (all && fwd_mma_supported(p, shape->dtype)) return launch_fwd_mma(p, shape->dtype, (cudaStream_t)stream);
@@ -246,12 +277,18 @@ int htree_b200_backward(const HtreeShape* shape, const void* q, void* const* lay
                         void* const* layers_k_rot, const float* cos_cache, const float* sin_cache, const void* cos_half,
                         const void* sin_half, int32_t n_pos, float scale, const void* out,
                         const void* dO, const float* gmax, const float* gsum, int32_t* const* parents, float* dq,
-                        float* const* dk_levels, float* const* dv_levels, int32_t* status, uint32_t flags,
-                        void* stream) {
+                        float* const* dk_levels, float* const* dv_levels, const HtreeTypedGrads* typed, int32_t* status,
+                        uint32_t flags, void* stream) {
     int32_t ln[HTREE_MAX_LEVELS];
     const int L = check_shape(shape, ln);
     if (L < 0) return L;
-    if (!out || !dO || !gmax || !gsum || !parents || !dq || !dk_levels || !dv_levels) return HTREE_E_NULL;
+    if (!out || !dO || !gmax || !gsum || !parents || !dk_levels || !dv_levels) return HTREE_E_NULL;
+    if (typed) {
+        if (!typed->dq || !typed->dk || !typed->dv) return HTREE_E_NULL;
+        if (!aligned16(typed->dq) || !aligned16(typed->dk) || !aligned16(typed->dv)) return HTREE_E_ALIGN;
+    } else if (!dq) {
+        return HTREE_E_NULL;
+    }
     if (shape->T_q != 0 && (shape->T_q != shape->T || shape->t_offset != 0)) return HTREE_E_WINDOW;
     AttnParams p;
     int rc = fill_params(p, shape, L, ln, q, layers_k, layers_v, cos_cache, sin_cache, n_pos, scale, parents, status, flags);
@@ -262,29 +299,32 @@ int htree_b200_backward(const HtreeShape* shape, const void* q, void* const* lay
         if (!aligned16(dk_levels[l]) || !aligned16(dv_levels[l])) return HTREE_E_ALIGN;
         p.dk[l] = dk_levels[l]; p.dv[l] = dv_levels[l];
     }
-    for (int l = 0; l < L; ++l) {   // gradient accumulators start at zero (src/backward.py:979-981)
-        const size_t rows = (size_t)shape->B * ln[l] * shape->H_kv;
-        cudaError_t e = cudaMemsetAsync(dk_levels[l], 0, rows * shape->K * sizeof(float), st);
-        if (e == cudaSuccess) e = cudaMemsetAsync(dv_levels[l], 0, rows * shape->V * sizeof(float), st);
-        if (e != cudaSuccess) return (int)e;
-    }
     p.out = const_cast<void*>(out); p.dO = dO; p.gmax = const_cast<float*>(gmax); p.gsum = const_cast<float*>(gsum);
-    p.dq = dq;
+    p.dq = typed ? nullptr : dq;
+    p.dq_typed = typed ? typed->dq : nullptr;
     if (cos_half && sin_half && aligned32(cos_half) && aligned32(sin_half)) {
         p.cosh = static_cast<const __half*>(cos_half); p.sinh = static_cast<const __half*>(sin_half);
     }
+    // choose the kernel before anything is queued: a shape that neither kernel takes is refused with nothing launched
     bool fast = layers_k_rot != nullptr && !(flags & HTREE_FWD_GENERIC);
     if (fast) {
         for (int l = 0; l < L; ++l) {
             if (!layers_k_rot[l] || !aligned32(layers_k_rot[l]) || !aligned32(layers_v[l])) fast = false;
             p.lkr[l] = layers_k_rot[l];
         }
-        fast = fast && aligned32(q) && aligned32(dO) && aligned32(out) && aligned16(dq) && aligned32(cos_cache) &&
-               aligned32(sin_cache) && bwd_mma_supported(p, shape->dtype);
+        fast = fast && aligned32(q) && aligned32(dO) && aligned32(out) && aligned16(typed ? typed->dq : (void*)dq) &&
+               aligned32(cos_cache) && aligned32(sin_cache) && bwd_mma_supported(p, shape->dtype);
+    }
+    if (!fast && !bwd_generic_supported(p, shape->dtype)) return HTREE_E_UNSUPPORTED;
+    for (int l = 0; l < L; ++l) {   // gradient accumulators start at zero (src/backward.py:979-981)
+        const size_t rows = (size_t)shape->B * ln[l] * shape->H_kv;
+        cudaError_t e = cudaMemsetAsync(dk_levels[l], 0, rows * shape->K * sizeof(float), st);
+        if (e == cudaSuccess) e = cudaMemsetAsync(dv_levels[l], 0, rows * shape->V * sizeof(float), st);
+        if (e != cudaSuccess) return (int)e;
     }
     rc = fast ? launch_bwd_mma(p, shape->dtype, st) : launch_bwd_generic(p, shape->dtype, st);
     if (rc) return rc;
-    return launch_tree_backward(*shape, L, ln, dk_levels, dv_levels, st);
+    return launch_tree_backward(*shape, L, ln, dk_levels, dv_levels, st, typed ? typed->dk : nullptr, typed ? typed->dv : nullptr);
 }
 
 }  // extern "C"

@@ -5,8 +5,9 @@
 //              instruction: the pattern in which fwd_mma_kernel / bwd_mma_kernel fetch K' and V rows
 //   reduction  red.global.add.v4.f32 into random 512-byte rows, four whole 128-byte lines per warp instruction: the
 //              pattern in which bwd_mma_kernel adds its dK' / dV tiles into the level buffers
-// No counterpart in the reference.
-#include "mma_common.cuh"
+// No counterpart in the reference.  These are measurement aids of the benchmark, not part of the operator: they are built
+// into a library of their own (libhtree_b200_probes.so) and are not declared in the operator's C header.
+#include "../mma_common.cuh"
 
 namespace htree {
 
@@ -67,7 +68,7 @@ static int time_launches(Launch&& launch, int reps, cudaStream_t st, float* ms_o
 
 }  // namespace htree
 
-extern "C" int htree_b200_probe_gather(void* table, int64_t table_bytes, int32_t reps, float* gbs, void* stream) {
+extern "C" int htree_probe_gather(void* table, int64_t table_bytes, int32_t reps, float* gbs, void* stream) {
     using namespace htree;
     if (!table || !gbs) return HTREE_E_NULL;
     if (table_bytes < (int64_t)256 * 64 || table_bytes / 256 > 0x7fffffff || reps <= 0) return HTREE_E_SHAPE;
@@ -80,14 +81,14 @@ extern "C" int htree_b200_probe_gather(void* table, int64_t table_bytes, int32_t
     cudaStream_t st = (cudaStream_t)stream;
     uint32_t* sink = reinterpret_cast<uint32_t*>(table);   // written only if the xor of everything read hits one value
     float ms = 0.f;
-    const int rc = time_launches([&] { probe_gather_kernel<<<blocks, 256, 0, st>>>(static_cast<const uint8_t*>(table), nrows, iters, sink); note_launch(); },
+    const int rc = time_launches([&] { probe_gather_kernel<<<blocks, 256, 0, st>>>(static_cast<const uint8_t*>(table), nrows, iters, sink); },
                                  reps, st, &ms);
     if (rc) return rc;
     *gbs = (float)((double)blocks * 8 * iters * 4 * 1024.0 / (ms * 1e-3) / 1e9);
     return 0;
 }
 
-extern "C" int htree_b200_probe_reduction(float* buffer, int64_t buffer_bytes, int32_t reps, float* gbs, void* stream) {
+extern "C" int htree_probe_reduction(float* buffer, int64_t buffer_bytes, int32_t reps, float* gbs, void* stream) {
     using namespace htree;
     if (!buffer || !gbs) return HTREE_E_NULL;
     if (buffer_bytes < (int64_t)512 * 64 || buffer_bytes / 512 > 0x7fffffff || reps <= 0) return HTREE_E_SHAPE;
@@ -99,7 +100,7 @@ extern "C" int htree_b200_probe_reduction(float* buffer, int64_t buffer_bytes, i
     const uint32_t nrows = (uint32_t)(buffer_bytes / 512);
     cudaStream_t st = (cudaStream_t)stream;
     float ms = 0.f;
-    const int rc = time_launches([&] { probe_reduction_kernel<<<blocks, 128, 0, st>>>(buffer, nrows, iters); note_launch(); }, reps, st, &ms);
+    const int rc = time_launches([&] { probe_reduction_kernel<<<blocks, 128, 0, st>>>(buffer, nrows, iters); }, reps, st, &ms);
     if (rc) return rc;
     *gbs = (float)((double)blocks * 4 * iters * 16384.0 / (ms * 1e-3) / 1e9);
     return 0;

@@ -296,7 +296,12 @@ __global__ void __launch_bounds__(NTB) bwd_generic_kernel(const __grid_constant_
         }
         __syncthreads();
     }
-    for (int i = tid; i < Gc * K; i += NTB) p.dq[hbase * K + i] = m.dqs[i];
+    if (p.dq_typed) {   // rounded once to the storage type instead of an fp32 tensor the caller casts afterwards
+        T* dqt = reinterpret_cast<T*>(p.dq_typed);
+        for (int i = tid; i < Gc * K; i += NTB) dqt[hbase * K + i] = from_f<T>(m.dqs[i]);
+    } else {
+        for (int i = tid; i < Gc * K; i += NTB) p.dq[hbase * K + i] = m.dqs[i];
+    }
 }
 
 template <typename T>
@@ -316,6 +321,15 @@ static int launch_bt(const AttnParams& p, cudaStream_t st) {
 #undef HT_LAUNCH
     note_launch();
     return (int)cudaGetLastError();
+}
+
+// The size checks of the launcher, for callers that must decide before they queue any work.
+bool bwd_generic_supported(const AttnParams& p, int dtype) {
+    (void)dtype;
+    const int Gc = p.G < 16 ? p.G : 16;
+    const int GP = Gc <= 4 ? 4 : (Gc <= 8 ? 8 : 16);
+    if (p.K / 2 > NTB || p.TK * p.CR > 65535) return false;
+    return bwd_smem_layout(p.K, p.V, GP, p.TK * p.CR, p.TK, nullptr, nullptr) <= 227 * 1024;
 }
 
 int launch_bwd_generic(const AttnParams& p, int dtype, cudaStream_t st) {

@@ -86,6 +86,9 @@ __global__ void HTREE_BWD_BOUNDS bwd_mma_kernel(const __grid_constant__ AttnPara
     for (int i = 0; i < NOT; ++i) { dqa[i][0] = dqa[i][1] = dqa[i][2] = dqa[i][3] = 0.f; }
 
     for (int l = L - 1; l >= 0; --l) {
+#ifdef HTREE_BWD_SKIP_LEVEL   // timing experiments only: leaves out one level's work (results are then incomplete)
+        if (l == HTREE_BWD_SKIP_LEVEL) continue;
+#endif
         const int Nl = p.ln[l];
         const __half* lkr = reinterpret_cast<const __half*>(p.lkr[l]);
         const T* lv = reinterpret_cast<const T*>(p.lv[l]);
@@ -246,17 +249,31 @@ __global__ void HTREE_BWD_BOUNDS bwd_mma_kernel(const __grid_constant__ AttnPara
     }
 
     // ---- dq: this thread owns columns PPT*r + [0, PPT) of both halves of rows g and g+8 ----
+    // fp32 (the reference's contract, src/backward.py:1119), or rounded once to the storage type when the caller asked for
+    // typed gradients (the cast of src/backward.py:1193 without an fp32 tensor in between)
 #pragma unroll
     for (int rr = 0; rr < 2; ++rr) {
         if (!row_ok[rr]) continue;
-        float* dqrow = p.dq + (hbase + g + 8 * rr) * D;
 #pragma unroll
         for (int hf = 0; hf < 2; ++hf) {
-            float4* dst = reinterpret_cast<float4*>(dqrow + hf * HALF + PPT * r);
+            if (p.dq_typed) {
+                T* dqrow = reinterpret_cast<T*>(p.dq_typed) + (hbase + g + 8 * rr) * D + hf * HALF + PPT * r;
+                uint32_t w[PPT / 2];
 #pragma unroll
-            for (int m = 0; m < KS / 2; ++m)
-                dst[m] = make_float4(dqa[2 * (2 * m) + hf][2 * rr], dqa[2 * (2 * m) + hf][2 * rr + 1],
-                                     dqa[2 * (2 * m + 1) + hf][2 * rr], dqa[2 * (2 * m + 1) + hf][2 * rr + 1]);
+                for (int m = 0; m < KS / 2; ++m) {
+                    w[2 * m] = F::pack(dqa[2 * (2 * m) + hf][2 * rr], dqa[2 * (2 * m) + hf][2 * rr + 1]);
+                    w[2 * m + 1] = F::pack(dqa[2 * (2 * m + 1) + hf][2 * rr], dqa[2 * (2 * m + 1) + hf][2 * rr + 1]);
+                }
+#pragma unroll
+                for (int i = 0; i < PPT / 8; ++i)
+                    reinterpret_cast<uint4*>(dqrow)[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+            } else {
+                float4* dst = reinterpret_cast<float4*>(p.dq + (hbase + g + 8 * rr) * D + hf * HALF + PPT * r);
+#pragma unroll
+                for (int m = 0; m < KS / 2; ++m)
+                    dst[m] = make_float4(dqa[2 * (2 * m) + hf][2 * rr], dqa[2 * (2 * m) + hf][2 * rr + 1],
+                                         dqa[2 * (2 * m + 1) + hf][2 * rr], dqa[2 * (2 * m + 1) + hf][2 * rr + 1]);
+            }
         }
     }
 }

@@ -19,6 +19,7 @@ struct AttnParams {
     const void* lk[HTREE_MAX_LEVELS];
     const void* lv[HTREE_MAX_LEVELS];
     const void* lkr[HTREE_MAX_LEVELS];   // keys pre-rotated by their child index (16-bit storage types only), or NULL
+    const void* lvb[HTREE_MAX_LEVELS];   // values re-laid-out per parent block for the P.V fragments (tree.cu), or NULL
     int32_t ln[HTREE_MAX_LEVELS];   // N_l
     int64_t lpow[HTREE_MAX_LEVELS]; // CR^l
     const float* cosc;
@@ -36,7 +37,8 @@ struct AttnParams {
     float* tr_out;
     // backward inputs / outputs
     const void* dO;
-    float* dq;
+    float* dq;          // fp32 dq (the reference's contract), or NULL when dq_typed is set
+    void* dq_typed;     // dq in the storage type of q, or NULL
     float* dk[HTREE_MAX_LEVELS];
     float* dv[HTREE_MAX_LEVELS];
     int32_t B, T, H, Hkv, K, V, CR, TK, L, G, n_pos;
@@ -126,17 +128,22 @@ __device__ __forceinline__ void store_parent(const AttnParams& p, int l, int64_t
 
 // launchers implemented in the .cu files (return cudaError_t as int)
 int launch_tree_build(const HtreeShape& s, int L, const int32_t* ln, void* const* lk, void* const* lv, cudaStream_t st);
-int launch_tree_backward(const HtreeShape& s, int L, const int32_t* ln, float* const* dk, float* const* dv, cudaStream_t st);
+// typed_dk / typed_dv: NULL, or buffers of the storage type that receive the finished leaf gradients (the cast is fused
+// into the last streaming pass; the fp32 level-0 buffers then only hold the accumulators)
+int launch_tree_backward(const HtreeShape& s, int L, const int32_t* ln, float* const* dk, float* const* dv, cudaStream_t st,
+                         void* typed_dk = nullptr, void* typed_dv = nullptr);
 int launch_rotate_keys(const HtreeShape& s, int L, const int32_t* ln, void* const* lk, void* const* lkr, const float* cosc,
                        const float* sinc, cudaStream_t st);
 int launch_fwd_generic(const AttnParams& p, int dtype, cudaStream_t st);
 int launch_merge_to_global(const float* lmax, const float* lsum, const float* lout, float* gmax, float* gsum, float* gout,
                            int64_t rows, int V, cudaStream_t st);
 int launch_final_normalize(const float* gout, const float* gsum, void* out, int dtype, int64_t rows, int V, cudaStream_t st);
+int launch_block_values(const HtreeShape& s, int L, const int32_t* ln, void* const* lv, void* const* lvb, cudaStream_t st);
 bool fwd_mma_supported(const AttnParams& p, int dtype);
 int launch_fwd_mma(const AttnParams& p, int dtype, cudaStream_t st);
 bool bwd_mma_supported(const AttnParams& p, int dtype);
 int launch_bwd_mma(const AttnParams& p, int dtype, cudaStream_t st);
+bool bwd_generic_supported(const AttnParams& p, int dtype);
 int launch_bwd_generic(const AttnParams& p, int dtype, cudaStream_t st);
 
 }  // namespace htree

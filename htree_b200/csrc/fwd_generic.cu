@@ -164,13 +164,16 @@ __global__ void __launch_bounds__(NT) fwd_generic_kernel(const __grid_constant__
 #pragma unroll
         for (int i = 0; i < NT / 32; ++i) np += m.wtot[i];
         const int rci = (int)(((int64_t)t / p.lpow[l]) % CR);
-        const int nc = (np - 1) * CR + rci + 1, rp = nc - 1;
+        // A parent list without entries (only possible in single-level mode, where the caller supplies the lists) is an
+        // empty level: no candidate, no rotation position; the level state comes out neutral and the next list empty.
+        const bool empty = np <= 0;
+        const int nc = empty ? 0 : (np - 1) * CR + rci + 1, rp = nc - 1;
 
         // ---- 1. queries: rotate by the right-most position, scale, store head-minor ----
         for (int i = tid; i < GPAD * half; i += NT) {
             const int g = i / half, d = i - g * half;
             float a = 0.f, c = 0.f;
-            if (g < G) {
+            if (g < G && !empty) {
                 const float lo = to_f(qg[(int64_t)g * K + d]), hi = to_f(qg[(int64_t)g * K + d + half]);
                 const float cs = __ldg(p.cosc + (int64_t)rp * half + d), sn = __ldg(p.sinc + (int64_t)rp * half + d);
                 a = (lo * cs - hi * sn) * p.scale;

@@ -122,7 +122,6 @@ __global__ void __launch_bounds__(MW * 32, MODE == 1 ? HTREE_SEL_MIN_BLOCKS : HT
     for (int l = L - 1; l >= 0; --l) {
         const int Nl = p.ln[l];
         const __half* lkr = reinterpret_cast<const __half*>(p.lkr[l]);
-        const T* lv = reinterpret_cast<const T*>(p.lv[l]);
         if (kAccumulateKernel) {
             __syncwarp();
             for (int i = lane; i < TK; i += 32) par[i] = load_parent(p, l, qidx * TK + i);
@@ -145,10 +144,16 @@ __global__ void __launch_bounds__(MW * 32, MODE == 1 ? HTREE_SEL_MIN_BLOCKS : HT
         // share of the rows, keeps that level (shared by neighbouring queries, small enough to live in L1) cached
         const bool stream_rows = kSelectKernel ? l < L - 1 : true;
         const __half* kq = lkr + ((int64_t)b * Nl * p.Hkv + hk) * D + (D == 64 ? D / 4 : D / 8) * r;
-        const T* vq = lv + ((int64_t)b * Nl * p.Hkv + hk) * D + VB * g;
+        // blocked values of this level: block (b, parent, hk) holds CR*D elements, lane (g, r) owns words [(8r+g)*CHW, +CHW)
+        const int64_t vb_stride = (int64_t)p.Hkv * (CR * D / 2);     // 32-bit words between consecutive parents
+        const uint32_t* vbq = reinterpret_cast<const uint32_t*>(p.lvb[l]) +
+                              ((int64_t)b * ((Nl + CR - 1) / CR) * p.Hkv + hk) * (CR * D / 2) + (8 * r + g) * (NOT * (CR / 8));
         auto score = [&](int a, float (&S0)[4], float (&S1)[4], bool select) {
             int node0 = par[a] * CR;
             if (node0 < 0 || node0 >= Nl) { if (p.status) atomicOr(p.status, 4); node0 = 0; }
+#ifdef HTREE_KNOCK_L1ROWS   // timing experiments only: every gather hits the same rows (wrong results, no L2 latency)
+            node0 = 0;
+#endif
             uint32_t unused[1][4];
             if (rot16 && !select) score_chunk<D, false, true, false, NR, CR>(p, kq, rstride, Nl, node0, rp - CR * a, g, r, qraw, S0, S1, unused, nullptr, stream_rows);
             else score_chunk<D, false, false, false, NR, CR>(p, kq, rstride, Nl, node0, rp - CR * a, g, r, qraw, S0, S1, unused, nullptr, stream_rows);
@@ -156,16 +161,27 @@ __global__ void __launch_bounds__(MW * 32, MODE == 1 ? HTREE_SEL_MIN_BLOCKS : HT
 
         // online-softmax accumulation of the columns in `mask` (bit c = child c of the parent at slot a)
         auto accumulate_chunk = [&](int a, float (&S0)[4], float (&S1)[4], uint32_t mask) {
-            int node0 = par[a] * CR;
-            if (node0 < 0 || node0 >= Nl) node0 = 0;
+            int pblk = par[a];
+            if (pblk < 0 || (int64_t)pblk * CR >= Nl) pblk = 0;
+#ifdef HTREE_KNOCK_L1ROWS
+            pblk = 0;
+#endif
             const int col[4] = {2 * r, 2 * r + 1, 8 + 2 * r, 9 + 2 * r};
             const bool cv[4] = {(mask >> col[0] & 1) != 0, (mask >> col[1] & 1) != 0, (mask >> col[2] & 1) != 0, (mask >> col[3] & 1) != 0};
-            // value rows first (longest latency): piece g (VB columns) of the rows of this thread's four candidates, one
-            // load each; 32-byte loads keep the L1 data pipe at a quarter of the cycles that 16-byte loads of the same
-            // bytes take
-            uint32_t vr[4][VB / 2];
+            // value fragments first (longest latency): this lane's piece of the parent's blocked values, NOT*NB words
+            // that ARE the B fragments of the P.V products; the warp reads the block front to back
+            constexpr int NB = CR / 8, CHW = NOT * NB;
+            uint32_t vw[CHW];
+            {
+                const uint32_t* src = vbq + (int64_t)pblk * vb_stride;
 #pragma unroll
-            for (int c = 0; c < 4; ++c) ldg_vec<VB / 8>(vq + (int64_t)(node0 + col[c]) * rstride, cv[c], vr[c], stream_rows);
+                for (int i = 0; i < CHW / 8; ++i) {
+                    uint32_t t8[8];
+                    if (stream_rows) ldg32_stream(src + 8 * i, t8); else ldg32(src + 8 * i, t8);
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) vw[8 * i + u] = t8[u];
+                }
+            }
             const float NINF = -INFINITY;
             float s[2][4];   // [row][tile0 c0, tile0 c1, tile1 c0, tile1 c1]
             s[0][0] = (cv[0] && row_ok[0]) ? S0[0] : NINF; s[0][1] = (cv[1] && row_ok[0]) ? S0[1] : NINF;
@@ -202,14 +218,10 @@ __global__ void __launch_bounds__(MW * 32, MODE == 1 ? HTREE_SEL_MIN_BLOCKS : HT
                 }
             const uint32_t pa0 = F::pack(pr[0][0], pr[0][1]), pa1 = F::pack(pr[1][0], pr[1][1]);
             const uint32_t pa2 = F::pack(pr[0][2], pr[0][3]), pa3 = F::pack(pr[1][2], pr[1][3]);
-            // output tile w, column c <-> value column VB*c + w: the w-th element of every thread's piece
+            // output tile w, column c <-> value column VB*c + w (the blocked layout is built for exactly this mapping);
+            // children that are not accumulated have probability 0, and every value of the block is finite
 #pragma unroll
-            for (int w = 0; w < VB; ++w) {
-                const uint32_t sel = (w & 1) ? 0x7632u : 0x5410u;
-                const uint32_t b0 = __byte_perm(vr[0][w >> 1], vr[1][w >> 1], sel);
-                const uint32_t b1 = __byte_perm(vr[2][w >> 1], vr[3][w >> 1], sel);
-                F::mma(O[w], pa0, pa1, pa2, pa3, b0, b1);
-            }
+            for (int w = 0; w < NOT; ++w) F::mma(O[w], pa0, pa1, pa2, pa3, vw[w * NB], NB == 2 ? vw[w * NB + 1] : 0u);
         };
 
         if (l > 0 && kAccumulateKernel) {
@@ -429,6 +441,8 @@ bool fwd_mma_supported(const AttnParams& p, int dtype) {
     if (p.K != p.V || (p.K != 64 && p.K != 128)) return false;
     if (p.G > 16 || (p.CR != 16 && p.CR != 8)) return false;
     for (int l = 0; l < p.L; ++l) if (!p.lkr[l]) return false;
+    if (!(p.flags & HTREE_FWD_SELECT_ONLY))
+        for (int l = 0; l < p.L; ++l) if (!p.lvb[l]) return false;
     return mma_smem_per_warp(p.TK, p.CR) * MW <= 200 * 1024;
 }
 

@@ -76,7 +76,7 @@ int htree_b200_backward_static_scratch(const HtreeShape* shape, const void* q, v
     // htree_b200_backward zero-fills every level it is given before accumulating, so whatever an earlier call left in
     // the array is cleared on the caller's stream before this call's kernels touch it.
     return htree_b200_backward(shape, q, layers_k, layers_v, layers_k_rot, cos_cache, sin_cache, cos_half, sin_half, n_pos, scale, out, dO,
-                               gmax, gsum, parents, dq, dk_levels, dv_levels, status, flags, stream);
+                               gmax, gsum, parents, dq, dk_levels, dv_levels, nullptr, status, flags, stream);
 }
 
 }  // extern "C"

@@ -202,15 +202,89 @@ int launch_rotate_keys(const HtreeShape& s, int L, const int32_t* ln, void* cons
     return 0;
 }
 
+struct BlkArgs {
+    const void* src;
+    void* dst;
+    int64_t total;     // B * NBLK * Hkv * 32: one thread writes the piece one lane of the attention kernels reads
+    int32_t Hkv, N, NBLK;
+};
+
+// V^ ("blocked values"): the rows of one parent's CR children, re-laid-out so that every lane of a warp of the
+// tensor-core forward fetches the B fragments of its P.V products (mma.sync.m16n8k16, k = child, n = value column) as one
+// contiguous piece, with no byte permutes and fully coalesced (the warp reads the block's CR*D*2 bytes front to back).
+// Block (b, p, h) starts at ((b*NBLK + p)*Hkv + h) * CR*D elements; inside it, lane (g = lane/4... see below) owns
+//   word ((r*8 + g)*NOT + w)*NB + j  =  { V[p*CR + 8j + 2r][VB*g + w],  V[p*CR + 8j + 2r + 1][VB*g + w] }
+// with r = 0..3, g = 0..7, w = 0..NOT-1 (NOT = VB = D/8 output tiles), j = 0..NB-1 (NB = CR/8 registers per tile).
+// Rows beyond the end of the level are zero.  16-bit storage types; the values are copied bit for bit.
+template <int D, int CR>
+__global__ void __launch_bounds__(256) block_values_kernel(const __grid_constant__ BlkArgs a) {
+    constexpr int NOT = D / 8, NB = CR / 8, CHW = NOT * NB;     // CHW 32-bit words per lane
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= a.total) return;
+    const int slot = (int)(idx & 31), r = slot >> 3, g = slot & 7;
+    const int64_t blk = idx >> 5;                      // (b * NBLK + p) * Hkv + h
+    const int h = (int)(blk % a.Hkv);
+    const int p = (int)((blk / a.Hkv) % a.NBLK);
+    const int64_t b = blk / ((int64_t)a.Hkv * a.NBLK);
+    const uint16_t* src = reinterpret_cast<const uint16_t*>(a.src);
+    uint16_t e[NB][2][NOT];
+#pragma unroll
+    for (int j = 0; j < NB; ++j)
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int row = p * CR + 8 * j + 2 * r + u;
+            const bool ok = row < a.N;
+            const uint4* rp = reinterpret_cast<const uint4*>(src + (((b * a.N + (ok ? row : 0)) * a.Hkv + h) * (int64_t)D + NOT * g));
+#pragma unroll
+            for (int i = 0; i < NOT / 8; ++i) {
+                uint4 x = make_uint4(0u, 0u, 0u, 0u);
+                if (ok) x = __ldg(rp + i);
+                const uint32_t w4[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+                for (int q = 0; q < 4; ++q) { e[j][u][8 * i + 2 * q] = (uint16_t)(w4[q] & 0xffffu); e[j][u][8 * i + 2 * q + 1] = (uint16_t)(w4[q] >> 16); }
+            }
+        }
+    uint32_t* dst = reinterpret_cast<uint32_t*>(a.dst) + blk * (int64_t)(CR * D / 2) + (int64_t)slot * CHW;
+    uint32_t o[CHW];
+#pragma unroll
+    for (int w = 0; w < NOT; ++w)
+#pragma unroll
+        for (int j = 0; j < NB; ++j) o[w * NB + j] = (uint32_t)e[j][0][w] | ((uint32_t)e[j][1][w] << 16);
+#pragma unroll
+    for (int i = 0; i < CHW / 4; ++i) reinterpret_cast<uint4*>(dst)[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+}
+
+int launch_block_values(const HtreeShape& s, int L, const int32_t* ln, void* const* lv, void* const* lvb, cudaStream_t st) {
+    const int CR = s.compression_rate, D = s.V;
+    if (s.dtype == HTREE_F32 || (D != 64 && D != 128) || (CR != 8 && CR != 16)) return HTREE_E_UNSUPPORTED;
+    for (int l = 0; l < L; ++l) {
+        BlkArgs a;
+        a.src = lv[l]; a.dst = lvb[l];
+        a.Hkv = s.H_kv; a.N = ln[l]; a.NBLK = (ln[l] + CR - 1) / CR;
+        a.total = (int64_t)s.B * a.NBLK * s.H_kv * 32;
+        const unsigned grid = (unsigned)((a.total + 255) / 256);
+        if (D == 128) { if (CR == 16) block_values_kernel<128, 16><<<grid, 256, 0, st>>>(a); else block_values_kernel<128, 8><<<grid, 256, 0, st>>>(a); }
+        else { if (CR == 16) block_values_kernel<64, 16><<<grid, 256, 0, st>>>(a); else block_values_kernel<64, 8><<<grid, 256, 0, st>>>(a); }
+        note_launch();
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return (int)e;
+    }
+    return 0;
+}
+
 struct TreeBwdArgs {
-    const float* dparent[2];
+    const float* dparent[2];   // NULL: no parent level (the pass only casts)
     float* dchild[2];
+    void* typed[2];            // NULL: the sum is written back to dchild; else it is written here in the storage type
     int32_t wv[2];     // float4 per row
     int64_t total[2];  // B * Nc * wv
     int32_t Nc, Np, CR;
 };
 
-// dchild[b, c, :] += dparent[b, c / CR, :] / count(c / CR): one float4 of a child row per thread.
+// dchild[b, c, :] += dparent[b, c / CR, :] / count(c / CR): one float4 of a child row per thread.  With a typed
+// destination (the last pass of a backward whose caller wants the gradients in the storage type) the sum goes there
+// instead, rounded once: the cast of src/backward.py:1193 without another pass over the tensor.
+template <typename TO>
 __global__ void __launch_bounds__(256) tree_backward_kernel(const __grid_constant__ TreeBwdArgs a) {
     const int which = blockIdx.y;
     const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -218,33 +292,62 @@ __global__ void __launch_bounds__(256) tree_backward_kernel(const __grid_constan
     const int wv = a.wv[which];
     const int col = (int)(idx % wv);
     const int64_t row = idx / wv;   // b * Nc + c
-    const int c = (int)(row % a.Nc);
-    const int64_t b = row / a.Nc;
-    const int p = c / a.CR;
-    const float cnt = (float)min(a.CR, a.Nc - p * a.CR);
-    const float4 g = __ldg(reinterpret_cast<const float4*>(a.dparent[which]) + ((b * a.Np + p) * (int64_t)wv + col));
     float4* dst = reinterpret_cast<float4*>(a.dchild[which]) + idx;
     float4 x = *dst;
-    x.x += g.x / cnt; x.y += g.y / cnt; x.z += g.z / cnt; x.w += g.w / cnt;
-    *dst = x;
+    if (a.dparent[which]) {
+        const int c = (int)(row % a.Nc);
+        const int64_t b = row / a.Nc;
+        const int p = c / a.CR;
+        const float cnt = (float)min(a.CR, a.Nc - p * a.CR);
+        const float4 g = __ldg(reinterpret_cast<const float4*>(a.dparent[which]) + ((b * a.Np + p) * (int64_t)wv + col));
+        x.x += g.x / cnt; x.y += g.y / cnt; x.z += g.z / cnt; x.w += g.w / cnt;
+    }
+    if (a.typed[which]) {
+        TO* o = reinterpret_cast<TO*>(a.typed[which]) + idx * 4;
+        if (sizeof(TO) == 4) {
+            *reinterpret_cast<float4*>(o) = x;
+        } else {
+            TO h[4] = {from_f<TO>(x.x), from_f<TO>(x.y), from_f<TO>(x.z), from_f<TO>(x.w)};
+            *reinterpret_cast<uint2*>(o) = *reinterpret_cast<const uint2*>(h);
+        }
+    } else {
+        *dst = x;
+    }
 }
 
-int launch_tree_backward(const HtreeShape& s, int L, const int32_t* ln, float* const* dk, float* const* dv, cudaStream_t st) {
-    for (int l = L - 1; l >= 1; --l) {
+template <typename TO>
+static int tree_backward_levels(const HtreeShape& s, int L, const int32_t* ln, float* const* dk, float* const* dv, cudaStream_t st,
+                                void* typed_dk, void* typed_dv) {
+    const bool typed = typed_dk != nullptr || typed_dv != nullptr;
+    for (int l = L - 1; l >= (typed ? 0 : 1); --l) {
+        // l >= 1: fold level l into level l-1; l == 0 (only with typed outputs and a single level): cast alone
+        const int child = l >= 1 ? l - 1 : 0;
         TreeBwdArgs a;
-        a.dparent[0] = dk[l]; a.dparent[1] = dv[l];
-        a.dchild[0] = dk[l - 1]; a.dchild[1] = dv[l - 1];
+        a.dparent[0] = l >= 1 ? dk[l] : nullptr; a.dparent[1] = l >= 1 ? dv[l] : nullptr;
+        a.dchild[0] = dk[child]; a.dchild[1] = dv[child];
+        const bool last = child == 0;
+        a.typed[0] = last ? typed_dk : nullptr; a.typed[1] = last ? typed_dv : nullptr;
         a.wv[0] = s.H_kv * s.K / 4; a.wv[1] = s.H_kv * s.V / 4;
-        a.Nc = ln[l - 1]; a.Np = ln[l]; a.CR = s.compression_rate;
+        a.Nc = ln[child]; a.Np = l >= 1 ? ln[l] : 1; a.CR = s.compression_rate;
         a.total[0] = (int64_t)s.B * a.Nc * a.wv[0]; a.total[1] = (int64_t)s.B * a.Nc * a.wv[1];
         int64_t mx = a.total[0] > a.total[1] ? a.total[0] : a.total[1];
         dim3 grid((unsigned)((mx + 255) / 256), 2);
-        tree_backward_kernel<<<grid, 256, 0, st>>>(a);
+        tree_backward_kernel<TO><<<grid, 256, 0, st>>>(a);
         note_launch();
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) return (int)e;
+        if (l == 1 || l == 0) break;
     }
     return 0;
+}
+
+int launch_tree_backward(const HtreeShape& s, int L, const int32_t* ln, float* const* dk, float* const* dv, cudaStream_t st,
+                         void* typed_dk, void* typed_dv) {
+    switch (s.dtype) {
+        case HTREE_BF16: return tree_backward_levels<__nv_bfloat16>(s, L, ln, dk, dv, st, typed_dk, typed_dv);
+        case HTREE_F16: return tree_backward_levels<__half>(s, L, ln, dk, dv, st, typed_dk, typed_dv);
+        default: return tree_backward_levels<float>(s, L, ln, dk, dv, st, typed_dk, typed_dv);
+    }
 }
 
 }  // namespace htree

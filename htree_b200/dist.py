@@ -165,8 +165,9 @@ def htree_forward_sequence_parallel(q_local: torch.Tensor, k: torch.Tensor, v: t
     else:
         t0, t1 = query_range(T, world, rank, compression_rate, L) if world > 1 else (0, T)
     assert q_local.shape[1] == t1 - t0
-    from .ops import rotate_keys
+    from .ops import block_values, rotate_keys
     layers_k, layers_v = build_tree_sequence_parallel(k, v, compression_rate, max_top_nodes, group, ranges=ranges)
     layers_kr = rotate_keys(layers_k, compression_rate, max_top_nodes, rope_base)   # local work on the gathered levels
+    layers_vb = block_values(layers_v, compression_rate, max_top_nodes) if layers_kr is not None else None
     return htree_forward(q_local, k, v, compression_rate, max_top_nodes, top_k_per_layer, scale, rope_base,
-                         _q_offset=t0, _layers=(layers_k, layers_v, layers_kr))
+                         _q_offset=t0, _layers=(layers_k, layers_v, layers_kr, layers_vb))

@@ -75,8 +75,8 @@ def forward_backward_host(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, dO:
             if bwd:
                 o, ctx = ops.htree_forward(dev_in[0], dev_in[1], dev_in[2], compression_rate, max_top_nodes,
                                            top_k_per_layer, scale, rope_base, _save_for_backward=True)
-                dq, dk, dv = ops.htree_backward(dev_in[3], dev_in[0], o, ctx)
-                res = [o, dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype)]
+                dq, dk, dv = ops.htree_backward(dev_in[3], dev_in[0], o, ctx, _typed=True)
+                res = [o, dq, dk, dv]
                 del ctx
             else:
                 res = [ops.htree_forward(dev_in[0], dev_in[1], dev_in[2], compression_rate, max_top_nodes,
@@ -128,8 +128,8 @@ def _by_units(q, k, v, dO, outs, dev, streams, compression_rate, max_top_nodes, 
                                                    top_k_per_layer, scale, rope_base, _save_for_backward=True)
                         fwd_done = torch.cuda.Event(); fwd_done.record(s_run)
                         s_run.wait_event(ready_bwd)
-                        dq, dk, dv = ops.htree_backward(dev_in[3], dev_in[0], o, ctx)
-                        res = [o, dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype)]
+                        dq, dk, dv = ops.htree_backward(dev_in[3], dev_in[0], o, ctx, _typed=True)
+                        res = [o, dq, dk, dv]
                         del ctx
                     else:
                         res = [ops.htree_forward(dev_in[0], dev_in[1], dev_in[2], compression_rate, max_top_nodes,

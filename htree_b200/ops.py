@@ -162,9 +162,11 @@ def build_tree(k: torch.Tensor, v: torch.Tensor, compression_rate: int, max_top_
                rope_base: Optional[float] = None):
     """Mean-pool tree (src/parallel.py:941-976).  Returns (layers_k, layers_v); level 0 are k and v themselves.
 
-    With `rope_base` given and a 16-bit storage type, a third list is returned: the keys of every level rotated by
-    their child index (node % compression_rate), which the tensor-core forward reads instead of layers_k.  These
-    are float16 tensors for bf16 inputs too (one rounding of the rotated value, with half's finer significand)."""
+    With `rope_base` given, (layers_k, layers_v, layers_k_rot, layers_v_blk) is returned; the last two are the operand
+    copies the tensor-core kernels read (None where no such kernel exists: fp32, or head sizes / compression rates they
+    do not cover): the keys of every level rotated by their child index (node % compression_rate), float16 for bf16
+    inputs too (one rounding of the rotated value, with half's finer significand), and the values of every level grouped
+    per parent in the order the kernel's lanes consume them ([B, ceil(N/CR)*CR, H_kv, V], rows past N zero)."""
     k = k.contiguous(); v = v.contiguous()
     B, T, H_kv, K = k.shape
     V = v.shape[-1]
@@ -175,6 +177,8 @@ def build_tree(k: torch.Tensor, v: torch.Tensor, compression_rate: int, max_top_
         layers_v.append(torch.empty(B, n, H_kv, V, dtype=v.dtype, device=v.device))
     want_rot = rope_base is not None and k.dtype != torch.float32 and K % 16 == 0
     layers_kr = [torch.empty(x.shape, dtype=torch.float16, device=x.device) for x in layers_k] if want_rot else None
+    want_blk = want_rot and _blockable(V, compression_rate)
+    layers_vb = [_blocked_like(x, compression_rate) for x in layers_v] if want_blk else None
     if len(sizes) > 1 or want_rot:
         shape = _lib.HtreeShape(B, T, H_kv, H_kv, K, V, int(compression_rate), 1, int(max_top_nodes),
                                 _DTYPES[k.dtype])   # H and top_k play no role in the tree
@@ -184,11 +188,35 @@ def build_tree(k: torch.Tensor, v: torch.Tensor, compression_rate: int, max_top_
         with torch.cuda.device(k.device):
             _lib.check(_lib.lib().htree_b200_build_tree(
                 ctypes.byref(shape), _ptrs(layers_k), _ptrs(layers_v), _ptrs(layers_kr) if want_rot else None,
+                _ptrs(layers_vb) if want_blk else None,
                 cos_c.data_ptr() if want_rot else None, sin_c.data_ptr() if want_rot else None, _stream()),
                 "build_tree")
     if rope_base is not None:
-        return layers_k, layers_v, layers_kr
+        return layers_k, layers_v, layers_kr, layers_vb
     return layers_k, layers_v
+
+
+def _blockable(V: int, compression_rate: int) -> bool:
+    return V in (64, 128) and int(compression_rate) in (8, 16)
+
+
+def _blocked_like(x: torch.Tensor, compression_rate: int) -> torch.Tensor:
+    B, N, H_kv, V = x.shape
+    cr = int(compression_rate)
+    return torch.empty(B, (N + cr - 1) // cr * cr, H_kv, V, dtype=x.dtype, device=x.device)
+
+
+def block_values(layers_v, compression_rate: int, max_top_nodes: int):
+    """Blocked copies of existing value levels (see build_tree); None for fp32 or shapes the tensor-core forward does not cover."""
+    v = layers_v[0]
+    B, T, H_kv, V = v.shape
+    if v.dtype == torch.float32 or not _blockable(V, compression_rate):
+        return None
+    out = [_blocked_like(x, compression_rate) for x in layers_v]
+    shape = _lib.HtreeShape(B, T, H_kv, H_kv, V, V, int(compression_rate), 1, int(max_top_nodes), _DTYPES[v.dtype])
+    with torch.cuda.device(v.device):
+        _lib.check(_lib.lib().htree_b200_block_values(ctypes.byref(shape), _ptrs(layers_v), _ptrs(out), _stream()), "block_values")
+    return out
 
 
 def rotate_keys(layers_k, compression_rate: int, max_top_nodes: int, rope_base: float):
@@ -207,11 +235,12 @@ def rotate_keys(layers_k, compression_rate: int, max_top_nodes: int, rope_base: 
 
 
 def _run_forward(shape, q, layers_k, layers_v, cos_cache, sin_cache, scale, out, gmax, gsum, parents, trace, flags,
-                 layers_kr=None, half_tables=None):
+                 layers_kr=None, half_tables=None, layers_vb=None):
     with torch.cuda.device(q.device):
         rc = _lib.lib().htree_b200_forward(
             ctypes.byref(shape), q.data_ptr(), _ptrs(layers_k), _ptrs(layers_v),
-            _ptrs(layers_kr) if layers_kr is not None else None, cos_cache.data_ptr(), sin_cache.data_ptr(),
+            _ptrs(layers_kr) if layers_kr is not None else None, _ptrs(layers_vb) if layers_vb is not None else None,
+            cos_cache.data_ptr(), sin_cache.data_ptr(),
             half_tables[0].data_ptr() if half_tables else None, half_tables[1].data_ptr() if half_tables else None,
             cos_cache.shape[0], float(scale),
             out.data_ptr() if out is not None else None, gmax.data_ptr() if gmax is not None else None,
@@ -246,8 +275,13 @@ def htree_forward(
     if _layers is not None:
         layers_k, layers_v = _layers[0], _layers[1]
         layers_kr = _layers[2] if len(_layers) > 2 else None
+        layers_vb = _layers[3] if len(_layers) > 3 else None
+        if layers_kr is not None and layers_vb is None:
+            layers_vb = block_values(layers_v, compression_rate, max_top_nodes)
     else:
-        layers_k, layers_v, layers_kr = build_tree(k, v, compression_rate, max_top_nodes, rope_base)
+        layers_k, layers_v, layers_kr, layers_vb = build_tree(k, v, compression_rate, max_top_nodes, rope_base)
+    if layers_vb is None:
+        layers_kr = None          # the tensor-core forward needs both operand copies
     L = len(layers_k)
     cos_cache, sin_cache = rope_cache(K, top_k_per_layer * compression_rate + 1024, rope_base, dev)
     out = torch.empty(B, T, H, V, dtype=q.dtype, device=dev)
@@ -272,7 +306,7 @@ def htree_forward(
     flags |= _parents_flag(parents)
     half_tables = rope_cache_half(K, cos_cache.shape[0], rope_base, scale, dev) if layers_kr is not None else None
     _run_forward(shape, q, layers_k, layers_v, cos_cache, sin_cache, scale, out, gmax, gsum, parents, trace, flags,
-                 layers_kr, half_tables)
+                 layers_kr, half_tables, layers_vb)
     if not (_save_for_backward or return_trace):
         return out
     result = [out]
@@ -281,7 +315,8 @@ def htree_forward(
         result.append(dict(
             global_max=gmax, global_sum=gsum,
             per_layer_parents={l: parents[l] for l in range(L)} if (_save_parents and want_parents) else None,
-            layers_k=layers_k, layers_v=layers_v, layers_k_rot=layers_kr, cos_cache=cos_cache, sin_cache=sin_cache,
+            layers_k=layers_k, layers_v=layers_v, layers_k_rot=layers_kr, layers_v_blk=layers_vb,
+            cos_cache=cos_cache, sin_cache=sin_cache,
             rope_half=half_tables,
             num_layers=L, rope_base=rope_base,
             compression_rate=compression_rate, top_k_per_layer=top_k_per_layer, max_top_nodes=max_top_nodes,
@@ -314,9 +349,16 @@ def recompute_parents(q, layers_k, layers_v, cos_cache, sin_cache, compression_r
     return {l: parents[l] for l in range(L)}
 
 
-def htree_backward(dO: torch.Tensor, q: torch.Tensor, output: torch.Tensor, bwd_ctx: dict, _force_generic: bool = False):
+def htree_backward(dO: torch.Tensor, q: torch.Tensor, output: torch.Tensor, bwd_ctx: dict, _force_generic: bool = False,
+                   _typed: bool = False):
     """Backward given the forward context; returns fp32 (dq, dk, dv) with the shapes of q, k, v
-    (src/backward.py:941-1119).  If bwd_ctx['per_layer_parents'] is None the selections are rebuilt first."""
+    (src/backward.py:941-1119).  If bwd_ctx['per_layer_parents'] is None the selections are rebuilt first.
+
+    `_typed=True` returns the three gradients in q's dtype instead, rounded once inside the kernels: what the
+    reference's autograd function produces by casting the fp32 results afterwards (src/backward.py:1193), without the
+    fp32 dq tensor and the extra passes over memory.
+    dO must have q's dtype (the kernels read it in the storage type; the reference up-casts both to fp32,
+    src/backward.py:966): a wider dO is refused rather than rounded silently."""
     B, T, H, K = q.shape
     layers_k, layers_v = bwd_ctx["layers_k"], bwd_ctx["layers_v"]
     H_kv, V = layers_k[0].shape[2], layers_v[0].shape[-1]
@@ -328,16 +370,26 @@ def htree_backward(dO: torch.Tensor, q: torch.Tensor, output: torch.Tensor, bwd_
     half_tables = bwd_ctx.get("rope_half")
     dev = q.device
     q = q.contiguous()
-    dO = dO.contiguous().to(q.dtype)
+    if dO.dtype != q.dtype:
+        raise ValueError(f"dO has dtype {dO.dtype} but q has {q.dtype}: pass the output gradient in the operator's storage "
+                         "type (cast it explicitly if the loss of precision is acceptable)")
+    dO = dO.contiguous()
     output = output.contiguous()
     parents = bwd_ctx.get("per_layer_parents")
     if parents is None:
         parents = recompute_parents(q, layers_k, layers_v, cos_cache, sin_cache, CR, TK, MTN, scale,
                                     bwd_ctx.get("layers_k_rot"))
     shape = _lib.HtreeShape(B, T, H, H_kv, K, V, int(CR), int(TK), int(MTN), _DTYPES[q.dtype])
-    dq = torch.empty(B, T, H, K, dtype=torch.float32, device=dev)
     dk_levels = [torch.empty(x.shape, dtype=torch.float32, device=dev) for x in layers_k]
     dv_levels = [torch.empty(x.shape, dtype=torch.float32, device=dev) for x in layers_v]
+    typed = None
+    if _typed:
+        dq = torch.empty(B, T, H, K, dtype=q.dtype, device=dev)
+        dk_t = torch.empty(layers_k[0].shape, dtype=q.dtype, device=dev)
+        dv_t = torch.empty(layers_v[0].shape, dtype=q.dtype, device=dev)
+        typed = _lib.HtreeTypedGrads(dq.data_ptr(), dk_t.data_ptr(), dv_t.data_ptr())
+    else:
+        dq = torch.empty(B, T, H, K, dtype=torch.float32, device=dev)
     with torch.cuda.device(dev):
         rc = _lib.lib().htree_b200_backward(
             ctypes.byref(shape), q.data_ptr(), _ptrs(layers_k), _ptrs(layers_v),
@@ -345,10 +397,12 @@ def htree_backward(dO: torch.Tensor, q: torch.Tensor, output: torch.Tensor, bwd_
             half_tables[0].data_ptr() if half_tables else None, half_tables[1].data_ptr() if half_tables else None,
             cos_cache.shape[0], float(scale), output.data_ptr(), dO.data_ptr(),
             bwd_ctx["global_max"].data_ptr(), bwd_ctx["global_sum"].data_ptr(),
-            _ptrs([parents[l] for l in range(L)]), dq.data_ptr(), _ptrs(dk_levels), _ptrs(dv_levels),
-            _status(dev).data_ptr(),
+            _ptrs([parents[l] for l in range(L)]), None if _typed else dq.data_ptr(), _ptrs(dk_levels), _ptrs(dv_levels),
+            ctypes.byref(typed) if typed is not None else None, _status(dev).data_ptr(),
             (_lib.FWD_GENERIC if _force_generic else 0) | _parents_flag([parents[l] for l in range(L)]), _stream())
     _lib.check(rc, "backward")
+    if _typed:
+        return dq, dk_t, dv_t
     return dq, dk_levels[0], dv_levels[0]
 
 
@@ -364,7 +418,7 @@ class HTreeFunction(torch.autograd.Function):
         ctx.save_for_backward(q, k, v, output, bwd_ctx["global_max"], bwd_ctx["global_sum"])
         ctx.bwd_ctx = bwd_ctx
         if not save:   # like the reference: drop the pooled levels and rebuild them in backward
-            bwd_ctx["layers_k"] = bwd_ctx["layers_v"] = bwd_ctx["layers_k_rot"] = None
+            bwd_ctx["layers_k"] = bwd_ctx["layers_v"] = bwd_ctx["layers_k_rot"] = bwd_ctx["layers_v_blk"] = None
         return output
 
     @staticmethod
@@ -372,10 +426,10 @@ class HTreeFunction(torch.autograd.Function):
         q, k, v, output, gmax, gsum = ctx.saved_tensors
         c = dict(ctx.bwd_ctx)
         if c["layers_k"] is None:
-            c["layers_k"], c["layers_v"], c["layers_k_rot"] = build_tree(k, v, c["compression_rate"],
-                                                                         c["max_top_nodes"], c["rope_base"])
-        dq, dk, dv = htree_backward(dO, q, output, c)
-        return dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype), None, None, None, None, None
+            c["layers_k"], c["layers_v"], c["layers_k_rot"], c["layers_v_blk"] = build_tree(
+                k, v, c["compression_rate"], c["max_top_nodes"], c["rope_base"])
+        dq, dk, dv = htree_backward(dO.to(q.dtype), q, output, c, _typed=True)    # gradients come back in the input dtype
+        return dq, dk, dv, None, None, None, None, None
 
 
 HTreeTritonFunction = HTreeFunction   # drop-in name of the reference
@@ -394,6 +448,7 @@ htree_forward_triton_autograd = htree_forward_autograd   # drop-in name of the r
 
 __all__ = [
     "decode_parents", "HTREE_SCORE_NEG_INF", "HTREE_SCORE_VALID_THRESHOLD", "LayerTrace", "build_tree", "rope_cache",
+    "rotate_keys", "block_values",
     "htree_forward", "htree_backward", "recompute_parents", "HTreeFunction", "HTreeTritonFunction",
     "htree_forward_autograd", "htree_forward_triton_autograd", "check_status",
 ]

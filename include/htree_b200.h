@@ -22,7 +22,7 @@
 extern "C" {
 #endif
 
-#define HTREE_B200_VERSION 1
+#define HTREE_B200_VERSION 2
 #define HTREE_MAX_LEVELS 12
 
 /* storage types */
@@ -81,6 +81,16 @@ typedef struct HtreeTrace {
     float* layer_out;
 } HtreeTrace;
 
+/* Optional gradient outputs in the storage type (`dtype` of the shape) for htree_b200_backward: dq [B,T,H,K],
+ * dk [B,T,H_kv,K], dv [B,T,H_kv,V], 16-byte aligned.  The reference returns fp32 gradients and its autograd function
+ * casts them afterwards (src/backward.py:1119, 1193); with this struct the cast is fused into the kernels that produce
+ * the values and no fp32 dq tensor exists at all. */
+typedef struct HtreeTypedGrads {
+    void* dq;
+    void* dk;
+    void* dv;
+} HtreeTypedGrads;
+
 int htree_b200_version(void);
 const char* htree_b200_error_string(int code);
 
@@ -102,9 +112,16 @@ int htree_b200_level_sizes(int32_t T, int32_t compression_rate, int32_t max_top_
  *                 (clamped to the finite half range).  The column order inside a K' row is private to the library
  *                 (rows of 64 columns interleave 8-column pieces of the two halves).  The tensor-core forward reads K' (16-bit storage
  *                 types only; needs cos_cache/sin_cache with at least compression_rate rows, and K % 16 == 0).
- *                 Pass NULL for fp32 or when only the generic kernels are wanted. */
+ *                 Pass NULL for fp32 or when only the generic kernels are wanted.
+ *   layers_v_blk  NULL, or L pointers to buffers of B * ceil(N_l / compression_rate) * H_kv * compression_rate * V
+ *                 elements of `dtype` (level 0 included; 32-byte aligned) that receive the values of every level grouped by
+ *                 parent: the compression_rate children of one parent and KV head form one block whose element order is
+ *                 private to the library (the order in which the lanes of the tensor-core forward consume them); rows
+ *                 past the end of a level are zero.  The tensor-core forward accumulates from these blocks instead of
+ *                 gathering value rows.  16-bit storage types, V in {64,128}, compression_rate 8 or 16 only. */
 int htree_b200_build_tree(const HtreeShape* shape, void* const* layers_k, void* const* layers_v,
-                          void* const* layers_k_rot, const float* cos_cache, const float* sin_cache, void* stream);
+                          void* const* layers_k_rot, void* const* layers_v_blk, const float* cos_cache,
+                          const float* sin_cache, void* stream);
 
 /* K' levels alone, from tree levels that already exist (e.g. levels assembled by an all-gather in sequence-sharded
  * runs): layers_k_rot[l][node] = R(node % compression_rate) layers_k[l][node] for every level.  16-bit storage types
@@ -112,15 +129,20 @@ int htree_b200_build_tree(const HtreeShape* shape, void* const* layers_k, void* 
 int htree_b200_rotate_keys(const HtreeShape* shape, void* const* layers_k, void* const* layers_k_rot,
                            const float* cos_cache, const float* sin_cache, void* stream);
 
+/* The blocked values alone (layers_v_blk of htree_b200_build_tree), from tree levels that already exist.  No counterpart
+ * in the reference. */
+int htree_b200_block_values(const HtreeShape* shape, void* const* layers_v, void* const* layers_v_blk, void* stream);
+
 /* Fused forward over all levels: replaces the per-level launches of htree_select_accumulate_gqa_kernel,
  * htree_bottom_accumulate_gqa_kernel, htree_merge_to_global_kernel and htree_final_normalize_kernel together with
  * the host-side state and virtual-parent initialisation (src/parallel.py:995-1134), and — with
  * HTREE_FWD_SELECT_ONLY — htree_recompute_selection_kernel / _recompute_parents (src/parallel.py:1167-1399,
  * src/backward.py:881-934).
- *   layers_k_rot  NULL or the K' levels written by htree_b200_build_tree; when present (and the shape qualifies:
- *                 bf16/fp16, K == V in {64,128}, H/H_kv <= 16, compression_rate 16 or 8, and q, every level of
- *                 layers_v and layers_k_rot and the tables 32-byte aligned; the backward also wants out and dO so)
- *                 the tensor-core kernel runs, otherwise the generic fp32-arithmetic kernel (16-byte alignment)
+ *   layers_k_rot, layers_v_blk  NULL or the K' levels and blocked values written by htree_b200_build_tree; when present
+ *                 (and the shape qualifies: bf16/fp16, K == V in {64,128}, H/H_kv <= 16, compression_rate 16 or 8, and q,
+ *                 every level of layers_k_rot / layers_v_blk and the tables 32-byte aligned; the backward also wants
+ *                 layers_v, out and dO so) the tensor-core kernel runs, otherwise the generic fp32-arithmetic kernel
+ *                 (16-byte alignment).  With HTREE_FWD_SELECT_ONLY layers_v_blk is not read and may be NULL.
  *   cos_cache, sin_cache  [n_pos, K/2] fp32 RoPE tables (src/parallel.py:983-988); n_pos >= top_k*compression_rate
  *   cos_half, sin_half    NULL, or [n_pos, K/2] IEEE half tables holding cos*scale and sin*scale: the tensor-core
  *                         kernels then rotate queries with packed half arithmetic where that does not touch the
@@ -132,7 +154,7 @@ int htree_b200_rotate_keys(const HtreeShape* shape, void* const* layers_k, void*
  *   status   NULL or one int32 on the device, OR-ed with a non-zero code if a kernel met an out-of-range node index
  */
 int htree_b200_forward(const HtreeShape* shape, const void* q, void* const* layers_k, void* const* layers_v,
-                       void* const* layers_k_rot, const float* cos_cache, const float* sin_cache, const void* cos_half,
+                       void* const* layers_k_rot, void* const* layers_v_blk, const float* cos_cache, const float* sin_cache, const void* cos_half,
                        const void* sin_half, int32_t n_pos, float scale, void* out,
                        float* gmax, float* gsum, int32_t* const* parents, const HtreeTrace* trace, int32_t* status,
                        uint32_t flags, void* stream);
@@ -160,14 +182,6 @@ int htree_b200_final_normalize(const float* global_out, const float* global_sum,
 int htree_b200_copy_rows(void* dst, int64_t dpitch, const void* src, int64_t spitch, int64_t width, int64_t height,
                          void* stream);
 
-/* Measured ceilings of the two memory paths the attention kernels depend on (measurement aids, no reference counterpart).
- * gather: GB/s of random 256-byte rows read from `table` (table_bytes, 32-byte aligned) with the kernels' 32-byte loads;
- * reduction: GB/s of fp32 red.global.add.v4 into random 512-byte rows of `buffer` (its contents are overwritten).
- * A buffer well below the L2 size measures the L2 path, a much larger one the HBM path.  Both calls time `reps` launches
- * with CUDA events on `stream` and wait for them. */
-int htree_b200_probe_gather(void* table, int64_t table_bytes, int32_t reps, float* gbs, void* stream);
-int htree_b200_probe_reduction(float* buffer, int64_t buffer_bytes, int32_t reps, float* gbs, void* stream);
-
 /* Selector micro-benchmark (no counterpart on the operator path; the experiment of topk_test/benchmark.py:34-46):
  * `batch` independent problems, the k largest of n <= 8192 fp32 values each; pay1 [batch,n] and pay8 [batch,n,8] are
  * optional int32 payloads gathered for the winners.  method 0 = threshold search (the attention kernels' selector),
@@ -185,13 +199,17 @@ int htree_b200_topk(const float* values, const int32_t* pay1, const int32_t* pay
  *   dk_levels[l] [B,N_l,H_kv,K] fp32, dv_levels[l] [B,N_l,H_kv,V] fp32 for every level: zero-filled by this call,
  *   accumulated, then folded top-down by the mean-pool gradient; level 0 holds dk, dv on return and levels >= 1 are
  *   scratch (the reference's dk_layers / dv_layers, src/backward.py:979-981).
+ *   typed  NULL (the reference's contract: fp32 dq, dk, dv as above), or the three outputs in the storage type: dq is
+ *          then not written (it may be NULL), dk_levels[0] / dv_levels[0] still have to be provided as fp32
+ *          accumulators but hold no result on return, and the finished gradients are rounded once into typed->dq/dk/dv.
+ * A shape that no compiled kernel takes is refused with HTREE_E_UNSUPPORTED before anything is queued on the stream.
  */
 int htree_b200_backward(const HtreeShape* shape, const void* q, void* const* layers_k, void* const* layers_v,
                         void* const* layers_k_rot, const float* cos_cache, const float* sin_cache, const void* cos_half,
                         const void* sin_half, int32_t n_pos, float scale, const void* out,
                         const void* dO, const float* gmax, const float* gsum, int32_t* const* parents, float* dq,
-                        float* const* dk_levels, float* const* dv_levels, int32_t* status, uint32_t flags,
-                        void* stream);
+                        float* const* dk_levels, float* const* dv_levels, const HtreeTypedGrads* typed, int32_t* status,
+                        uint32_t flags, void* stream);
 
 /* Backward without caller-provided scratch.  No counterpart in the reference (its backward allocates its level
  * buffers with torch, src/backward.py:979-981); it exists for callers that cannot allocate device memory around
@@ -206,7 +224,8 @@ int htree_b200_backward(const HtreeShape* shape, const void* q, void* const* lay
  *   - Shapes whose pooled levels need more than that, sum over l >= 1 of B*N_l*H_kv*(K+V) floats (each level slice
  *     rounded up to 64 floats), are rejected with HTREE_E_SCRATCH before anything is launched.
  *   - The first call on a device looks up the array's device address (once per device, with that device current);
- *     make that first call outside of any stream capture.
+ *     make that first call outside of any stream capture.  As everywhere in this library, `stream` must belong to the
+ *     device that is current in the calling thread: the address is looked up and cached for the current device.
  *   - All calls on one device share the array.  It keeps the previous call's contents; each call clears the part it
  *     uses on its own stream before use.  Two calls that overlap on the GPU (different streams, or threads without
  *     ordering between them) race on it: serialise them. */

@@ -140,3 +140,56 @@ def test_compat_argument_errors():
         compat.htree_select_accumulate_gqa_kernel[(16, 1)](x, x, x, par, cs, cs, st, st, x, par, layer_power=6, **kw)
     with pytest.raises(RuntimeError):   # CPU tensors are refused, never computed on the host
         compat.htree_final_normalize_kernel[(16, 1)](x.cpu(), st.cpu(), x.cpu(), B=1, T=16, H=1, V=8)
+
+
+@pytest.mark.parametrize("level", [0, 1])
+def test_level_forward_with_an_empty_parent_list(level):
+    """A parent row that is all -1 (no parent at all) is an empty level for that group: neutral state (max = -1e10,
+    sum = 0, output = 0), an empty next list, no status bit, and the other groups are unaffected."""
+    from htree_b200 import compat, ops
+    B, T, H, H_kv, D, CR, TK = 1, 64, 4, 2, 32, 4, 4
+    q, k, v, _ = make_inputs(B, T, H, H_kv, D, D, "float32", seed=5)
+    q, k, v = q.cuda(), k.cuda(), v.cuda()
+    lk, lv = ops.build_tree(k, v, CR, 4)                      # levels of 64, 16, 4 nodes
+    cos_c, sin_c = ops.rope_cache(D, TK * CR + 1024, 10000.0, q.device)
+    n_level = lk[level].shape[1]
+    # valid lists: the first parents of the level above, truncated so that the right-most one holds the query's node
+    t_idx = torch.arange(T, device="cuda")
+    last = (t_idx // CR ** level) // CR
+    first = (last - (TK - 1)).clamp(min=0)
+    par = (first[:, None] + torch.arange(TK, device="cuda")[None, :])
+    par = torch.where(par <= last[:, None], par, torch.full_like(par, -1)).to(torch.int32)
+    par = par[None, :, None, :].expand(B, T, H_kv, TK).contiguous()
+    empty_t, empty_hk = 37, 1
+    ref_state = [torch.empty(B, T, H, device="cuda"), torch.empty(B, T, H, device="cuda"), torch.empty(B, T, H, D, device="cuda")]
+    ref_next = torch.empty_like(par)
+    kw = dict(layer_power=CR ** level, B=B, T=T, H=H, H_kv=H_kv, NUM_GROUPS=H // H_kv, K=D, V=D, N_layer=n_level,
+              COMPRESSION_RATE=CR, TOP_K=TK, scale=D ** -0.5)
+
+    def run(parents, state, nxt):
+        if level == 0:
+            compat.htree_bottom_accumulate_gqa_kernel[(T, B * H_kv)](q, lk[0], lv[0], parents, cos_c, sin_c, *state, **kw)
+        else:
+            compat.htree_select_accumulate_gqa_kernel[(T, B * H_kv)](q, lk[level], lv[level], parents, cos_c, sin_c, *state,
+                                                                     nxt, **kw)
+    run(par, ref_state, ref_next)
+    par2 = par.clone()
+    par2[0, empty_t, empty_hk] = -1
+    state = [torch.full_like(x, 7.0) for x in ref_state]
+    nxt = torch.full_like(par, 7)
+    run(par2, state, nxt)
+    ops.check_status(q.device)                                  # raises if a kernel flagged an index
+    G = H // H_kv
+    hs = slice(empty_hk * G, (empty_hk + 1) * G)
+    assert torch.all(state[0][0, empty_t, hs] == NEG_INF) and torch.all(state[1][0, empty_t, hs] == 0)
+    assert torch.all(state[2][0, empty_t, hs] == 0)
+    if level > 0:
+        assert torch.all(nxt[0, empty_t, empty_hk] == -1)
+    keep = torch.ones(B, T, H, dtype=torch.bool, device="cuda")
+    keep[0, empty_t, hs] = False
+    for a, b in zip(state, ref_state):
+        assert torch.equal(a[keep], b[keep])
+    if level > 0:
+        keep_g = torch.ones(B, T, H_kv, dtype=torch.bool, device="cuda")
+        keep_g[0, empty_t, empty_hk] = False
+        assert torch.equal(nxt[keep_g], ref_next[keep_g])

@@ -321,7 +321,17 @@ def test_tensor_core_selection_only_matches_full_forward():
 def test_prerotated_keys_match_direct_rotation():
     ops = _ops()
     _, k, v, _ = parity.make_inputs(1, 700, 2, 2, 64, 64, "bfloat16", 31)
-    lk, lv, lkr = ops.build_tree(k.to(DEV), v.to(DEV), 16, 16, 10000.0)
+    lk, lv, lkr, lvb = ops.build_tree(k.to(DEV), v.to(DEV), 16, 16, 10000.0)
+    # the blocked values hold the same elements, grouped per parent: word ((r*8+g)*NOT + w)*NB + j of block (b, p, h) is
+    # {V[16p + 8j + 2r][VB*g + w], V[16p + 8j + 2r + 1][VB*g + w]} with NOT = VB = 8 (64-wide rows), NB = 2; rows past N are zero
+    for a, b in zip(lv, lvb):
+        B_, N, Hkv, D = a.shape
+        nblk = (N + 15) // 16
+        pad = torch.zeros(B_, nblk * 16, Hkv, D, dtype=a.dtype, device=a.device)
+        pad[:, :N] = a
+        x = pad.view(B_, nblk, 2, 4, 2, Hkv, 8, 8)              # [b, p, j, r, e, h, g, w]
+        want = x.permute(0, 1, 5, 3, 6, 7, 2, 4).contiguous()   # [b, p, h, r, g, w, j, e]
+        assert torch.equal(b.view(-1), want.view(-1))
     cs, sn = oracle.rope_cache(64, 16)
     for a, b in zip(lk, lkr):
         x = parity.f32(a)
@@ -573,3 +583,32 @@ def test_tensor_core_kernels_with_reference_sized_top_k():
         st = parity.err_stats(parity.f32(a), parity.f32(b))
         scale = max(1.0, float(b.abs().max()))
         assert st["max"] <= 2e-2 * scale and st["p99"] <= 5e-3 * scale, (nm, st)
+
+
+@pytest.mark.parametrize("dtype,B,T,H,Hkv,D,CR,TK,MTN", [
+    ("bfloat16", 1, 3000, 32, 2, 128, 16, 16, 64),     # tensor-core kernels, three levels
+    ("float16", 2, 900, 8, 2, 64, 8, 16, 32),          # tensor-core kernels, 64-wide heads, compression rate 8
+    ("bfloat16", 1, 96, 4, 2, 32, 4, 32, 128),         # generic kernels, a single level: the cast runs alone
+    ("float32", 1, 700, 4, 2, 32, 4, 8, 16),           # fp32 storage: typed outputs are fp32 too
+])
+def test_typed_gradients_equal_the_cast_of_the_fp32_ones(dtype, B, T, H, Hkv, D, CR, TK, MTN):
+    """htree_backward(_typed=True) writes dq, dk, dv in the storage type from inside the kernels: the same values as
+    casting the fp32 results (src/backward.py:1193).  dq is bit-identical (one owner per row, same rounding); dk and dv
+    are sums of floating-point atomics whose order differs between two runs, so they agree to one storage ulp."""
+    ops = _ops()
+    q, k, v, dO = (x.to(DEV) for x in parity.make_inputs(B, T, H, Hkv, D, D, dtype, 91))
+    out, ctx = ops.htree_forward(q, k, v, CR, MTN, TK, _save_for_backward=True)
+    dq, dk, dv = ops.htree_backward(dO, q, out, ctx)
+    tq, tk, tv = ops.htree_backward(dO, q, out, ctx, _typed=True)
+    torch.cuda.synchronize(); ops.check_status()
+    assert tq.dtype == tk.dtype == tv.dtype == q.dtype and dq.dtype == torch.float32
+    assert torch.equal(tq, dq.to(q.dtype))
+    ulp = {"bfloat16": 2.0 ** -7, "float16": 2.0 ** -10, "float32": 2.0 ** -20}[dtype]
+    for a, b in ((tk, dk), (tv, dv)):
+        err = (a.float() - b).abs()
+        assert bool((err <= ulp * b.abs().clamp(min=1e-3) + 1e-6).all())
+    with pytest.raises(ValueError):          # a wider dO is refused, not rounded silently
+        if dtype != "float32":
+            ops.htree_backward(dO.float(), q, out, ctx)
+        else:
+            raise ValueError

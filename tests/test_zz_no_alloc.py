@@ -16,26 +16,33 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda"
 
 
-def _call(lib, shape, q, ctx, out, dO, dq, dk_arg, dv_arg, static):
+def _call(lib, shape, q, ctx, out, dO, dq, dk_arg, dv_arg, static, half_tables=False):
     from htree_b200 import _lib
     L = ctx["num_layers"]
     ptrs = lambda ts: _lib.ptr_array([t.data_ptr() for t in ts])
+    parents = [ctx["per_layer_parents"][l] for l in range(L)]
+    flags = _lib.PARENTS_U16 if parents[0].dtype == torch.int16 else 0
+    rope_half = ctx["rope_half"] if half_tables else None       # cos*scale, sin*scale as float16: packed-half rotations
     common = [ctypes.byref(shape), q.data_ptr(), ptrs(ctx["layers_k"]), ptrs(ctx["layers_v"]),
               ptrs(ctx["layers_k_rot"]) if ctx["layers_k_rot"] is not None else None, ctx["cos_cache"].data_ptr(),
-              ctx["sin_cache"].data_ptr(), None, None, ctx["cos_cache"].shape[0], float(ctx["scale"]), out.data_ptr(),
+              ctx["sin_cache"].data_ptr(), rope_half[0].data_ptr() if rope_half else None,
+              rope_half[1].data_ptr() if rope_half else None, ctx["cos_cache"].shape[0], float(ctx["scale"]), out.data_ptr(),
               dO.data_ptr(),
-              ctx["global_max"].data_ptr(), ctx["global_sum"].data_ptr(),
-              ptrs([ctx["per_layer_parents"][l] for l in range(L)]), dq.data_ptr()]
+              ctx["global_max"].data_ptr(), ctx["global_sum"].data_ptr(), ptrs(parents), dq.data_ptr()]
     stream = torch.cuda.current_stream().cuda_stream
     if static:
-        return lib.htree_b200_backward_static_scratch(*common, dk_arg.data_ptr(), dv_arg.data_ptr(), None, 0, stream)
-    return lib.htree_b200_backward(*common, ptrs(dk_arg), ptrs(dv_arg), None, 0, stream)
+        return lib.htree_b200_backward_static_scratch(*common, dk_arg.data_ptr(), dv_arg.data_ptr(), None, flags, stream)
+    return lib.htree_b200_backward(*common, ptrs(dk_arg), ptrs(dv_arg), None, None, flags, stream)
 
 
-@pytest.mark.parametrize("dtype,K", [("float32", 32), ("bfloat16", 128)])
-def test_static_scratch_backward_matches_backward_twice(dtype, K):
+@pytest.mark.parametrize("dtype,K,compact", [("float32", 32, False), ("bfloat16", 128, False), ("bfloat16", 128, True)])
+def test_static_scratch_backward_matches_backward_twice(dtype, K, compact, monkeypatch):
+    """compact: the selections travel as uint16 node ids and the kernels rotate with the packed-half tables, the
+    combination the autograd path of a memory-constrained caller would use."""
     import htree_b200 as ht
-    from htree_b200 import _lib
+    from htree_b200 import _lib, ops
+    if compact:
+        monkeypatch.setattr(ops, "SELECTION_STORAGE", "uint16")
     lib = _lib.lib()
     assert lib.htree_b200_static_scratch_bytes() == 16 << 20
     B, T, H, Hkv, CR, TK, MTN = 2, 1500, 8, 2, 16, 8, 16                 # levels 1500 -> 94 -> 6
@@ -49,10 +56,11 @@ def test_static_scratch_backward_matches_backward_twice(dtype, K):
         dq_a = torch.empty(B, T, H, K, dtype=torch.float32, device=DEV)
         dk_l = [torch.empty(x.shape, dtype=torch.float32, device=DEV) for x in ctx["layers_k"]]
         dv_l = [torch.empty(x.shape, dtype=torch.float32, device=DEV) for x in ctx["layers_v"]]
-        assert _call(lib, shape, q, ctx, out, dO, dq_a, dk_l, dv_l, static=False) == 0
+        assert (ctx["per_layer_parents"][0].dtype == torch.int16) == compact
+        assert _call(lib, shape, q, ctx, out, dO, dq_a, dk_l, dv_l, static=False, half_tables=compact) == 0
         dq_b = torch.empty_like(dq_a)
         dk_b = torch.full_like(dk_l[0], float("nan")); dv_b = torch.full_like(dv_l[0], float("nan"))
-        assert _call(lib, shape, q, ctx, out, dO, dq_b, dk_b, dv_b, static=True) == 0
+        assert _call(lib, shape, q, ctx, out, dO, dq_b, dk_b, dv_b, static=True, half_tables=compact) == 0
         torch.cuda.synchronize()
         for a, b in ((dq_a, dq_b), (dk_l[0], dk_b), (dv_l[0], dv_b)):
             scale = max(1.0, float(a.abs().max()))
