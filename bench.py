@@ -13,6 +13,7 @@ public Python API with pinned HOST buffers (H2D of q,k,v,dO and D2H of out,dq,dk
   workloads        the other benchmark configurations on one GPU (cfg2 and cfg4 forward, cfg5 bf16 / fp32 forward+backward)
   mode_b           (N > 1) cfg4 forward with the query positions split over the ranks and the pooled levels all-gathered
   triton_baseline  (N = 1) the unmodified reference's Triton path on the same GPU, when it has been staged under oracle/_ref
+  nsa_baseline     (N = 1) the NSA comparison baseline the reference ships, timed beside the htree forward as its speed script does
   cpu_baseline     the reference's CPU oracle (src/naive.py, from oracle/_ref) at its own CPU-runnable configuration
                    cfg1, and the C port of it (oracle/) on a bounded sample of the headline workload
 --impl reference times the unmodified reference itself on the headline workload: its Triton path on one GPU when it
@@ -274,6 +275,29 @@ def triton_baseline(dev, ours: dict, budget_s: float) -> dict:
         out["error"] = f"{type(e).__name__}: {e}"[:500]
     out["seconds"] = time.perf_counter() - t_begin
     return out
+
+
+def nsa_leg(dev, ours_cfg2_fwd_ms) -> dict:
+    """The NSA comparison of the reference's speed script (speed_test.py:157-215, 261-270): its NSA baseline (ref_nsa/,
+    staged unmodified; needs the flash-linear-attention package) timed beside the htree forward on the cfg2 tensors at
+    its script's budget (16 selected blocks of 64 tokens + the compressed blocks).  A competitor baseline, not part of
+    the operator; reported for completeness."""
+    from oracle import ref_triton
+    ok, why = ref_triton.available()
+    if not ok:
+        return {"unavailable": why}
+    c = dict(configs.CONFIGS["cfg2"])
+    try:
+        q, k, v, _ = configs.make_inputs(c, dev, seed=42, want_dO=False)
+        ms = ref_triton.time_nsa(q, k, v, block_size=64, block_counts=16, warmup=2, iters=2)
+        res = {"workload": "cfg2 tensors: " + configs.describe(c), "nsa": "parallel_nsa(block_size=64, block_counts=16, zero compression gate)",
+               "nsa_forward_ms": ms, "htree_forward_ms": ours_cfg2_fwd_ms,
+               "htree_over_nsa": (ms / ours_cfg2_fwd_ms) if ours_cfg2_fwd_ms else None}
+        del q, k, v
+        torch.cuda.empty_cache()
+        return res
+    except Exception as e:
+        return {"unavailable": f"{type(e).__name__}: {e}"[:400]}
 
 
 # --------------------------------------------------------------------------------------------- GPU helpers
@@ -633,6 +657,7 @@ def main():
                 ours["cfg2_fwd_ms"] = wl["cfg2"]["forward_ms"]
             if not args.no_triton:
                 line["triton_baseline"] = triton_baseline(dev, ours, args.triton_seconds)
+                line["nsa_baseline"] = nsa_leg(dev, ours.get("cfg2_fwd_ms"))
         if not args.no_cpu_baseline:
             tps, info = cpu_oracle_leg(c, args.cpu_seconds)
             line["cpu_baseline"] = {"value": tps, "unit": "tokens/s", "cores": info["cores"], "kind": info["kind"],

@@ -17,6 +17,8 @@ FWD_GENERIC = 2
 FWD_FUSED = 4
 FWD_TILED = 8
 PARENTS_U16 = 16
+BWD_KEEP_ACCUM = 32
+BWD_NO_FOLD = 64
 
 # every exported symbol of include/htree_b200.h; tests check that the library exports all of them
 SYMBOLS = (

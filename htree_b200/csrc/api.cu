@@ -92,7 +92,7 @@ const char* htree_b200_error_string(int code) {
         case HTREE_E_ALIGN: return "pointers must be 16-byte aligned and K, V multiples of 8";
         case HTREE_E_UNSUPPORTED: return "shape not supported by the compiled kernels";
         case HTREE_E_NODEVICE: return "no usable CUDA device";
-        case HTREE_E_WINDOW: return "query window outside the sequence, or a window passed to the backward";
+        case HTREE_E_WINDOW: return "query window outside the sequence, or a backward window without HTREE_BWD_KEEP_ACCUM / HTREE_BWD_NO_FOLD";
         case HTREE_E_SCRATCH: return "pooled tree levels do not fit the built-in scratch array (see htree_b200_static_scratch_bytes)";
         default: return code > 0 ? cudaGetErrorString((cudaError_t)code) : "unknown htree_b200 error";
     }
@@ -134,8 +134,8 @@ int htree_b200_build_tree(const HtreeShape* shape, void* const* layers_k, void* 
         }
     }
     if (layers_v_blk) {
-        if (shape->dtype == HTREE_F32 || (shape->V != 64 && shape->V != 128) ||
-            (shape->compression_rate != 8 && shape->compression_rate != 16))
+        if ((shape->V != 64 && shape->V != 128) || (shape->compression_rate != 8 && shape->compression_rate != 16) ||
+            (shape->dtype == HTREE_F32 && shape->V != 64))
             return HTREE_E_UNSUPPORTED;
         for (int l = 0; l < L; ++l) {
             if (!layers_v_blk[l]) return HTREE_E_NULL;
@@ -155,8 +155,8 @@ int htree_b200_block_values(const HtreeShape* shape, void* const* layers_v, void
     const int L = check_shape(shape, ln, false);
     if (L < 0) return L;
     if (!layers_v || !layers_v_blk) return HTREE_E_NULL;
-    if (shape->dtype == HTREE_F32 || (shape->V != 64 && shape->V != 128) ||
-        (shape->compression_rate != 8 && shape->compression_rate != 16))
+    if ((shape->V != 64 && shape->V != 128) || (shape->compression_rate != 8 && shape->compression_rate != 16) ||
+        (shape->dtype == HTREE_F32 && shape->V != 64))
         return HTREE_E_UNSUPPORTED;
     for (int l = 0; l < L; ++l) {
         if (!layers_v[l] || !layers_v_blk[l]) return HTREE_E_NULL;
@@ -289,7 +289,10 @@ int htree_b200_backward(const HtreeShape* shape, const void* q, void* const* lay
     } else if (!dq) {
         return HTREE_E_NULL;
     }
-    if (shape->T_q != 0 && (shape->T_q != shape->T || shape->t_offset != 0)) return HTREE_E_WINDOW;
+    // a query window is one part of a backward that the caller runs window by window over the same accumulators: only
+    // meaningful with the flags that say which part it is
+    const bool windowed = shape->T_q != 0 && (shape->T_q != shape->T || shape->t_offset != 0);
+    if (windowed && !(flags & (HTREE_BWD_KEEP_ACCUM | HTREE_BWD_NO_FOLD))) return HTREE_E_WINDOW;
     AttnParams p;
     int rc = fill_params(p, shape, L, ln, q, layers_k, layers_v, cos_cache, sin_cache, n_pos, scale, parents, status, flags);
     if (rc) return rc;
@@ -316,14 +319,14 @@ int htree_b200_backward(const HtreeShape* shape, const void* q, void* const* lay
                aligned32(cos_cache) && aligned32(sin_cache) && bwd_mma_supported(p, shape->dtype);
     }
     if (!fast && !bwd_generic_supported(p, shape->dtype)) return HTREE_E_UNSUPPORTED;
-    for (int l = 0; l < L; ++l) {   // gradient accumulators start at zero (src/backward.py:979-981)
+    for (int l = 0; l < L && !(flags & HTREE_BWD_KEEP_ACCUM); ++l) {   // gradient accumulators start at zero (src/backward.py:979-981)
         const size_t rows = (size_t)shape->B * ln[l] * shape->H_kv;
         cudaError_t e = cudaMemsetAsync(dk_levels[l], 0, rows * shape->K * sizeof(float), st);
         if (e == cudaSuccess) e = cudaMemsetAsync(dv_levels[l], 0, rows * shape->V * sizeof(float), st);
         if (e != cudaSuccess) return (int)e;
     }
     rc = fast ? launch_bwd_mma(p, shape->dtype, st) : launch_bwd_generic(p, shape->dtype, st);
-    if (rc) return rc;
+    if (rc || (flags & HTREE_BWD_NO_FOLD)) return rc;
     return launch_tree_backward(*shape, L, ln, dk_levels, dv_levels, st, typed ? typed->dk : nullptr, typed ? typed->dv : nullptr);
 }
 

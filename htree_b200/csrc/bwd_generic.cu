@@ -58,12 +58,12 @@ __global__ void __launch_bounds__(NTB) bwd_generic_kernel(const __grid_constant_
     float *Dg = m.hd, *gmx = m.hd + GP, *gsm = m.hd + 2 * GP;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int t = blockIdx.x;
+    const int t = p.t0 + blockIdx.x;                                         // query window: row blockIdx.x is position t0 + blockIdx.x
     const int b = blockIdx.y / p.Hkv, hk = blockIdx.y % p.Hkv;
     const int g_begin = blockIdx.z * 16;
     const int Gc = min(16, p.G - g_begin);                                   // heads of this chunk
-    const int64_t hbase = ((int64_t)b * p.T + t) * p.H + (int64_t)hk * p.G + g_begin;
-    const int64_t qidx = ((int64_t)b * p.T + t) * p.Hkv + hk;
+    const int64_t hbase = ((int64_t)b * p.Tq + blockIdx.x) * p.H + (int64_t)hk * p.G + g_begin;
+    const int64_t qidx = ((int64_t)b * p.Tq + blockIdx.x) * p.Hkv + hk;
     const T* qg = reinterpret_cast<const T*>(p.q) + hbase * K;
     const T* dOg = reinterpret_cast<const T*>(p.dO) + hbase * V;
     const T* og = reinterpret_cast<const T*>(p.out) + hbase * V;
@@ -311,7 +311,7 @@ static int launch_bt(const AttnParams& p, cudaStream_t st) {
     if (p.K / 2 > NTB || p.TK * p.CR > 65535) return HTREE_E_UNSUPPORTED;
     const size_t smem = bwd_smem_layout(p.K, p.V, GP, p.TK * p.CR, p.TK, nullptr, nullptr);
     if (smem > 227 * 1024) return HTREE_E_UNSUPPORTED;
-    dim3 grid(p.T, p.B * p.Hkv, (p.G + 15) / 16);
+    dim3 grid(p.Tq, p.B * p.Hkv, (p.G + 15) / 16);
     cudaError_t e;
 #define HT_LAUNCH(GPV)                                                                                              \
     e = cudaFuncSetAttribute(bwd_generic_kernel<T, GPV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \

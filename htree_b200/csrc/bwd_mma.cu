@@ -33,49 +33,77 @@ constexpr int MWB = HTREE_BWD_WARPS;   // warps (= queries) per block
 
 __host__ __device__ inline size_t bwd_mma_smem_per_warp(int TK) { return sizeof(int32_t) * 3 * (size_t)TK; }
 
+// T = float: split-half products (every operand carried as hi + lo half pairs, three MMAs per product; mma_common.cuh),
+// 64-wide heads; the K' levels then hold a hi and a lo plane, value rows are read as fp32 and split in registers.
 template <typename T, int D, bool ROT16, int NR, int CR>
 __global__ void HTREE_BWD_BOUNDS bwd_mma_kernel(const __grid_constant__ AttnParams p) {
+    constexpr bool X3 = std::is_same<T, float>::value;
     constexpr bool T1 = CR > 8;   // CR = children per parent: 16, or 8 (then tile 1 stays empty)
     constexpr int HALF = D / 2, KS = D / 16, PPT = HALF / 4, NV = PPT / 8, NOT = D / 8;
-    using F = Frag<T>;
+    using F = Frag<typename std::conditional<X3, __half, T>::type>;
     using FS = Frag<__half>;
     extern __shared__ __align__(16) unsigned char smem_raw[];
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, r = lane & 3;
     const int tl = blockIdx.x * MWB + warp;
-    if (tl >= p.T) return;                          // warps are independent (no block barrier anywhere)
-    const int t = tl;
+    if (tl >= p.Tq) return;                         // warps are independent (no block barrier anywhere)
+    const int t = p.t0 + tl;                        // query window: row tl of q / dO / out / dq is sequence position t0 + tl
     const int b = blockIdx.y / p.Hkv, hk = blockIdx.y % p.Hkv;
     const int G = p.G, TK = p.TK, L = p.L;
     int32_t* par = reinterpret_cast<int32_t*>(smem_raw + (size_t)warp * bwd_mma_smem_per_warp(TK));
     int32_t* nsel = par + TK;
     uint32_t* keptw = reinterpret_cast<uint32_t*>(nsel + TK);
 
-    const int64_t hbase = ((int64_t)b * p.T + t) * p.H + (int64_t)hk * G;
-    const int64_t qidx = ((int64_t)b * p.T + t) * p.Hkv + hk;
+    const int64_t hbase = ((int64_t)b * p.Tq + tl) * p.H + (int64_t)hk * G;
+    const int64_t qidx = ((int64_t)b * p.Tq + tl) * p.Hkv + hk;
     const bool row_ok[2] = {g < G, NR == 2 && g + 8 < G};   // NR = 1: at most 8 heads, rows g+8 are padding
 
-    uint32_t qraw[2][2][KS], dOraw[2][2][KS];
-    load_rows_half<T, D>(reinterpret_cast<const T*>(p.q) + hbase * D, g, r, row_ok, qraw);
+    // 16-bit types: qraw = IEEE half pairs, dOraw = storage-type pairs.  fp32: qraw = the float bits of q; dOraw / dOlo =
+    // the hi and lo half pairs of dO.
+    uint32_t qraw[2][2][X3 ? 2 * KS : KS], dOraw[2][2][KS], dOlo[2][2][X3 ? KS : 1];
     constexpr bool rot16 = ROT16;   // packed-half rotations (needs the pre-scaled half tables)
-    load_rows<T, D>(reinterpret_cast<const T*>(p.dO) + hbase * D, g, r, row_ok, dOraw);
     float Drow[2], gmx[2], ginv[2];
-    {   // D = sum_v dO * out over the whole row (src/naive.py:333); this thread holds 32 of the 128 columns
+    if constexpr (X3) {
+        load_rows_f32<D>(reinterpret_cast<const float*>(p.q) + hbase * D, g, r, row_ok, qraw);
+        uint32_t dOf[2][2][2 * KS], of[2][2][2 * KS];
+        load_rows_f32<D>(reinterpret_cast<const float*>(p.dO) + hbase * D, g, r, row_ok, dOf);
+        load_rows_f32<D>(reinterpret_cast<const float*>(p.out) + hbase * D, g, r, row_ok, of);
+#pragma unroll
+        for (int rr = 0; rr < 2; ++rr) {
+            float sdo = 0.f;
+#pragma unroll
+            for (int hf = 0; hf < 2; ++hf)
+#pragma unroll
+                for (int ks = 0; ks < KS; ++ks) {
+                    const float a0 = __uint_as_float(dOf[rr][hf][2 * ks]), a1 = __uint_as_float(dOf[rr][hf][2 * ks + 1]);
+                    sdo += a0 * __uint_as_float(of[rr][hf][2 * ks]) + a1 * __uint_as_float(of[rr][hf][2 * ks + 1]);
+                    split_half2(a0, a1, dOraw[rr][hf][ks], dOlo[rr][hf][ks]);
+                }
+            sdo += __shfl_xor_sync(0xffffffffu, sdo, 1);
+            sdo += __shfl_xor_sync(0xffffffffu, sdo, 2);
+            Drow[rr] = sdo;
+            gmx[rr] = row_ok[rr] ? p.gmax[hbase + g + 8 * rr] : 0.f;
+            ginv[rr] = row_ok[rr] ? 1.f / p.gsum[hbase + g + 8 * rr] : 0.f;
+        }
+    } else {
+        load_rows_half<T, D>(reinterpret_cast<const T*>(p.q) + hbase * D, g, r, row_ok, qraw);
+        load_rows<T, D>(reinterpret_cast<const T*>(p.dO) + hbase * D, g, r, row_ok, dOraw);
+        // D = sum_v dO * out over the whole row (src/naive.py:333); this thread holds 32 of the 128 columns
         uint32_t oraw[2][2][KS];
         load_rows<T, D>(reinterpret_cast<const T*>(p.out) + hbase * D, g, r, row_ok, oraw);
 #pragma unroll
         for (int rr = 0; rr < 2; ++rr) {
-            float s = 0.f;
+            float sdo = 0.f;
 #pragma unroll
             for (int hf = 0; hf < 2; ++hf)
 #pragma unroll
                 for (int ks = 0; ks < KS; ++ks) {
                     const float2 a = F::unpack(dOraw[rr][hf][ks]), o = F::unpack(oraw[rr][hf][ks]);
-                    s += a.x * o.x + a.y * o.y;
+                    sdo += a.x * o.x + a.y * o.y;
                 }
-            s += __shfl_xor_sync(0xffffffffu, s, 1);
-            s += __shfl_xor_sync(0xffffffffu, s, 2);
-            Drow[rr] = s;
+            sdo += __shfl_xor_sync(0xffffffffu, sdo, 1);
+            sdo += __shfl_xor_sync(0xffffffffu, sdo, 2);
+            Drow[rr] = sdo;
             gmx[rr] = row_ok[rr] ? p.gmax[hbase + g + 8 * rr] : 0.f;
             ginv[rr] = row_ok[rr] ? 1.f / p.gsum[hbase + g + 8 * rr] : 0.f;
         }
@@ -141,23 +169,52 @@ __global__ void HTREE_BWD_BOUNDS bwd_mma_kernel(const __grid_constant__ AttnPara
                 const int n0 = min(node0 + g, Nl - 1), n1 = min(node0 + 8 + g, Nl - 1);
                 const T* v0 = vq + (int64_t)n0 * rstride;
                 const T* v1 = vq + (int64_t)n1 * rstride;
-                uint32_t vb[2][2][KS];
+                if constexpr (X3) {
+                    // fp32 rows: 8 floats of each half per lane, split into hi / lo half pairs in registers
 #pragma unroll
-                for (int hf = 0; hf < 2; ++hf) {
-                    ldg_vec<NV>(v0 + hf * HALF, true, vb[0][hf], stream_rows);
-                    if (T1) ldg_vec<NV>(v1 + hf * HALF, true, vb[1][hf], stream_rows);
-                }
+                    for (int tl = 0; tl < (T1 ? 2 : 1); ++tl) {
+                        const T* vr = tl ? v1 : v0;
+                        uint32_t vf[2][8];
+                        ldg_vec<2>(vr, true, vf[0], stream_rows);
+                        ldg_vec<2>(vr + HALF, true, vf[1], stream_rows);
 #pragma unroll
-                for (int ks = 0; ks < KS; ++ks) {
-                    F::mma(dP0, dOraw[0][0][ks], dOraw[1][0][ks], dOraw[0][1][ks], dOraw[1][1][ks], vb[0][0][ks], vb[0][1][ks]);
-                    if (T1) F::mma(dP1, dOraw[0][0][ks], dOraw[1][0][ks], dOraw[0][1][ks], dOraw[1][1][ks], vb[1][0][ks], vb[1][1][ks]);
+                        for (int ks = 0; ks < KS; ++ks) {
+                            uint32_t bh[2], bl[2];
+#pragma unroll
+                            for (int hf = 0; hf < 2; ++hf) {
+                                const float x0 = fminf(fmaxf(__uint_as_float(vf[hf][2 * ks]), -65504.f), 65504.f);
+                                const float x1 = fminf(fmaxf(__uint_as_float(vf[hf][2 * ks + 1]), -65504.f), 65504.f);
+                                split_half2(x0, x1, bh[hf], bl[hf]);
+                            }
+                            float (&dP)[4] = tl ? dP1 : dP0;
+                            F::mma(dP, dOraw[0][0][ks], dOraw[1][0][ks], dOraw[0][1][ks], dOraw[1][1][ks], bh[0], bh[1]);
+                            F::mma(dP, dOraw[0][0][ks], dOraw[1][0][ks], dOraw[0][1][ks], dOraw[1][1][ks], bl[0], bl[1]);
+                            F::mma(dP, dOlo[0][0][ks], dOlo[1][0][ks], dOlo[0][1][ks], dOlo[1][1][ks], bh[0], bh[1]);
+                        }
+                    }
+                } else {
+                    uint32_t vb[2][2][KS];
+#pragma unroll
+                    for (int hf = 0; hf < 2; ++hf) {
+                        ldg_vec<NV>(v0 + hf * HALF, true, vb[0][hf], stream_rows);
+                        if (T1) ldg_vec<NV>(v1 + hf * HALF, true, vb[1][hf], stream_rows);
+                    }
+#pragma unroll
+                    for (int ks = 0; ks < KS; ++ks) {
+                        F::mma(dP0, dOraw[0][0][ks], dOraw[1][0][ks], dOraw[0][1][ks], dOraw[1][1][ks], vb[0][0][ks], vb[0][1][ks]);
+                        if (T1) F::mma(dP1, dOraw[0][0][ks], dOraw[1][0][ks], dOraw[0][1][ks], dOraw[1][1][ks], vb[1][0][ks], vb[1][1][ks]);
+                    }
                 }
             }
 
             // ---- S, the rotated-query fragments and the keys rotated back into q's frame ----
             float S0[4], S1[4];
-            uint32_t qa[KS][4], kr[2][2][KS];
-            score_chunk<D, true, ROT16, true, NR, CR>(p, kq, rstride, Nl, node0, delta, g, r, qraw, S0, S1, qa, kr, stream_rows);
+            uint32_t qa[KS][4], qal[X3 ? KS : 1][4];      // rotated-query A fragments (fp32: hi and lo)
+            uint32_t kr[2][2][X3 ? 1 : KS];                // 16-bit: keys rotated back, packed half pairs
+            float krf[2][2][X3 ? 2 * KS : 1];              // fp32: the same as floats
+            if constexpr (X3) score_chunk_x3<D, NR, CR, true>(p, kq, (int64_t)p.B * Nl * rstride, rstride, Nl, node0, delta, g, r, qraw, S0, S1,
+                                                             stream_rows, qa, qal, krf);
+            else score_chunk<D, true, ROT16, true, NR, CR>(p, kq, rstride, Nl, node0, delta, g, r, qraw, S0, S1, qa, kr, stream_rows);
 
             // ---- P and dS (src/naive.py:379-382), zero outside the accumulated set ----
             float P[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}}, dS[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
@@ -173,19 +230,55 @@ __global__ void HTREE_BWD_BOUNDS bwd_mma_kernel(const __grid_constant__ AttnPara
                         dS[rr][c] = on ? P[rr][c] * (dp[rr][c] - Drow[rr]) : 0.f;
                     }
             }
-            // A fragments of dS (heads x children) and, transposed with movmatrix, of dS^T and P^T (children x heads)
-            const uint32_t ds0 = FS::pack(dS[0][0], dS[0][1]), ds1 = FS::pack(dS[1][0], dS[1][1]);
-            const uint32_t ds2 = FS::pack(dS[0][2], dS[0][3]), ds3 = FS::pack(dS[1][2], dS[1][3]);
-            const uint32_t dst0 = movmatrix_trans(ds0), dst1 = movmatrix_trans(ds2);
-            const uint32_t dst2 = movmatrix_trans(ds1), dst3 = movmatrix_trans(ds3);
-            const uint32_t pt0 = movmatrix_trans(F::pack(P[0][0], P[0][1])), pt1 = movmatrix_trans(F::pack(P[0][2], P[0][3]));
-            const uint32_t pt2 = movmatrix_trans(F::pack(P[1][0], P[1][1])), pt3 = movmatrix_trans(F::pack(P[1][2], P[1][3]));
+            // A fragments of dS (heads x children) and, transposed with movmatrix, of dS^T and P^T (children x heads);
+            // fp32 storage: hi parts in ds/dst/pt, lo parts in dsl/dstl/ptl
+            uint32_t ds[4], dsl[4] = {0u, 0u, 0u, 0u}, pp[4], ppl[4] = {0u, 0u, 0u, 0u};
+            if constexpr (X3) {
+                split_half2(dS[0][0], dS[0][1], ds[0], dsl[0]); split_half2(dS[1][0], dS[1][1], ds[1], dsl[1]);
+                split_half2(dS[0][2], dS[0][3], ds[2], dsl[2]); split_half2(dS[1][2], dS[1][3], ds[3], dsl[3]);
+                split_half2(P[0][0], P[0][1], pp[0], ppl[0]); split_half2(P[1][0], P[1][1], pp[1], ppl[1]);
+                split_half2(P[0][2], P[0][3], pp[2], ppl[2]); split_half2(P[1][2], P[1][3], pp[3], ppl[3]);
+            } else {
+                ds[0] = FS::pack(dS[0][0], dS[0][1]); ds[1] = FS::pack(dS[1][0], dS[1][1]);
+                ds[2] = FS::pack(dS[0][2], dS[0][3]); ds[3] = FS::pack(dS[1][2], dS[1][3]);
+                pp[0] = F::pack(P[0][0], P[0][1]); pp[1] = F::pack(P[1][0], P[1][1]);
+                pp[2] = F::pack(P[0][2], P[0][3]); pp[3] = F::pack(P[1][2], P[1][3]);
+            }
+            const uint32_t ds0 = ds[0], ds1 = ds[1], ds2 = ds[2], ds3 = ds[3];
+            const uint32_t dst0 = movmatrix_trans(ds[0]), dst1 = movmatrix_trans(ds[2]);
+            const uint32_t dst2 = movmatrix_trans(ds[1]), dst3 = movmatrix_trans(ds[3]);
+            const uint32_t pt0 = movmatrix_trans(pp[0]), pt1 = movmatrix_trans(pp[2]);
+            const uint32_t pt2 = movmatrix_trans(pp[1]), pt3 = movmatrix_trans(pp[3]);
+            uint32_t dstl[4] = {0u, 0u, 0u, 0u}, ptl[4] = {0u, 0u, 0u, 0u};
+            if constexpr (X3) {
+                dstl[0] = movmatrix_trans(dsl[0]); dstl[1] = movmatrix_trans(dsl[2]); dstl[2] = movmatrix_trans(dsl[1]); dstl[3] = movmatrix_trans(dsl[3]);
+                ptl[0] = movmatrix_trans(ppl[0]); ptl[1] = movmatrix_trans(ppl[2]); ptl[2] = movmatrix_trans(ppl[1]); ptl[3] = movmatrix_trans(ppl[3]);
+            }
 
             // ---- dq += dS K~: B fragments = the rotated keys of the score product, transposed in registers ----
 #pragma unroll
             for (int ks = 0; ks < KS; ++ks) {
-                FS::mma(dqa[2 * ks], ds0, ds1, ds2, ds3, movmatrix_trans(kr[0][0][ks]), movmatrix_trans(kr[1][0][ks]));
-                FS::mma(dqa[2 * ks + 1], ds0, ds1, ds2, ds3, movmatrix_trans(kr[0][1][ks]), movmatrix_trans(kr[1][1][ks]));
+                if constexpr (X3) {
+#pragma unroll
+                    for (int hf = 0; hf < 2; ++hf) {
+                        uint32_t k0h, k0l, k1h, k1l;
+                        split_half2(krf[0][hf][2 * ks], krf[0][hf][2 * ks + 1], k0h, k0l);
+                        split_half2(krf[1][hf][2 * ks], krf[1][hf][2 * ks + 1], k1h, k1l);
+                        const uint32_t b0h = movmatrix_trans(k0h), b1h = movmatrix_trans(k1h);
+                        const uint32_t b0l = movmatrix_trans(k0l), b1l = movmatrix_trans(k1l);
+                        // summed from zero, then added with a round-to-nearest fp32 add (the tensor core's accumulation
+                        // truncates; dq runs over every chunk of the query)
+                        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+                        FS::mma(acc, dsl[0], dsl[1], dsl[2], dsl[3], b0h, b1h);
+                        FS::mma(acc, ds0, ds1, ds2, ds3, b0l, b1l);
+                        FS::mma(acc, ds0, ds1, ds2, ds3, b0h, b1h);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) dqa[2 * ks + hf][i] += acc[i];
+                    }
+                } else {
+                    FS::mma(dqa[2 * ks], ds0, ds1, ds2, ds3, movmatrix_trans(kr[0][0][ks]), movmatrix_trans(kr[1][0][ks]));
+                    FS::mma(dqa[2 * ks + 1], ds0, ds1, ds2, ds3, movmatrix_trans(kr[0][1][ks]), movmatrix_trans(kr[1][1][ks]));
+                }
             }
 
             // ---- dK'[node0 + c] += dS^T q^_a and dV[node0 + c] += P^T dO, rows c = g and g + 8 ----
@@ -214,13 +307,31 @@ __global__ void HTREE_BWD_BOUNDS bwd_mma_kernel(const __grid_constant__ AttnPara
                 for (int u = 0; u < 2; ++u) {
                     const int ks = 2 * m + u;
                     float tl_[4] = {0.f, 0.f, 0.f, 0.f}, th_[4] = {0.f, 0.f, 0.f, 0.f};
-                    FS::mma(tl_, dst0, dst1, dst2, dst3, movmatrix_trans(qa[ks][0]), movmatrix_trans(qa[ks][1]));
-                    FS::mma(th_, dst0, dst1, dst2, dst3, movmatrix_trans(qa[ks][2]), movmatrix_trans(qa[ks][3]));
+                    float ul_[4] = {0.f, 0.f, 0.f, 0.f}, uh_[4] = {0.f, 0.f, 0.f, 0.f};
+                    const uint32_t q0 = movmatrix_trans(qa[ks][0]), q1 = movmatrix_trans(qa[ks][1]);
+                    const uint32_t q2 = movmatrix_trans(qa[ks][2]), q3 = movmatrix_trans(qa[ks][3]);
+                    const uint32_t o0 = movmatrix_trans(dOraw[0][0][ks]), o1 = movmatrix_trans(dOraw[1][0][ks]);
+                    const uint32_t o2 = movmatrix_trans(dOraw[0][1][ks]), o3 = movmatrix_trans(dOraw[1][1][ks]);
+                    FS::mma(tl_, dst0, dst1, dst2, dst3, q0, q1);
+                    FS::mma(th_, dst0, dst1, dst2, dst3, q2, q3);
+                    F::mma(ul_, pt0, pt1, pt2, pt3, o0, o1);
+                    F::mma(uh_, pt0, pt1, pt2, pt3, o2, o3);
+                    if constexpr (X3) {
+                        const uint32_t ql0 = movmatrix_trans(qal[ks][0]), ql1 = movmatrix_trans(qal[ks][1]);
+                        const uint32_t ql2 = movmatrix_trans(qal[ks][2]), ql3 = movmatrix_trans(qal[ks][3]);
+                        const uint32_t ol0 = movmatrix_trans(dOlo[0][0][ks]), ol1 = movmatrix_trans(dOlo[1][0][ks]);
+                        const uint32_t ol2 = movmatrix_trans(dOlo[0][1][ks]), ol3 = movmatrix_trans(dOlo[1][1][ks]);
+                        FS::mma(tl_, dst0, dst1, dst2, dst3, ql0, ql1);
+                        FS::mma(tl_, dstl[0], dstl[1], dstl[2], dstl[3], q0, q1);
+                        FS::mma(th_, dst0, dst1, dst2, dst3, ql2, ql3);
+                        FS::mma(th_, dstl[0], dstl[1], dstl[2], dstl[3], q2, q3);
+                        F::mma(ul_, pt0, pt1, pt2, pt3, ol0, ol1);
+                        F::mma(ul_, ptl[0], ptl[1], ptl[2], ptl[3], o0, o1);
+                        F::mma(uh_, pt0, pt1, pt2, pt3, ol2, ol3);
+                        F::mma(uh_, ptl[0], ptl[1], ptl[2], ptl[3], o2, o3);
+                    }
                     klo_[0][2 * u] = tl_[0]; klo_[0][2 * u + 1] = tl_[1]; klo_[1][2 * u] = tl_[2]; klo_[1][2 * u + 1] = tl_[3];
                     khi_[0][2 * u] = th_[0]; khi_[0][2 * u + 1] = th_[1]; khi_[1][2 * u] = th_[2]; khi_[1][2 * u + 1] = th_[3];
-                    float ul_[4] = {0.f, 0.f, 0.f, 0.f}, uh_[4] = {0.f, 0.f, 0.f, 0.f};
-                    F::mma(ul_, pt0, pt1, pt2, pt3, movmatrix_trans(dOraw[0][0][ks]), movmatrix_trans(dOraw[1][0][ks]));
-                    F::mma(uh_, pt0, pt1, pt2, pt3, movmatrix_trans(dOraw[0][1][ks]), movmatrix_trans(dOraw[1][1][ks]));
                     vlo_[0][2 * u] = ul_[0]; vlo_[0][2 * u + 1] = ul_[1]; vlo_[1][2 * u] = ul_[2]; vlo_[1][2 * u + 1] = ul_[3];
                     vhi_[0][2 * u] = uh_[0]; vhi_[0][2 * u + 1] = uh_[1]; vhi_[1][2 * u] = uh_[2]; vhi_[1][2 * u + 1] = uh_[3];
                 }
@@ -256,7 +367,7 @@ __global__ void HTREE_BWD_BOUNDS bwd_mma_kernel(const __grid_constant__ AttnPara
         if (!row_ok[rr]) continue;
 #pragma unroll
         for (int hf = 0; hf < 2; ++hf) {
-            if (p.dq_typed) {
+            if (!X3 && p.dq_typed) {
                 T* dqrow = reinterpret_cast<T*>(p.dq_typed) + (hbase + g + 8 * rr) * D + hf * HALF + PPT * r;
                 uint32_t w[PPT / 2];
 #pragma unroll
@@ -268,7 +379,8 @@ __global__ void HTREE_BWD_BOUNDS bwd_mma_kernel(const __grid_constant__ AttnPara
                 for (int i = 0; i < PPT / 8; ++i)
                     reinterpret_cast<uint4*>(dqrow)[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
             } else {
-                float4* dst = reinterpret_cast<float4*>(p.dq + (hbase + g + 8 * rr) * D + hf * HALF + PPT * r);
+                float* dqf = (X3 && p.dq_typed) ? reinterpret_cast<float*>(p.dq_typed) : p.dq;
+                float4* dst = reinterpret_cast<float4*>(dqf + (hbase + g + 8 * rr) * D + hf * HALF + PPT * r);
 #pragma unroll
                 for (int m = 0; m < KS / 2; ++m)
                     dst[m] = make_float4(dqa[2 * (2 * m) + hf][2 * rr], dqa[2 * (2 * m) + hf][2 * rr + 1],
@@ -314,8 +426,9 @@ __global__ void __launch_bounds__(256) finalize_grads_kernel(float* dk, float* d
 }
 
 bool bwd_mma_supported(const AttnParams& p, int dtype) {
-    if (dtype != HTREE_BF16 && dtype != HTREE_F16) return false;
+    if (dtype != HTREE_BF16 && dtype != HTREE_F16 && dtype != HTREE_F32) return false;
     if (p.K != p.V || (p.K != 64 && p.K != 128) || p.G > 16 || (p.CR != 16 && p.CR != 8)) return false;
+    if (dtype == HTREE_F32 && p.K != 64) return false;     // split-half kernels: 64-wide heads
     for (int l = 0; l < p.L; ++l) if (!p.lkr[l]) return false;
     return bwd_mma_smem_per_warp(p.TK) * MWB <= 200 * 1024;
 }
@@ -323,13 +436,14 @@ bool bwd_mma_supported(const AttnParams& p, int dtype) {
 template <typename T, int D, bool ROT16, int NR, int CR>
 static int launch_bwd_mma_cr(const AttnParams& p, cudaStream_t st) {
     const size_t smem = bwd_mma_smem_per_warp(p.TK) * MWB;
-    dim3 grid((p.T + MWB - 1) / MWB, p.B * p.Hkv);
+    dim3 grid((p.Tq + MWB - 1) / MWB, p.B * p.Hkv);
     cudaError_t e = cudaFuncSetAttribute(bwd_mma_kernel<T, D, ROT16, NR, CR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     bwd_mma_kernel<T, D, ROT16, NR, CR><<<grid, MWB * 32, smem, st>>>(p);
     note_launch();
     e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
+    if (p.flags & HTREE_BWD_NO_FOLD) return 0;      // more query windows follow: the accumulators stay in their private layout
     for (int l = 0; l < p.L; ++l) {
         const int64_t rows = (int64_t)p.B * p.ln[l] * p.Hkv;
         const unsigned blocks = (unsigned)((rows * (D / 8) + 255) / 256);
@@ -352,6 +466,7 @@ static int launch_bwd_mma_t(const AttnParams& p, cudaStream_t st) {
 }
 
 int launch_bwd_mma(const AttnParams& p, int dtype, cudaStream_t st) {
+    if (dtype == HTREE_F32) return launch_bwd_mma_t<float, 64, false>(p, st);
     const bool rot16 = p.cosh != nullptr && p.sinh != nullptr;
     if (p.K == 128) {
         if (dtype == HTREE_BF16) return rot16 ? launch_bwd_mma_t<__nv_bfloat16, 128, true>(p, st) : launch_bwd_mma_t<__nv_bfloat16, 128, false>(p, st);

@@ -64,8 +64,11 @@ __host__ __device__ inline size_t mma_smem_per_warp(int TK, int CR) {
 #define HTREE_SEL_MIN_BLOCKS 4   // the selection kernel carries no accumulators: 128 registers, 16 warps per SM
 #endif
 // NR = 1: groups of at most 8 heads (rows g+8 of every fragment are padding and their ALU work is skipped).
+// T = float: split-half products (mma_common.cuh), 64-wide heads; K' and the blocked values then hold a hi and a lo plane.
 template <typename T, int D, bool ROT16, int MODE, int NR, int CR>
-__global__ void __launch_bounds__(MW * 32, MODE == 1 ? HTREE_SEL_MIN_BLOCKS : HTREE_FWD_MIN_BLOCKS) fwd_mma_kernel(const __grid_constant__ AttnParams p) {
+__global__ void __launch_bounds__(MW * 32, MODE == 1 ? (std::is_same<T, float>::value ? 3 : HTREE_SEL_MIN_BLOCKS) : HTREE_FWD_MIN_BLOCKS)
+fwd_mma_kernel(const __grid_constant__ AttnParams p) {
+    constexpr bool X3 = std::is_same<T, float>::value;
     constexpr uint32_t kAllChildren = (1u << CR) - 1u;   // CR = children per parent: 16, or 8 (then tile 1 stays empty)
     constexpr int HALF = D / 2;
     constexpr int KS = D / 16;        // k-steps of the score product
@@ -73,7 +76,7 @@ __global__ void __launch_bounds__(MW * 32, MODE == 1 ? HTREE_SEL_MIN_BLOCKS : HT
     constexpr int NV = PPT / 8;       // 16-byte loads per (row, half): 2 for D=128, 1 for D=64
     constexpr int VB = D / 8;         // value columns one thread loads per row: one 32-byte (D=128) or 16-byte (D=64) piece
     constexpr int NOT = D / 8;        // n8 output tiles
-    using F = Frag<T>;          // P.V product: values stay in their storage type
+    using F = Frag<typename std::conditional<X3, __half, T>::type>;   // P.V product: values stay in their storage type (fp32: half planes)
     using FS = Frag<__half>;    // score product: rotated queries and K' are IEEE half for every storage type
     extern __shared__ __align__(16) unsigned char smem_raw[];
 
@@ -98,8 +101,9 @@ __global__ void __launch_bounds__(MW * 32, MODE == 1 ? HTREE_SEL_MIN_BLOCKS : HT
     const bool row_ok[2] = {g < G, NR == 2 && g + 8 < G};
 
     // raw queries of rows g and g+8: pairs [PPT*r, PPT*(r+1)) of the low and of the high half
-    uint32_t qraw[2][2][KS];
-    load_rows_half<T, D>(reinterpret_cast<const T*>(p.q) + hbase * D, g, r, row_ok, qraw);
+    uint32_t qraw[2][2][X3 ? 2 * KS : KS];     // 16-bit types: IEEE half pairs; fp32: the float bits
+    if constexpr (X3) load_rows_f32<D>(reinterpret_cast<const float*>(p.q) + hbase * D, g, r, row_ok, qraw);
+    else load_rows_half<T, D>(reinterpret_cast<const T*>(p.q) + hbase * D, g, r, row_ok, qraw);
     constexpr bool rot16 = ROT16;   // packed-half rotation where the Top-K is not being decided
 
     float O[NOT][4];
@@ -146,6 +150,7 @@ __global__ void __launch_bounds__(MW * 32, MODE == 1 ? HTREE_SEL_MIN_BLOCKS : HT
         const __half* kq = lkr + ((int64_t)b * Nl * p.Hkv + hk) * D + (D == 64 ? D / 4 : D / 8) * r;
         // blocked values of this level: block (b, parent, hk) holds CR*D elements, lane (g, r) owns words [(8r+g)*CHW, +CHW)
         const int64_t vb_stride = (int64_t)p.Hkv * (CR * D / 2);     // 32-bit words between consecutive parents
+        const int64_t vb_plane = (int64_t)p.B * ((Nl + CR - 1) / CR) * vb_stride;   // fp32 storage: words from the hi plane to the lo plane
         const uint32_t* vbq = reinterpret_cast<const uint32_t*>(p.lvb[l]) +
                               ((int64_t)b * ((Nl + CR - 1) / CR) * p.Hkv + hk) * (CR * D / 2) + (8 * r + g) * (NOT * (CR / 8));
         auto score = [&](int a, float (&S0)[4], float (&S1)[4], bool select) {
@@ -154,9 +159,13 @@ __global__ void __launch_bounds__(MW * 32, MODE == 1 ? HTREE_SEL_MIN_BLOCKS : HT
 #ifdef HTREE_KNOCK_L1ROWS   // timing experiments only: every gather hits the same rows (wrong results, no L2 latency)
             node0 = 0;
 #endif
-            uint32_t unused[1][4];
-            if (rot16 && !select) score_chunk<D, false, true, false, NR, CR>(p, kq, rstride, Nl, node0, rp - CR * a, g, r, qraw, S0, S1, unused, nullptr, stream_rows);
-            else score_chunk<D, false, false, false, NR, CR>(p, kq, rstride, Nl, node0, rp - CR * a, g, r, qraw, S0, S1, unused, nullptr, stream_rows);
+            if constexpr (X3) {
+                score_chunk_x3<D, NR, CR>(p, kq, (int64_t)p.B * Nl * rstride, rstride, Nl, node0, rp - CR * a, g, r, qraw, S0, S1, stream_rows);
+            } else {
+                uint32_t unused[1][4];
+                if (rot16 && !select) score_chunk<D, false, true, false, NR, CR>(p, kq, rstride, Nl, node0, rp - CR * a, g, r, qraw, S0, S1, unused, nullptr, stream_rows);
+                else score_chunk<D, false, false, false, NR, CR>(p, kq, rstride, Nl, node0, rp - CR * a, g, r, qraw, S0, S1, unused, nullptr, stream_rows);
+            }
         };
 
         // online-softmax accumulation of the columns in `mask` (bit c = child c of the parent at slot a)
@@ -171,7 +180,7 @@ __global__ void __launch_bounds__(MW * 32, MODE == 1 ? HTREE_SEL_MIN_BLOCKS : HT
             // value fragments first (longest latency): this lane's piece of the parent's blocked values, NOT*NB words
             // that ARE the B fragments of the P.V products; the warp reads the block front to back
             constexpr int NB = CR / 8, CHW = NOT * NB;
-            uint32_t vw[CHW];
+            uint32_t vw[CHW], vl[X3 ? CHW : 1];     // fp32 storage: hi plane and lo plane
             {
                 const uint32_t* src = vbq + (int64_t)pblk * vb_stride;
 #pragma unroll
@@ -180,6 +189,11 @@ __global__ void __launch_bounds__(MW * 32, MODE == 1 ? HTREE_SEL_MIN_BLOCKS : HT
                     if (stream_rows) ldg32_stream(src + 8 * i, t8); else ldg32(src + 8 * i, t8);
 #pragma unroll
                     for (int u = 0; u < 8; ++u) vw[8 * i + u] = t8[u];
+                    if constexpr (X3) {
+                        if (stream_rows) ldg32_stream(src + vb_plane + 8 * i, t8); else ldg32(src + vb_plane + 8 * i, t8);
+#pragma unroll
+                        for (int u = 0; u < 8; ++u) vl[8 * i + u] = t8[u];
+                    }
                 }
             }
             const float NINF = -INFINITY;
@@ -216,12 +230,30 @@ __global__ void __launch_bounds__(MW * 32, MODE == 1 ? HTREE_SEL_MIN_BLOCKS : HT
                     pr[rr][c] = __expf(s[rr][c] - m_run[rr]);
                     s_run[rr] += pr[rr][c];
                 }
-            const uint32_t pa0 = F::pack(pr[0][0], pr[0][1]), pa1 = F::pack(pr[1][0], pr[1][1]);
-            const uint32_t pa2 = F::pack(pr[0][2], pr[0][3]), pa3 = F::pack(pr[1][2], pr[1][3]);
             // output tile w, column c <-> value column VB*c + w (the blocked layout is built for exactly this mapping);
             // children that are not accumulated have probability 0, and every value of the block is finite
+            if constexpr (X3) {
+                uint32_t ph[4], pl[4];
+                split_half2(pr[0][0], pr[0][1], ph[0], pl[0]); split_half2(pr[1][0], pr[1][1], ph[1], pl[1]);
+                split_half2(pr[0][2], pr[0][3], ph[2], pl[2]); split_half2(pr[1][2], pr[1][3], ph[3], pl[3]);
+                // The chunk's three products are summed from zero and then added to the running output with an ordinary
+                // (round-to-nearest) fp32 add: the tensor core's own accumulation truncates, and over the ~10^3 chunks of a
+                // query that bias would reach 1e-4 relative.
 #pragma unroll
-            for (int w = 0; w < NOT; ++w) F::mma(O[w], pa0, pa1, pa2, pa3, vw[w * NB], NB == 2 ? vw[w * NB + 1] : 0u);
+                for (int w = 0; w < NOT; ++w) {
+                    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+                    F::mma(acc, pl[0], pl[1], pl[2], pl[3], vw[w * NB], NB == 2 ? vw[w * NB + 1] : 0u);
+                    F::mma(acc, ph[0], ph[1], ph[2], ph[3], vl[w * NB], NB == 2 ? vl[w * NB + 1] : 0u);
+                    F::mma(acc, ph[0], ph[1], ph[2], ph[3], vw[w * NB], NB == 2 ? vw[w * NB + 1] : 0u);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) O[w][i] += acc[i];
+                }
+            } else {
+                const uint32_t pa0 = F::pack(pr[0][0], pr[0][1]), pa1 = F::pack(pr[1][0], pr[1][1]);
+                const uint32_t pa2 = F::pack(pr[0][2], pr[0][3]), pa3 = F::pack(pr[1][2], pr[1][3]);
+#pragma unroll
+                for (int w = 0; w < NOT; ++w) F::mma(O[w], pa0, pa1, pa2, pa3, vw[w * NB], NB == 2 ? vw[w * NB + 1] : 0u);
+            }
         };
 
         if (l > 0 && kAccumulateKernel) {
@@ -381,6 +413,17 @@ __global__ void __launch_bounds__(MW * 32, MODE == 1 ? HTREE_SEL_MIN_BLOCKS : HT
     for (int rr = 0; rr < 2; ++rr) {
         if (!row_ok[rr]) continue;
         const float inv = 1.f / s_run[rr];
+        if constexpr (X3) {
+            // columns 2*VB*r + [0, VB) (element 2rr of the tiles) and the VB after them (element 2rr+1), as fp32
+            float* orow = reinterpret_cast<float*>(p.out) + (hbase + g + 8 * rr) * D + 2 * VB * r;
+#pragma unroll
+            for (int i = 0; i < VB / 4; ++i) {
+                reinterpret_cast<float4*>(orow)[i] = make_float4(O[4 * i][2 * rr] * inv, O[4 * i + 1][2 * rr] * inv, O[4 * i + 2][2 * rr] * inv, O[4 * i + 3][2 * rr] * inv);
+                reinterpret_cast<float4*>(orow + VB)[i] = make_float4(O[4 * i][2 * rr + 1] * inv, O[4 * i + 1][2 * rr + 1] * inv, O[4 * i + 2][2 * rr + 1] * inv, O[4 * i + 3][2 * rr + 1] * inv);
+            }
+            if (r == 0) { p.gmax[hbase + g + 8 * rr] = m_true[rr]; p.gsum[hbase + g + 8 * rr] = s_run[rr] * __expf(m_run[rr] - m_true[rr]); }
+            continue;
+        }
         T* orow = reinterpret_cast<T*>(p.out) + (hbase + g + 8 * rr) * D;
         // this thread owns columns 2*VB*r + [0, VB) (element 2rr of tiles 0..VB-1) and the VB after them (element 2rr+1)
         uint32_t wlo[VB / 2], whi[VB / 2];
@@ -437,8 +480,9 @@ static int launch_mma_td(const AttnParams& p, cudaStream_t st) {
 }
 
 bool fwd_mma_supported(const AttnParams& p, int dtype) {
-    if (dtype != HTREE_BF16 && dtype != HTREE_F16) return false;
+    if (dtype != HTREE_BF16 && dtype != HTREE_F16 && dtype != HTREE_F32) return false;
     if (p.K != p.V || (p.K != 64 && p.K != 128)) return false;
+    if (dtype == HTREE_F32 && p.K != 64) return false;     // split-half kernels: 64-wide heads
     if (p.G > 16 || (p.CR != 16 && p.CR != 8)) return false;
     for (int l = 0; l < p.L; ++l) if (!p.lkr[l]) return false;
     if (!(p.flags & HTREE_FWD_SELECT_ONLY))
@@ -447,6 +491,7 @@ bool fwd_mma_supported(const AttnParams& p, int dtype) {
 }
 
 int launch_fwd_mma(const AttnParams& p, int dtype, cudaStream_t st) {
+    if (dtype == HTREE_F32) return launch_mma_tdr<float, 64, false>(p, st);
     if (dtype == HTREE_BF16) return p.K == 128 ? launch_mma_td<__nv_bfloat16, 128>(p, st) : launch_mma_td<__nv_bfloat16, 64>(p, st);
     return p.K == 128 ? launch_mma_td<__half, 128>(p, st) : launch_mma_td<__half, 64>(p, st);
 }

@@ -270,4 +270,107 @@ __device__ __forceinline__ void load_rows_half(const T* base, int g, int r, cons
     }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// fp32 storage on the tensor cores: split-half products.  A value x is carried as hi = half(x) and lo = half(x - hi)
+// (22 significand bits together); a product of two such values is formed as hi*hi + hi*lo + lo*hi by three
+// mma.sync.m16n8k16 f16 instructions with fp32 accumulation (lo*lo is below fp32 resolution).  This keeps the scores,
+// and with them the Top-K decisions, at fp32 accuracy, which single TF32 / half products (10-11 bits) do not.
+// 64-wide heads only: the fp32 query rows already take 32 registers per thread.
+
+// two floats -> packed (hi, hi) and (lo, lo) half pairs
+__device__ __forceinline__ void split_half2(float x0, float x1, uint32_t& hi, uint32_t& lo) {
+    const __half2 h = __floats2half2_rn(x0, x1);
+    const float2 f = __half22float2(h);
+    const __half2 l = __floats2half2_rn(x0 - f.x, x1 - f.y);
+    hi = *reinterpret_cast<const uint32_t*>(&h);
+    lo = *reinterpret_cast<const uint32_t*>(&l);
+}
+
+// fp32 rows g and g+8 of a [heads, D] block: raw[rr][hf][i] = bits of element hf*D/2 + PPT*r + i (zero for rows beyond the group)
+template <int D>
+__device__ __forceinline__ void load_rows_f32(const float* base, int g, int r, const bool (&row_ok)[2], uint32_t (&raw)[2][2][D / 8]) {
+    constexpr int HALF = D / 2, PPT = HALF / 4;
+    static_assert(PPT == 8, "split-half kernels are built for 64-wide heads");
+#pragma unroll
+    for (int rr = 0; rr < 2; ++rr)
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) ldg_vec<2>(base + (int64_t)(g + 8 * rr) * D + hf * HALF + PPT * r, row_ok[rr], raw[rr][hf]);
+}
+
+// score_chunk for fp32 storage, D = 64.  kq points at this lane's piece of the hi plane of K' (plane elements further: the
+// lo plane); qf holds the fp32 query rows (load_rows_f32).  The query is rotated and scaled in fp32, then split.
+// With KEEP (backward) the rotated-query fragments (qa_hi/qa_lo [ks][4]) and the keys rotated back into the query's
+// frame (fp32, kr[tile][half][2*ks + {0,1}]) are returned as well.
+template <int D, int NR, int CR, bool KEEP = false>
+__device__ __forceinline__ void score_chunk_x3(const AttnParams& p, const __half* kq, int64_t plane, int rstride, int Nl, int node0,
+                                               int delta, int g, int r, const uint32_t (&qf)[2][2][D / 8], float (&S0)[4],
+                                               float (&S1)[4], bool stream, uint32_t (*qa_hi)[4] = nullptr,
+                                               uint32_t (*qa_lo)[4] = nullptr, float (*kr)[2][D / 8] = nullptr) {
+    constexpr int HALF = D / 2, KS = D / 16, PPT = HALF / 4;
+    constexpr bool T1 = CR > 8;
+    using FS = Frag<__half>;
+    const int n0 = min(node0 + g, Nl - 1), n1 = min(node0 + 8 + g, Nl - 1);
+    uint32_t kh[2][2][KS], kl[2][2][KS];   // [tile][half][k-step], hi and lo planes
+    {
+        uint32_t t0[8], t1[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u}, u0[8], u1[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+        const __half* k0 = kq + (int64_t)n0 * rstride;
+        const __half* k1 = kq + (int64_t)n1 * rstride;
+        ldg_vec<2>(k0, true, t0, stream); ldg_vec<2>(k0 + plane, true, u0, stream);
+        if (T1) { ldg_vec<2>(k1, true, t1, stream); ldg_vec<2>(k1 + plane, true, u1, stream); }
+#pragma unroll
+        for (int i = 0; i < KS; ++i) {
+            kh[0][0][i] = t0[i]; kh[0][1][i] = t0[4 + i]; kh[1][0][i] = t1[i]; kh[1][1][i] = t1[4 + i];
+            kl[0][0][i] = u0[i]; kl[0][1][i] = u0[4 + i]; kl[1][0][i] = u1[i]; kl[1][1][i] = u1[4 + i];
+        }
+    }
+    float cs[PPT], sn[PPT];
+    {
+        const float4* cp = reinterpret_cast<const float4*>(p.cosc + (size_t)delta * HALF + PPT * r);
+        const float4* sp = reinterpret_cast<const float4*>(p.sinc + (size_t)delta * HALF + PPT * r);
+#pragma unroll
+        for (int i = 0; i < PPT / 4; ++i) {
+            const float4 c4 = __ldg(cp + i), s4 = __ldg(sp + i);
+            cs[4 * i] = c4.x * p.scale; cs[4 * i + 1] = c4.y * p.scale; cs[4 * i + 2] = c4.z * p.scale; cs[4 * i + 3] = c4.w * p.scale;
+            sn[4 * i] = s4.x * p.scale; sn[4 * i + 1] = s4.y * p.scale; sn[4 * i + 2] = s4.z * p.scale; sn[4 * i + 3] = s4.w * p.scale;
+        }
+    }
+    float A0[4] = {0.f, 0.f, 0.f, 0.f}, B0[4] = {0.f, 0.f, 0.f, 0.f}, C0[4] = {0.f, 0.f, 0.f, 0.f};
+    float A1[4] = {0.f, 0.f, 0.f, 0.f}, B1[4] = {0.f, 0.f, 0.f, 0.f}, C1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) {
+        uint32_t ah[4] = {0u, 0u, 0u, 0u}, al[4] = {0u, 0u, 0u, 0u};
+        const float c0 = cs[2 * ks], c1 = cs[2 * ks + 1], s0 = sn[2 * ks], s1 = sn[2 * ks + 1];
+#pragma unroll
+        for (int rr = 0; rr < NR; ++rr) {
+            const float lx = __uint_as_float(qf[rr][0][2 * ks]), ly = __uint_as_float(qf[rr][0][2 * ks + 1]);
+            const float hx = __uint_as_float(qf[rr][1][2 * ks]), hy = __uint_as_float(qf[rr][1][2 * ks + 1]);
+            split_half2(lx * c0 - hx * s0, ly * c1 - hy * s1, ah[rr], al[rr]);              // rotated low half
+            split_half2(lx * s0 + hx * c0, ly * s1 + hy * c1, ah[2 + rr], al[2 + rr]);      // rotated high half
+        }
+        if (KEEP) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { qa_hi[ks][i] = ah[i]; qa_lo[ks][i] = al[i]; }
+#pragma unroll
+            for (int tl = 0; tl < 2; ++tl) {
+                if (!T1 && tl == 1) { kr[1][0][2 * ks] = kr[1][0][2 * ks + 1] = kr[1][1][2 * ks] = kr[1][1][2 * ks + 1] = 0.f; continue; }
+                const float2 lh = FS::unpack(kh[tl][0][ks]), ll = FS::unpack(kl[tl][0][ks]);
+                const float2 hh = FS::unpack(kh[tl][1][ks]), hl = FS::unpack(kl[tl][1][ks]);
+                const float klx = lh.x + ll.x, kly = lh.y + ll.y, khx = hh.x + hl.x, khy = hh.y + hl.y;
+                kr[tl][0][2 * ks] = klx * c0 + khx * s0; kr[tl][0][2 * ks + 1] = kly * c1 + khy * s1;      // scale * R(-delta) K'
+                kr[tl][1][2 * ks] = khx * c0 - klx * s0; kr[tl][1][2 * ks + 1] = khy * c1 - kly * s1;
+            }
+        }
+        FS::mma(A0, ah[0], ah[1], ah[2], ah[3], kh[0][0][ks], kh[0][1][ks]);
+        FS::mma(B0, ah[0], ah[1], ah[2], ah[3], kl[0][0][ks], kl[0][1][ks]);
+        FS::mma(C0, al[0], al[1], al[2], al[3], kh[0][0][ks], kh[0][1][ks]);
+        if (T1) {
+            FS::mma(A1, ah[0], ah[1], ah[2], ah[3], kh[1][0][ks], kh[1][1][ks]);
+            FS::mma(B1, ah[0], ah[1], ah[2], ah[3], kl[1][0][ks], kl[1][1][ks]);
+            FS::mma(C1, al[0], al[1], al[2], al[3], kh[1][0][ks], kh[1][1][ks]);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { S0[i] = A0[i] + (B0[i] + C0[i]); S1[i] = A1[i] + (B1[i] + C1[i]); }
+}
+
 }  // namespace htree

@@ -138,6 +138,7 @@ struct RotArgs {
     const float* cosc;
     const float* sinc;
     int64_t total;     // rows * (K/16): one thread rotates 8 pairs
+    int64_t plane;     // fp32 storage only: elements between the hi plane and the lo plane of the destination
     int32_t Hkv, K, N, CR;
 };
 
@@ -184,16 +185,56 @@ __global__ void __launch_bounds__(256) rotate_keys_kernel(const __grid_constant_
     }
 }
 
+// fp32 storage, 64-wide rows: K' = R(node % CR) K in fp32, written as TWO IEEE-half planes hi = half(K'), lo = half(K' - hi)
+// (plane 1 follows plane 0, each shaped and ordered like the 16-bit K' of 64-wide rows).  hi + lo carries 22 significand
+// bits; the split-half tensor-core kernels form q.k as q_hi.k_hi + q_hi.k_lo + q_lo.k_hi with fp32 accumulation.
+__global__ void __launch_bounds__(256) rotate_keys_split_kernel(const __grid_constant__ RotArgs a) {
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= a.total) return;
+    const int half = a.K >> 1, cpr = half >> 3;
+    const int ch = (int)(idx % cpr);
+    const int64_t row = idx / cpr;
+    const int node = (int)((row / a.Hkv) % a.N);
+    const int c = node % a.CR;
+    const float* src = reinterpret_cast<const float*>(a.src) + row * a.K + 8 * ch;
+    float lo[8], hi[8], cs[8], sn[8];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const float4 x = __ldg(reinterpret_cast<const float4*>(src) + i), y = __ldg(reinterpret_cast<const float4*>(src + half) + i);
+        lo[4 * i] = x.x; lo[4 * i + 1] = x.y; lo[4 * i + 2] = x.z; lo[4 * i + 3] = x.w;
+        hi[4 * i] = y.x; hi[4 * i + 1] = y.y; hi[4 * i + 2] = y.z; hi[4 * i + 3] = y.w;
+        const float4 cc = __ldg(reinterpret_cast<const float4*>(a.cosc + (int64_t)c * half + 8 * ch) + i);
+        const float4 ss = __ldg(reinterpret_cast<const float4*>(a.sinc + (int64_t)c * half + 8 * ch) + i);
+        cs[4 * i] = cc.x; cs[4 * i + 1] = cc.y; cs[4 * i + 2] = cc.z; cs[4 * i + 3] = cc.w;
+        sn[4 * i] = ss.x; sn[4 * i + 1] = ss.y; sn[4 * i + 2] = ss.z; sn[4 * i + 3] = ss.w;
+    }
+    float olo[8], ohi[8], rlo[8], rhi[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const float x = fminf(fmaxf(lo[i] * cs[i] - hi[i] * sn[i], -65504.f), 65504.f);
+        const float y = fminf(fmaxf(lo[i] * sn[i] + hi[i] * cs[i], -65504.f), 65504.f);
+        olo[i] = __half2float(__float2half_rn(x)); rlo[i] = x - olo[i];
+        ohi[i] = __half2float(__float2half_rn(y)); rhi[i] = y - ohi[i];
+    }
+    // 64-wide rows: chunk ch holds its 8 low pairs then its 8 high pairs (see rotate_keys_kernel)
+    __half* p0 = reinterpret_cast<__half*>(a.dst) + row * a.K + 16 * ch;
+    __half* p1 = p0 + a.plane;
+    *reinterpret_cast<uint4*>(p0) = pack16<__half>(olo); *reinterpret_cast<uint4*>(p0 + 8) = pack16<__half>(ohi);
+    *reinterpret_cast<uint4*>(p1) = pack16<__half>(rlo); *reinterpret_cast<uint4*>(p1 + 8) = pack16<__half>(rhi);
+}
+
 int launch_rotate_keys(const HtreeShape& s, int L, const int32_t* ln, void* const* lk, void* const* lkr, const float* cosc,
                        const float* sinc, cudaStream_t st) {
-    if (s.dtype == HTREE_F32 || (s.K % 16) != 0) return HTREE_E_UNSUPPORTED;
+    if ((s.K % 16) != 0 || (s.dtype == HTREE_F32 && s.K != 64)) return HTREE_E_UNSUPPORTED;
     for (int l = 0; l < L; ++l) {
         RotArgs a;
         a.src = lk[l]; a.dst = lkr[l]; a.cosc = cosc; a.sinc = sinc;
         a.Hkv = s.H_kv; a.K = s.K; a.N = ln[l]; a.CR = s.compression_rate;
         a.total = (int64_t)s.B * ln[l] * s.H_kv * (s.K / 16);
+        a.plane = (int64_t)s.B * ln[l] * s.H_kv * s.K;
         const unsigned grid = (unsigned)((a.total + 255) / 256);
-        if (s.dtype == HTREE_BF16) rotate_keys_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(a);
+        if (s.dtype == HTREE_F32) rotate_keys_split_kernel<<<grid, 256, 0, st>>>(a);
+        else if (s.dtype == HTREE_BF16) rotate_keys_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(a);
         else rotate_keys_kernel<__half><<<grid, 256, 0, st>>>(a);
         note_launch();
         cudaError_t e = cudaGetLastError();
@@ -206,6 +247,7 @@ struct BlkArgs {
     const void* src;
     void* dst;
     int64_t total;     // B * NBLK * Hkv * 32: one thread writes the piece one lane of the attention kernels reads
+    int64_t plane;     // fp32 storage only: elements between the hi plane and the lo plane of the destination
     int32_t Hkv, N, NBLK;
 };
 
@@ -216,7 +258,8 @@ struct BlkArgs {
 //   word ((r*8 + g)*NOT + w)*NB + j  =  { V[p*CR + 8j + 2r][VB*g + w],  V[p*CR + 8j + 2r + 1][VB*g + w] }
 // with r = 0..3, g = 0..7, w = 0..NOT-1 (NOT = VB = D/8 output tiles), j = 0..NB-1 (NB = CR/8 registers per tile).
 // Rows beyond the end of the level are zero.  16-bit storage types; the values are copied bit for bit.
-template <int D, int CR>
+// SPLIT (fp32 storage): the source rows are fp32 and two planes are written, hi = half(v) and lo = half(v - hi).
+template <int D, int CR, bool SPLIT>
 __global__ void __launch_bounds__(256) block_values_kernel(const __grid_constant__ BlkArgs a) {
     constexpr int NOT = D / 8, NB = CR / 8, CHW = NOT * NB;     // CHW 32-bit words per lane
     const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -226,45 +269,71 @@ __global__ void __launch_bounds__(256) block_values_kernel(const __grid_constant
     const int h = (int)(blk % a.Hkv);
     const int p = (int)((blk / a.Hkv) % a.NBLK);
     const int64_t b = blk / ((int64_t)a.Hkv * a.NBLK);
-    const uint16_t* src = reinterpret_cast<const uint16_t*>(a.src);
-    uint16_t e[NB][2][NOT];
+    uint16_t e[NB][2][NOT], elo[SPLIT ? NB : 1][2][NOT];
 #pragma unroll
     for (int j = 0; j < NB; ++j)
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
             const int row = p * CR + 8 * j + 2 * r + u;
             const bool ok = row < a.N;
-            const uint4* rp = reinterpret_cast<const uint4*>(src + (((b * a.N + (ok ? row : 0)) * a.Hkv + h) * (int64_t)D + NOT * g));
+            const int64_t off = ((b * a.N + (ok ? row : 0)) * a.Hkv + h) * (int64_t)D + NOT * g;
+            if (SPLIT) {
+                const float4* rp = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.src) + off);
 #pragma unroll
-            for (int i = 0; i < NOT / 8; ++i) {
-                uint4 x = make_uint4(0u, 0u, 0u, 0u);
-                if (ok) x = __ldg(rp + i);
-                const uint32_t w4[4] = {x.x, x.y, x.z, x.w};
+                for (int i = 0; i < NOT / 4; ++i) {
+                    float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (ok) x = __ldg(rp + i);
+                    const float f4[4] = {x.x, x.y, x.z, x.w};
 #pragma unroll
-                for (int q = 0; q < 4; ++q) { e[j][u][8 * i + 2 * q] = (uint16_t)(w4[q] & 0xffffu); e[j][u][8 * i + 2 * q + 1] = (uint16_t)(w4[q] >> 16); }
+                    for (int q = 0; q < 4; ++q) {
+                        const float v = fminf(fmaxf(f4[q], -65504.f), 65504.f);
+                        const __half hv = __float2half_rn(v);
+                        const __half lv = __float2half_rn(v - __half2float(hv));
+                        e[j][u][4 * i + q] = __half_as_ushort(hv);
+                        elo[SPLIT ? j : 0][u][4 * i + q] = __half_as_ushort(lv);
+                    }
+                }
+            } else {
+                const uint4* rp = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(a.src) + off);
+#pragma unroll
+                for (int i = 0; i < NOT / 8; ++i) {
+                    uint4 x = make_uint4(0u, 0u, 0u, 0u);
+                    if (ok) x = __ldg(rp + i);
+                    const uint32_t w4[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) { e[j][u][8 * i + 2 * q] = (uint16_t)(w4[q] & 0xffffu); e[j][u][8 * i + 2 * q + 1] = (uint16_t)(w4[q] >> 16); }
+                }
             }
         }
     uint32_t* dst = reinterpret_cast<uint32_t*>(a.dst) + blk * (int64_t)(CR * D / 2) + (int64_t)slot * CHW;
-    uint32_t o[CHW];
 #pragma unroll
-    for (int w = 0; w < NOT; ++w)
+    for (int pl = 0; pl < (SPLIT ? 2 : 1); ++pl) {
+        uint32_t o[CHW];
 #pragma unroll
-        for (int j = 0; j < NB; ++j) o[w * NB + j] = (uint32_t)e[j][0][w] | ((uint32_t)e[j][1][w] << 16);
+        for (int w = 0; w < NOT; ++w)
 #pragma unroll
-    for (int i = 0; i < CHW / 4; ++i) reinterpret_cast<uint4*>(dst)[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+            for (int j = 0; j < NB; ++j)
+                o[w * NB + j] = pl == 0 ? ((uint32_t)e[j][0][w] | ((uint32_t)e[j][1][w] << 16))
+                                        : ((uint32_t)elo[SPLIT ? j : 0][0][w] | ((uint32_t)elo[SPLIT ? j : 0][1][w] << 16));
+        uint32_t* d = dst + (pl ? a.plane / 2 : 0);
+#pragma unroll
+        for (int i = 0; i < CHW / 4; ++i) reinterpret_cast<uint4*>(d)[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+    }
 }
 
 int launch_block_values(const HtreeShape& s, int L, const int32_t* ln, void* const* lv, void* const* lvb, cudaStream_t st) {
     const int CR = s.compression_rate, D = s.V;
-    if (s.dtype == HTREE_F32 || (D != 64 && D != 128) || (CR != 8 && CR != 16)) return HTREE_E_UNSUPPORTED;
+    if ((D != 64 && D != 128) || (CR != 8 && CR != 16) || (s.dtype == HTREE_F32 && D != 64)) return HTREE_E_UNSUPPORTED;
     for (int l = 0; l < L; ++l) {
         BlkArgs a;
         a.src = lv[l]; a.dst = lvb[l];
         a.Hkv = s.H_kv; a.N = ln[l]; a.NBLK = (ln[l] + CR - 1) / CR;
         a.total = (int64_t)s.B * a.NBLK * s.H_kv * 32;
+        a.plane = (int64_t)s.B * a.NBLK * s.H_kv * CR * D;
         const unsigned grid = (unsigned)((a.total + 255) / 256);
-        if (D == 128) { if (CR == 16) block_values_kernel<128, 16><<<grid, 256, 0, st>>>(a); else block_values_kernel<128, 8><<<grid, 256, 0, st>>>(a); }
-        else { if (CR == 16) block_values_kernel<64, 16><<<grid, 256, 0, st>>>(a); else block_values_kernel<64, 8><<<grid, 256, 0, st>>>(a); }
+        if (s.dtype == HTREE_F32) { if (CR == 16) block_values_kernel<64, 16, true><<<grid, 256, 0, st>>>(a); else block_values_kernel<64, 8, true><<<grid, 256, 0, st>>>(a); }
+        else if (D == 128) { if (CR == 16) block_values_kernel<128, 16, false><<<grid, 256, 0, st>>>(a); else block_values_kernel<128, 8, false><<<grid, 256, 0, st>>>(a); }
+        else { if (CR == 16) block_values_kernel<64, 16, false><<<grid, 256, 0, st>>>(a); else block_values_kernel<64, 8, false><<<grid, 256, 0, st>>>(a); }
         note_launch();
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) return (int)e;

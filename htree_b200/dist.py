@@ -109,8 +109,13 @@ def build_tree_sequence_parallel(k: torch.Tensor, v: torch.Tensor, compression_r
     k, v are the full (replicated) leaves [B,T,H_kv,*].  Returns full-length (layers_k, layers_v) in local memory.
     `_build(k, v, compression_rate, max_top_nodes)` replaces the CUDA tree build in host-only tests.
     `ranges`: per-rank leaf ranges [(t0, t1), ...] (multiples of compression_rate^(levels-1)); default = even split.
-    With uneven ranges every rank pads its pooled slices to the longest one for the all-gather."""
+
+    Even ranges of a single sequence (B == 1) take the direct route: every rank pools its leaves straight into its own
+    slot of the full-length level buffers and one in-place all_gather_into_tensor per level and tensor completes them;
+    nothing is staged, padded or concatenated.  Uneven ranges (or B > 1, where a rank's slot is not one contiguous
+    piece) pad the pooled slices to the longest one for the all-gather and copy them into place."""
     import torch.distributed as dist
+    direct = _build is None
     if _build is None:
         from .ops import build_tree as _build
     build_tree = _build
@@ -127,6 +132,19 @@ def build_tree_sequence_parallel(k: torch.Tensor, v: torch.Tensor, compression_r
     t0, t1 = ranges[rank]
     grain = compression_rate ** (L - 1)
     assert all(a % grain == 0 and b % grain == 0 and b > a for a, b in ranges) and ranges[0][0] == 0 and ranges[-1][1] == T
+    span = t1 - t0
+    even = all(b - a == span for a, b in ranges)
+    if direct and even and B == 1:
+        from .ops import build_tree_into
+        layers_k = [k] + [torch.empty(B, n, H_kv, K, dtype=k.dtype, device=k.device) for n in sizes[1:]]
+        layers_v = [v] + [torch.empty(B, n, H_kv, v.shape[-1], dtype=v.dtype, device=v.device) for n in sizes[1:]]
+        slots_k = [layers_k[l][:, rank * (span // compression_rate ** l):(rank + 1) * (span // compression_rate ** l)] for l in range(1, L)]
+        slots_v = [layers_v[l][:, rank * (span // compression_rate ** l):(rank + 1) * (span // compression_rate ** l)] for l in range(1, L)]
+        build_tree_into(k[:, t0:t1], v[:, t0:t1], slots_k, slots_v, compression_rate, span // grain)
+        for l in range(1, L):
+            for full, slot in ((layers_k[l], slots_k[l - 1]), (layers_v[l], slots_v[l - 1])):
+                dist.all_gather_into_tensor(full.view(-1), slot.reshape(-1), group=group)   # in place: the slot is this rank's part of `full`
+        return layers_k, layers_v
     # pool the local slice to the same depth: its top level is this rank's share of the global top level
     lk, lv = build_tree(k[:, t0:t1].contiguous(), v[:, t0:t1].contiguous(), compression_rate, (t1 - t0) // grain)
     assert len(lk) == L
@@ -144,15 +162,33 @@ def build_tree_sequence_parallel(k: torch.Tensor, v: torch.Tensor, compression_r
             gathered = torch.empty((world * B,) + tuple(src.shape[1:]), dtype=src.dtype, device=src.device)
             dist.all_gather_into_tensor(gathered, src.contiguous(), group=group)   # rank-major along dim 0
             gathered = gathered.view(world, B, n_max, H_kv, src.shape[-1])
-            dst.append(torch.cat([gathered[r, :, :lens[r]] for r in range(world)], dim=1).contiguous())
+            full = torch.empty((B, sizes[l], H_kv, src.shape[-1]), dtype=src.dtype, device=src.device)
+            at = 0
+            for r in range(world):
+                full[:, at:at + lens[r]] = gathered[r, :, :lens[r]]
+                at += lens[r]
+            dst.append(full)
     return layers_k, layers_v
+
+
+def default_query_ranges(T: int, world_size: int, compression_rate: int, top_k: int, max_top_nodes: int):
+    """The split htree_forward_sequence_parallel uses when none is given: by equal work where the sequence has at least one
+    block of compression_rate^(levels-1) positions per rank, else the even split."""
+    L = len(configs.level_sizes(T, compression_rate, max_top_nodes))
+    if world_size == 1:
+        return [(0, T)]
+    try:
+        return balanced_query_ranges(T, world_size, compression_rate, top_k, max_top_nodes)
+    except ValueError:
+        return [query_range(T, world_size, r, compression_rate, L) for r in range(world_size)]
 
 
 def htree_forward_sequence_parallel(q_local: torch.Tensor, k: torch.Tensor, v: torch.Tensor, compression_rate: int = 16,
                                     max_top_nodes: int = 8192, top_k_per_layer: int = 512, scale: Optional[float] = None,
                                     rope_base: float = 10000.0, group=None, ranges=None) -> torch.Tensor:
     """Mode B forward: q_local holds this rank's query positions [B, t1-t0, H, K]; k, v are the full sequence.
-    `ranges` (e.g. from balanced_query_ranges) overrides the even split.  Returns out_local [B, t1-t0, H, V]."""
+    `ranges`: per-rank query ranges; None = the even split (use default_query_ranges for the work-balanced one, which
+    the caller also needs in order to cut q).  Returns out_local [B, t1-t0, H, V]."""
     import torch.distributed as dist
     from .ops import htree_forward
 

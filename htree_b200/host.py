@@ -95,8 +95,24 @@ def forward_backward_host(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, dO:
     return tuple(outs)
 
 
+WINDOW_TARGET = 8192      # positions per query window of the unit pipeline; a call of n units uses at most ceil(8/n) windows per unit
+
+
+def _t_chunks(T: int, target: Optional[int] = None, most: int = 8):
+    """Cut [0, T) into at most `most` windows of about `target` positions (multiples of 256 except the last)."""
+    n = max(1, min(most, T // (target or WINDOW_TARGET)))
+    step = -(-T // n)
+    step = -(-step // 256) * 256
+    return [(a, min(T, a + step)) for a in range(0, T, step)]
+
+
 def _by_units(q, k, v, dO, outs, dev, streams, compression_rate, max_top_nodes, top_k_per_layer, scale, rope_base):
-    """One (batch, KV head) unit at a time: q/dO/out/dq slices [1,T,G,D] and k/v/dk/dv slices [1,T,1,D]."""
+    """One (batch, KV head) unit at a time, and inside a unit one window of query positions at a time.
+
+    A unit reads q/dO slices [1,T,G,D] and k/v slices [1,T,1,D] and writes the same slices of the results.  Its k and v
+    go up first and the tree is built once; q, dO, out and dq then move window by window (the forward takes a query
+    window, the backward accumulates dK/dV across windows), so that only one window's upload precedes the first kernel
+    and only one window's download follows the last one."""
     s_in, s_run, s_out = streams
     B, T, H, K = q.shape
     H_kv, V = k.shape[2], v.shape[-1]
@@ -104,49 +120,68 @@ def _by_units(q, k, v, dO, outs, dev, streams, compression_rate, max_top_nodes, 
     bwd = dO is not None
     if scale is None:
         scale = K ** -0.5
+    # windows shorten the exposed first upload / last download but cost launch tails; they pay when a call has few units
+    windows = _t_chunks(T, most=max(1, min(8, -(-8 // (B * H_kv)))))
     keep = []
+
+    def held(ts):
+        for t in ts:
+            t.record_stream(s_run); t.record_stream(s_out)
+        keep.append(ts)
+        if len(keep) > 6:
+            keep.pop(0)
+
     with torch.cuda.device(dev):
         for b in range(B):
             for hk in range(H_kv):
                 hs = slice(hk * G, (hk + 1) * G)
-                srcs = [q[b:b + 1, :, hs], k[b:b + 1, :, hk:hk + 1], v[b:b + 1, :, hk:hk + 1]] + ([dO[b:b + 1, :, hs]] if bwd else [])
-                dsts = [outs[0][b:b + 1, :, hs]] + ([outs[1][b:b + 1, :, hs], outs[2][b:b + 1, :, hk:hk + 1],
-                                                     outs[3][b:b + 1, :, hk:hk + 1]] if bwd else [])
-                # the forward starts as soon as q, k, v are there (dO follows), and its output leaves while the backward runs
                 with torch.cuda.stream(s_in):
-                    dev_in = [torch.empty(x.shape, dtype=x.dtype, device=dev) for x in srcs]
-                    for d, x in zip(dev_in[:3], srcs[:3]):
-                        _copy_unit(d, x, s_in)
-                    ready = torch.cuda.Event(); ready.record(s_in)
-                    if bwd:
-                        _copy_unit(dev_in[3], srcs[3], s_in)
-                        ready_bwd = torch.cuda.Event(); ready_bwd.record(s_in)
+                    k_d = torch.empty((1, T, 1, K), dtype=k.dtype, device=dev)
+                    v_d = torch.empty((1, T, 1, V), dtype=v.dtype, device=dev)
+                    _copy_unit(k_d, k[b:b + 1, :, hk:hk + 1], s_in)
+                    _copy_unit(v_d, v[b:b + 1, :, hk:hk + 1], s_in)
+                    kv_ready = torch.cuda.Event(); kv_ready.record(s_in)
                 with torch.cuda.stream(s_run):
-                    s_run.wait_event(ready)
-                    if bwd:
-                        o, ctx = ops.htree_forward(dev_in[0], dev_in[1], dev_in[2], compression_rate, max_top_nodes,
-                                                   top_k_per_layer, scale, rope_base, _save_for_backward=True)
-                        fwd_done = torch.cuda.Event(); fwd_done.record(s_run)
-                        s_run.wait_event(ready_bwd)
-                        dq, dk, dv = ops.htree_backward(dev_in[3], dev_in[0], o, ctx, _typed=True)
-                        res = [o, dq, dk, dv]
-                        del ctx
-                    else:
-                        res = [ops.htree_forward(dev_in[0], dev_in[1], dev_in[2], compression_rate, max_top_nodes,
-                                                 top_k_per_layer, scale, rope_base)]
-                        fwd_done = torch.cuda.Event(); fwd_done.record(s_run)
-                    done = torch.cuda.Event(); done.record(s_run)
-                with torch.cuda.stream(s_out):
-                    s_out.wait_event(fwd_done)
-                    _copy_unit(dsts[0], res[0], s_out)
-                    if bwd:
-                        s_out.wait_event(done)
-                        for h, r in zip(dsts[1:], res[1:]):
-                            _copy_unit(h, r, s_out)
-                for t in dev_in + res:
-                    t.record_stream(s_run); t.record_stream(s_out)
-                keep.append((dev_in, res))
-                if len(keep) > 2:
-                    keep.pop(0)
+                    s_run.wait_event(kv_ready)
+                    layers = ops.build_tree(k_d, v_d, compression_rate, max_top_nodes, rope_base)
+                held([k_d, v_d] + [x for lv in layers if lv is not None for x in lv])
+                acc = {}
+                for wi, (t0, t1) in enumerate(windows):
+                    first, last = wi == 0, wi == len(windows) - 1
+                    with torch.cuda.stream(s_in):
+                        q_d = torch.empty((1, t1 - t0, G, K), dtype=q.dtype, device=dev)
+                        _copy_unit(q_d, q[b:b + 1, t0:t1, hs], s_in)
+                        q_ready = torch.cuda.Event(); q_ready.record(s_in)
+                        if bwd:
+                            dO_d = torch.empty((1, t1 - t0, G, V), dtype=dO.dtype, device=dev)
+                            _copy_unit(dO_d, dO[b:b + 1, t0:t1, hs], s_in)
+                            dO_ready = torch.cuda.Event(); dO_ready.record(s_in)
+                    with torch.cuda.stream(s_run):
+                        s_run.wait_event(q_ready)
+                        if bwd:
+                            o, ctx = ops.htree_forward(q_d, k_d, v_d, compression_rate, max_top_nodes, top_k_per_layer, scale,
+                                                       rope_base, _save_for_backward=True, _q_offset=t0, _layers=layers)
+                            fwd_done = torch.cuda.Event(); fwd_done.record(s_run)
+                            s_run.wait_event(dO_ready)
+                            dq, dk, dv = ops.htree_backward(dO_d, q_d, o, ctx, _typed=True,
+                                                            _window=dict(t0=t0, first=first, last=last, acc=acc))
+                            del ctx
+                        else:
+                            o = ops.htree_forward(q_d, k_d, v_d, compression_rate, max_top_nodes, top_k_per_layer, scale,
+                                                  rope_base, _q_offset=t0, _layers=layers)
+                            fwd_done = torch.cuda.Event(); fwd_done.record(s_run)
+                        done = torch.cuda.Event(); done.record(s_run)
+                    with torch.cuda.stream(s_out):
+                        s_out.wait_event(fwd_done)
+                        _copy_unit(outs[0][b:b + 1, t0:t1, hs], o, s_out)
+                        if bwd:
+                            s_out.wait_event(done)
+                            _copy_unit(outs[1][b:b + 1, t0:t1, hs], dq, s_out)
+                            if last:
+                                _copy_unit(outs[2][b:b + 1, :, hk:hk + 1], dk, s_out)
+                                _copy_unit(outs[3][b:b + 1, :, hk:hk + 1], dv, s_out)
+                    held([q_d, o] + ([dO_d, dq] if bwd else []) + ([dk, dv] if bwd and last else []))
+                if bwd:
+                    held([x for lst in (acc["dk"], acc["dv"]) for x in lst])
     s_out.synchronize(); s_run.synchronize(); s_in.synchronize()
     return tuple(outs)

@@ -175,8 +175,8 @@ def build_tree(k: torch.Tensor, v: torch.Tensor, compression_rate: int, max_top_
     for n in sizes[1:]:
         layers_k.append(torch.empty(B, n, H_kv, K, dtype=k.dtype, device=k.device))
         layers_v.append(torch.empty(B, n, H_kv, V, dtype=v.dtype, device=v.device))
-    want_rot = rope_base is not None and k.dtype != torch.float32 and K % 16 == 0
-    layers_kr = [torch.empty(x.shape, dtype=torch.float16, device=x.device) for x in layers_k] if want_rot else None
+    want_rot = rope_base is not None and _rotatable(k.dtype, K, V, compression_rate)
+    layers_kr = [_rotated_like(x) for x in layers_k] if want_rot else None
     want_blk = want_rot and _blockable(V, compression_rate)
     layers_vb = [_blocked_like(x, compression_rate) for x in layers_v] if want_blk else None
     if len(sizes) > 1 or want_rot:
@@ -196,6 +196,42 @@ def build_tree(k: torch.Tensor, v: torch.Tensor, compression_rate: int, max_top_
     return layers_k, layers_v
 
 
+def build_tree_into(k: torch.Tensor, v: torch.Tensor, out_k, out_v, compression_rate: int, max_top_nodes: int) -> None:
+    """Mean-pool tree of (k, v) with the pooled levels written into caller-provided tensors out_k[i], out_v[i]
+    (level i+1; contiguous, shaped [B, N_{i+1}, H_kv, *]).  Sequence-sharded runs pool their slice of the leaves straight
+    into their slot of the buffers that the all-gather then completes."""
+    B, T, H_kv, K = k.shape
+    V = v.shape[-1]
+    sizes = _lib.level_sizes(T, compression_rate, max_top_nodes)
+    assert len(out_k) == len(out_v) == len(sizes) - 1
+    layers_k, layers_v = [k] + list(out_k), [v] + list(out_v)
+    for x, n in zip(layers_k, sizes):
+        assert x.is_contiguous() and x.shape[1] == n, "level tensors must be contiguous and of the level's length"
+    for x in layers_v:
+        assert x.is_contiguous()
+    if len(sizes) == 1:
+        return
+    shape = _lib.HtreeShape(B, T, H_kv, H_kv, K, V, int(compression_rate), 1, int(max_top_nodes), _DTYPES[k.dtype])
+    with torch.cuda.device(k.device):
+        _lib.check(_lib.lib().htree_b200_build_tree(ctypes.byref(shape), _ptrs(layers_k), _ptrs(layers_v), None, None, None, None,
+                                                    _stream()), "build_tree")
+
+
+def _split_half(dtype, K: int, V: int, compression_rate: int) -> bool:
+    """fp32 storage on the tensor cores (operands carried as hi + lo half planes): 64-wide heads only."""
+    return dtype == torch.float32 and K == 64 and V == 64 and int(compression_rate) in (8, 16)
+
+
+def _rotatable(dtype, K: int, V: int, compression_rate: int) -> bool:
+    return (dtype != torch.float32 and K % 16 == 0) or _split_half(dtype, K, V, compression_rate)
+
+
+def _rotated_like(x: torch.Tensor) -> torch.Tensor:
+    """K' buffer of one level: float16, for fp32 storage two planes (hi, lo)."""
+    shape = ((2,) if x.dtype == torch.float32 else ()) + tuple(x.shape)
+    return torch.empty(shape, dtype=torch.float16, device=x.device)
+
+
 def _blockable(V: int, compression_rate: int) -> bool:
     return V in (64, 128) and int(compression_rate) in (8, 16)
 
@@ -203,6 +239,8 @@ def _blockable(V: int, compression_rate: int) -> bool:
 def _blocked_like(x: torch.Tensor, compression_rate: int) -> torch.Tensor:
     B, N, H_kv, V = x.shape
     cr = int(compression_rate)
+    if x.dtype == torch.float32:      # split-half planes (hi, lo) of float16
+        return torch.empty(2, B, (N + cr - 1) // cr * cr, H_kv, V, dtype=torch.float16, device=x.device)
     return torch.empty(B, (N + cr - 1) // cr * cr, H_kv, V, dtype=x.dtype, device=x.device)
 
 
@@ -210,7 +248,7 @@ def block_values(layers_v, compression_rate: int, max_top_nodes: int):
     """Blocked copies of existing value levels (see build_tree); None for fp32 or shapes the tensor-core forward does not cover."""
     v = layers_v[0]
     B, T, H_kv, V = v.shape
-    if v.dtype == torch.float32 or not _blockable(V, compression_rate):
+    if not _blockable(V, compression_rate) or (v.dtype == torch.float32 and V != 64):
         return None
     out = [_blocked_like(x, compression_rate) for x in layers_v]
     shape = _lib.HtreeShape(B, T, H_kv, H_kv, V, V, int(compression_rate), 1, int(max_top_nodes), _DTYPES[v.dtype])
@@ -220,12 +258,13 @@ def block_values(layers_v, compression_rate: int, max_top_nodes: int):
 
 
 def rotate_keys(layers_k, compression_rate: int, max_top_nodes: int, rope_base: float):
-    """K' levels (keys rotated by their child index) for existing tree levels; None for fp32 or K % 16 != 0."""
+    """K' levels (keys rotated by their child index) for existing tree levels; None where no tensor-core kernel reads them
+    (K % 16 != 0, or fp32 storage with heads other than 64 wide)."""
     k = layers_k[0]
     B, T, H_kv, K = k.shape
-    if k.dtype == torch.float32 or K % 16:
+    if not _rotatable(k.dtype, K, K, compression_rate):
         return None
-    out = [torch.empty(x.shape, dtype=torch.float16, device=x.device) for x in layers_k]
+    out = [_rotated_like(x) for x in layers_k]
     shape = _lib.HtreeShape(B, T, H_kv, H_kv, K, K, int(compression_rate), 1, int(max_top_nodes), _DTYPES[k.dtype])
     cos_c, sin_c = rope_cache(K, max(int(compression_rate), 16), rope_base, k.device)
     with torch.cuda.device(k.device):
@@ -350,7 +389,7 @@ def recompute_parents(q, layers_k, layers_v, cos_cache, sin_cache, compression_r
 
 
 def htree_backward(dO: torch.Tensor, q: torch.Tensor, output: torch.Tensor, bwd_ctx: dict, _force_generic: bool = False,
-                   _typed: bool = False):
+                   _typed: bool = False, _window: Optional[dict] = None):
     """Backward given the forward context; returns fp32 (dq, dk, dv) with the shapes of q, k, v
     (src/backward.py:941-1119).  If bwd_ctx['per_layer_parents'] is None the selections are rebuilt first.
 
@@ -358,7 +397,13 @@ def htree_backward(dO: torch.Tensor, q: torch.Tensor, output: torch.Tensor, bwd_
     reference's autograd function produces by casting the fp32 results afterwards (src/backward.py:1193), without the
     fp32 dq tensor and the extra passes over memory.
     dO must have q's dtype (the kernels read it in the storage type; the reference up-casts both to fp32,
-    src/backward.py:966): a wider dO is refused rather than rounded silently."""
+    src/backward.py:966): a wider dO is refused rather than rounded silently.
+
+    `_window` runs the backward over consecutive query windows that share the dK/dV accumulators (what the host-buffer
+    pipeline does to overlap transfers with kernels): {"t0": first position of this window, "first": bool, "last": bool,
+    "acc": dict kept by the caller across the windows of one backward}.  q, dO, output and bwd_ctx then belong to the
+    window (a forward called with `_q_offset`); dq is returned for the window, dk and dv only with the last window
+    (None before)."""
     B, T, H, K = q.shape
     layers_k, layers_v = bwd_ctx["layers_k"], bwd_ctx["layers_v"]
     H_kv, V = layers_k[0].shape[2], layers_v[0].shape[-1]
@@ -379,14 +424,27 @@ def htree_backward(dO: torch.Tensor, q: torch.Tensor, output: torch.Tensor, bwd_
     if parents is None:
         parents = recompute_parents(q, layers_k, layers_v, cos_cache, sin_cache, CR, TK, MTN, scale,
                                     bwd_ctx.get("layers_k_rot"))
-    shape = _lib.HtreeShape(B, T, H, H_kv, K, V, int(CR), int(TK), int(MTN), _DTYPES[q.dtype])
-    dk_levels = [torch.empty(x.shape, dtype=torch.float32, device=dev) for x in layers_k]
-    dv_levels = [torch.empty(x.shape, dtype=torch.float32, device=dev) for x in layers_v]
+    flags = 0
+    if _window is None:
+        shape = _lib.HtreeShape(B, T, H, H_kv, K, V, int(CR), int(TK), int(MTN), _DTYPES[q.dtype])
+        dk_levels = [torch.empty(x.shape, dtype=torch.float32, device=dev) for x in layers_k]
+        dv_levels = [torch.empty(x.shape, dtype=torch.float32, device=dev) for x in layers_v]
+    else:
+        T_full = layers_k[0].shape[1]
+        shape = _lib.HtreeShape(B, T_full, H, H_kv, K, V, int(CR), int(TK), int(MTN), _DTYPES[q.dtype], T, int(_window["t0"]))
+        acc = _window["acc"]
+        if _window["first"]:
+            acc["dk"] = [torch.empty(x.shape, dtype=torch.float32, device=dev) for x in layers_k]
+            acc["dv"] = [torch.empty(x.shape, dtype=torch.float32, device=dev) for x in layers_v]
+        dk_levels, dv_levels = acc["dk"], acc["dv"]
+        flags |= (0 if _window["first"] else _lib.BWD_KEEP_ACCUM) | (0 if _window["last"] else _lib.BWD_NO_FOLD)
+    final = _window is None or _window["last"]
     typed = None
     if _typed:
         dq = torch.empty(B, T, H, K, dtype=q.dtype, device=dev)
-        dk_t = torch.empty(layers_k[0].shape, dtype=q.dtype, device=dev)
-        dv_t = torch.empty(layers_v[0].shape, dtype=q.dtype, device=dev)
+        # before the last window the leaf gradients are not written; the struct still wants valid pointers
+        dk_t = torch.empty(layers_k[0].shape if final else (8,), dtype=q.dtype, device=dev)
+        dv_t = torch.empty(layers_v[0].shape if final else (8,), dtype=q.dtype, device=dev)
         typed = _lib.HtreeTypedGrads(dq.data_ptr(), dk_t.data_ptr(), dv_t.data_ptr())
     else:
         dq = torch.empty(B, T, H, K, dtype=torch.float32, device=dev)
@@ -399,8 +457,10 @@ def htree_backward(dO: torch.Tensor, q: torch.Tensor, output: torch.Tensor, bwd_
             bwd_ctx["global_max"].data_ptr(), bwd_ctx["global_sum"].data_ptr(),
             _ptrs([parents[l] for l in range(L)]), None if _typed else dq.data_ptr(), _ptrs(dk_levels), _ptrs(dv_levels),
             ctypes.byref(typed) if typed is not None else None, _status(dev).data_ptr(),
-            (_lib.FWD_GENERIC if _force_generic else 0) | _parents_flag([parents[l] for l in range(L)]), _stream())
+            flags | (_lib.FWD_GENERIC if _force_generic else 0) | _parents_flag([parents[l] for l in range(L)]), _stream())
     _lib.check(rc, "backward")
+    if not final:
+        return dq, None, None
     if _typed:
         return dq, dk_t, dv_t
     return dq, dk_levels[0], dv_levels[0]

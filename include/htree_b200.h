@@ -40,7 +40,7 @@ extern "C" {
 #define HTREE_E_ALIGN (-7)       /* a pointer or row size breaks the 16-byte alignment the kernels need */
 #define HTREE_E_UNSUPPORTED (-8) /* shape outside what the kernels were built for (e.g. shared memory need) */
 #define HTREE_E_NODEVICE (-9)    /* no CUDA device / wrong architecture */
-#define HTREE_E_WINDOW (-10)     /* query window outside the sequence, or a window given to the backward */
+#define HTREE_E_WINDOW (-10)     /* query window outside the sequence, or a backward window without the window flags */
 #define HTREE_E_SCRATCH (-11)    /* pooled-level accumulators exceed the library's built-in scratch array */
 
 /* forward flags */
@@ -56,6 +56,15 @@ extern "C" {
 #define HTREE_FWD_FUSED 4u       /* tensor-core forward: keep selection and accumulation in ONE kernel even when parent
                                     buffers are provided (default then: a selection kernel followed by an accumulation kernel) */
 
+/* backward flags: a backward may be run as several calls over consecutive query windows (HtreeShape.T_q / t_offset) that share
+ * the dk_levels / dv_levels accumulators, e.g. to overlap transfers of q, dO, out and dq with the kernels.  The first call
+ * passes HTREE_BWD_NO_FOLD, calls in the middle HTREE_BWD_KEEP_ACCUM | HTREE_BWD_NO_FOLD, the last one HTREE_BWD_KEEP_ACCUM;
+ * dq (or typed->dq) of every call covers that call's window only, dk / dv are complete after the last call.  Every call
+ * of one backward must be given the same level buffers and operand copies (they select the same kernel).
+ * No counterpart in the reference (its backward always runs every position, src/backward.py:941-1119). */
+#define HTREE_BWD_KEEP_ACCUM 32u /* do not zero-fill dk_levels / dv_levels: they hold the sums of earlier windows */
+#define HTREE_BWD_NO_FOLD 64u    /* stop after accumulating: later windows follow, dk / dv are not final yet */
+
 /* Problem description shared by all entry points (mirrors the keyword arguments of htree_forward,
  * src/parallel.py:874-885). */
 typedef struct HtreeShape {
@@ -64,10 +73,11 @@ typedef struct HtreeShape {
     int32_t top_k;          /* top_k_per_layer */
     int32_t max_top_nodes;  /* may be smaller than top_k*compression_rate; the reference asserts equality */
     int32_t dtype;          /* HTREE_F32 / HTREE_BF16 / HTREE_F16 */
-    /* Query window for sequence-sharded forward calls: the call computes query positions
-     * t_offset .. t_offset + T_q - 1 of the sequence, q/out are [B,T_q,H,*], gmax/gsum [B,T_q,H] and parents
-     * [B,T_q,H_kv,top_k], while the tree levels still cover all T positions.  T_q = 0 means the whole sequence
-     * (T_q = T, t_offset = 0).  The reference has no counterpart (it always runs every position). */
+    /* Query window (sequence-sharded forward calls, windowed forward / backward of the host-buffer pipeline): the call
+     * computes query positions t_offset .. t_offset + T_q - 1 of the sequence, q/out/dO/dq are [B,T_q,H,*], gmax/gsum
+     * [B,T_q,H] and parents [B,T_q,H_kv,top_k], while the tree levels (and dk_levels/dv_levels) still cover all T
+     * positions.  T_q = 0 means the whole sequence (T_q = T, t_offset = 0).  The backward accepts a window only together
+     * with HTREE_BWD_KEEP_ACCUM / HTREE_BWD_NO_FOLD.  The reference has no counterpart (it always runs every position). */
     int32_t T_q;
     int32_t t_offset;
 } HtreeShape;

@@ -176,3 +176,31 @@ def time_naive(q, k, v, dO, compression_rate, top_k, runs=1):
             out.backward(dO)
             tfb.append(time.perf_counter() - t0)
     return statistics.median(tf), (statistics.median(tfb) if tfb else None)
+
+
+def time_nsa(q, k, v, block_size=64, block_counts=16, warmup=2, iters=2):
+    """Forward latency in ms of the NSA comparison baseline the reference ships (ref_nsa/, adapted from
+    flash-linear-attention; staged unmodified), called as speed_test.py:261-270 calls it: the full pipeline (pooling,
+    compression, selection, execution) with a zero compression gate.  Raises whatever its imports raise."""
+    import torch
+    if REF not in sys.path:
+        sys.path.insert(0, REF)
+    from ref_nsa.nsa_parallel import parallel_nsa
+    B, T, HQ, K = q.shape
+    gate = torch.zeros(B, T, HQ, device=q.device, dtype=q.dtype)
+    scale = K ** -0.5
+
+    def run():
+        return parallel_nsa(q, k, v, g_cmp=gate, block_indices=None, block_size=block_size, scale=scale, block_counts=block_counts)
+
+    with torch.no_grad():
+        for _ in range(warmup):
+            run()
+        torch.cuda.synchronize()
+        a = torch.cuda.Event(enable_timing=True); b = torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(iters):
+            run()
+        b.record()
+        torch.cuda.synchronize()
+    return a.elapsed_time(b) / max(iters, 1)

@@ -136,8 +136,8 @@ def test_config5_near_tie_stress(dtype, tk):
     for x in (out, dq, dk, dv):
         assert bool(torch.isfinite(x.float()).all())
     queries = sample_queries(c["B"], c["T"], c["H_kv"], 512, 3)
-    fast = dtype != "float32"       # 16-bit storage, head_dim 64, compression_rate 8: tensor-core kernels
-    assert (ctx["layers_k_rot"] is not None) == fast
+    fast = dtype != "float32"       # 16-bit storage, head_dim 64, compression_rate 8: half-precision tensor-core kernels
+    assert ctx["layers_k_rot"] is not None      # fp32 storage with 64-wide heads: the split-half tensor-core kernels
     # Half-precision operands give a score an absolute error proportional to |q||k| * 2^-11, and the importance the
     # same RELATIVE error, so the near-tie window of the tensor-core path scales with the key magnitude (here rms 6:
     # scores reach 70).  Measured on B200: 96.7 % - 98.8 % of groups identical, swapped nodes within 1.8e-3.
@@ -248,3 +248,58 @@ def test_config4_length_forward():
     layers = (ctx["layers_k"], ctx["layers_v"], ctx["layers_k_rot"])
     out_w = ops.htree_forward(qd[:, a:b].contiguous(), kd, vd, 16, 512, 64, _q_offset=a, _layers=layers)
     assert torch.equal(out_w, out[:, a:b])
+
+
+def test_config3_full_batch_matches_single_batch_runs():
+    """Configuration cfg3 exactly (B=4, T=65536, H_q=64, H_kv=4, head_dim=128, bf16): 2^31 elements in q, so every offset
+    into the last batch element needs 64-bit arithmetic.  The last batch element computed inside the batch of four must
+    equal the same element computed alone, bit for bit (out, selections, dq) and up to the atomic order (dk, dv);
+    sampled groups of that element are checked against the CPU oracle."""
+    ops = _ops()
+    c = dict(B=4, T=65536, H=64, H_kv=4, K=128, V=128, CR=16, TK=64, MTN=256, dtype="bfloat16", seed=5)
+    gen = torch.Generator(device=DEV).manual_seed(c["seed"])
+    rnd = lambda *s: torch.randn(*s, generator=gen, device=DEV, dtype=torch.float32).bfloat16()
+    q, k, v, dO = rnd(4, c["T"], 64, 128), rnd(4, c["T"], 4, 128), rnd(4, c["T"], 4, 128), rnd(4, c["T"], 64, 128)
+    assert q.numel() >= 2 ** 31
+    out, ctx = ops.htree_forward(q, k, v, c["CR"], c["MTN"], c["TK"], _save_for_backward=True)
+    dq, dk, dv = ops.htree_backward(dO, q, out, ctx, _typed=True)
+    b = 3
+    out1, ctx1 = ops.htree_forward(q[b:b + 1], k[b:b + 1], v[b:b + 1], c["CR"], c["MTN"], c["TK"], _save_for_backward=True)
+    dq1, dk1, dv1 = ops.htree_backward(dO[b:b + 1], q[b:b + 1], out1, ctx1, _typed=True)
+    torch.cuda.synchronize(); ops.check_status()
+    assert torch.equal(out[b:b + 1], out1) and torch.equal(dq[b:b + 1], dq1)
+    for l in range(ctx["num_layers"]):
+        assert torch.equal(ctx["per_layer_parents"][l][b:b + 1], ctx1["per_layer_parents"][l])
+    for x, y in ((dk[b:b + 1], dk1), (dv[b:b + 1], dv1)):
+        assert float((x.float() - y.float()).abs().max()) <= 2.0 ** -6 * max(1.0, float(y.float().abs().max()))
+    c1 = dict(c, B=1)
+    queries = sample_queries(1, c["T"], c["H_kv"], 128, 6)
+    frac, err, _, _ = compare_sampled(c1, q[b:b + 1], k[b:b + 1], v[b:b + 1], out1, ctx1, queries, EPS_SEL_MMA)
+    print(f"\n[cfg3 B=4, batch 3] sampled groups identical at every level: {frac:.4f}; max|out-oracle| on them {err:.3e}")
+    assert frac > 0.95 and err <= 2e-2
+
+
+def test_config4_full_shape_forward():
+    """Configuration cfg4 exactly: B=1, T=524288, H_q=32, H_kv=4 (groups of 8 heads), head_dim=128, bf16, four tree
+    levels.  Sampled groups against the CPU oracle (only the sampled query rows exist on the host)."""
+    ops = _ops()
+    c = dict(B=1, T=524288, H=32, H_kv=4, K=128, V=128, CR=16, TK=64, MTN=512, dtype="bfloat16", seed=9)
+    g = torch.Generator().manual_seed(c["seed"])
+    k = torch.randn(1, c["T"], 4, 128, generator=g).bfloat16()
+    v = torch.randn(1, c["T"], 4, 128, generator=g).bfloat16()
+    n = 96
+    rng = np.random.default_rng(10)
+    ts = np.sort(rng.choice(c["T"], n, replace=False))
+    ts[-1] = c["T"] - 1
+    q_rows = torch.randn(n, 32, 128, generator=g).bfloat16()
+    qd = torch.randn(1, c["T"], 32, 128, device=DEV, generator=torch.Generator(device=DEV).manual_seed(2)).bfloat16()
+    qd[0, torch.from_numpy(ts).to(DEV)] = q_rows.to(DEV)
+    out, ctx = ops.htree_forward(qd, k.to(DEV), v.to(DEV), 16, 512, 64, _save_for_backward=True)
+    torch.cuda.synchronize(); ops.check_status()
+    assert ctx["num_layers"] == 4 and bool(torch.isfinite(out.float()).all())
+    q_sparse = np.zeros((1, c["T"], 32, 128), np.float32)       # untouched pages stay virtual
+    q_sparse[0, ts] = q_rows.float().numpy()
+    queries = np.stack([np.zeros(n, np.int64), ts, rng.integers(0, 4, n)], 1).astype(np.int32)
+    frac, err, _, _ = compare_sampled(c, q_sparse, k, v, out, ctx, queries, EPS_SEL_MMA)
+    print(f"\n[cfg4 full shape] sampled groups identical at every level: {frac:.4f}; max|out-oracle| on them {err:.3e}")
+    assert frac > 0.93 and err <= 2e-2

@@ -3,6 +3,8 @@ reference's naive path and against the CPU oracle on the same seeded inputs.
 
 Bar (stated per assertion): selections identical except documented near-ties; fp32 outputs/gradients within 1e-4
 relative; bf16/fp16 outputs within 2e-2 absolute."""
+import ctypes
+
 import numpy as np
 import pytest
 import torch
@@ -460,6 +462,57 @@ def test_host_buffer_pipeline_by_units():
         assert torch.allclose(a.float(), b.to(torch.bfloat16).float().cpu(), rtol=2e-2, atol=2e-3)   # reduction order
     (o2,) = host.forward_backward_host(hq, hk, hv, None, c["CR"], c["MTN"], c["TK"], chunk="unit")
     assert torch.equal(o2, out.cpu())
+
+
+def test_host_buffer_pipeline_with_query_windows(monkeypatch):
+    """The unit pipeline cuts long sequences into query windows (forward per window, backward accumulating dK/dV across
+    windows); forced here on a short sequence: three windows per unit, same results as the device calls."""
+    ops = _ops()
+    from htree_b200 import host
+    monkeypatch.setattr(host, "WINDOW_TARGET", 512)
+    c = dict(B=1, T=1700, H=16, H_kv=2, K=128, V=128, CR=16, TK=16, MTN=64, dtype="bfloat16", seed=64)    # 2 units: up to 4 windows each
+    assert len(host._t_chunks(c["T"], most=4)) == 3
+    q, k, v, dO = parity.case_inputs(c)
+    hq, hk, hv, hd = (x.pin_memory() for x in (q, k, v, dO))
+    out_h, dq_h, dk_h, dv_h = host.forward_backward_host(hq, hk, hv, hd, c["CR"], c["MTN"], c["TK"], chunk="unit")
+    out, ctx = ops.htree_forward(q.to(DEV), k.to(DEV), v.to(DEV), c["CR"], c["MTN"], c["TK"], _save_for_backward=True)
+    dq, dk, dv = ops.htree_backward(dO.to(DEV), q.to(DEV), out, ctx)
+    assert torch.equal(out_h, out.cpu())
+    assert torch.equal(dq_h, dq.to(torch.bfloat16).cpu())         # one owner per dq row: windows change nothing
+    for a, b in ((dk_h, dk), (dv_h, dv)):
+        assert torch.allclose(a.float(), b.to(torch.bfloat16).float().cpu(), rtol=2e-2, atol=2e-3)   # reduction order
+    (o2,) = host.forward_backward_host(hq, hk, hv, None, c["CR"], c["MTN"], c["TK"], chunk="unit")
+    assert torch.equal(o2, out.cpu())
+
+
+@pytest.mark.parametrize("dtype,D,CR", [("float32", 32, 4), ("bfloat16", 128, 16), ("float32", 64, 8)])
+def test_backward_over_query_windows_equals_the_whole_backward(dtype, D, CR):
+    """htree_backward(_window=...) over three consecutive windows (generic, tensor-core and split-half kernels): dq of every
+    window is bit-identical to the rows of the whole backward, dk / dv agree up to the order of the atomic sums; a window
+    without the window flags is refused by the C entry point."""
+    ops = _ops()
+    B, T, H, Hkv, TK, MTN = 1, 1300, 8, 2, 8, 16
+    q, k, v, dO = (x.to(DEV) for x in parity.make_inputs(B, T, H, Hkv, D, D, dtype, 93))
+    out, ctx = ops.htree_forward(q, k, v, CR, MTN, TK, _save_for_backward=True)
+    dq, dk, dv = ops.htree_backward(dO, q, out, ctx)
+    layers = (ctx["layers_k"], ctx["layers_v"], ctx["layers_k_rot"], ctx["layers_v_blk"])
+    acc, cuts = {}, [(0, 500), (500, 501), (501, T)]
+    for i, (a, b) in enumerate(cuts):
+        qw, dOw = q[:, a:b].contiguous(), dO[:, a:b].contiguous()
+        ow, cw = ops.htree_forward(qw, k, v, CR, MTN, TK, _save_for_backward=True, _q_offset=a, _layers=layers)
+        assert torch.equal(ow, out[:, a:b])
+        dqw, dkw, dvw = ops.htree_backward(dOw, qw, ow, cw, _window=dict(t0=a, first=i == 0, last=i == len(cuts) - 1, acc=acc))
+        assert torch.equal(dqw, dq[:, a:b])
+        assert (dkw is None) == (i < len(cuts) - 1)
+    torch.cuda.synchronize(); ops.check_status()
+    for x, y in ((dkw, dk), (dvw, dv)):
+        assert float((x - y).abs().max()) <= 1e-4 * max(1.0, float(y.abs().max()))
+    from htree_b200 import _lib, ops as hops
+    shape = _lib.HtreeShape(B, T, H, Hkv, D, D, CR, TK, MTN, hops._DTYPES[q.dtype], 100, 50)
+    one = _lib.ptr_array([256] * ctx["num_layers"])
+    rc = _lib.lib().htree_b200_backward(ctypes.byref(shape), 256, one, one, None, 256, 256, None, None, 4096, 0.1, 256, 256, 256, 256,
+                                        one, 256, one, one, None, None, 0, None)
+    assert rc == -10
 
 
 @pytest.mark.parametrize("c", [
