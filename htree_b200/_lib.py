@@ -17,6 +17,7 @@ FWD_GENERIC = 2
 FWD_FUSED = 4
 FWD_TILED = 8
 PARENTS_U16 = 16
+FWD_NO_PIPELINE = 128
 BWD_KEEP_ACCUM = 32
 BWD_NO_FOLD = 64
 
@@ -30,6 +31,7 @@ SYMBOLS = (
     "htree_b200_build_tree",
     "htree_b200_rotate_keys",
     "htree_b200_block_values",
+    "htree_b200_block_keys",
     "htree_b200_forward",
     "htree_b200_level_forward",
     "htree_b200_merge_to_global",
@@ -84,13 +86,15 @@ def lib() -> ctypes.CDLL:
         L.htree_b200_level_sizes.restype = ctypes.c_int
         L.htree_b200_level_sizes.argtypes = [i32, i32, i32, ctypes.POINTER(i32), i32]
         L.htree_b200_build_tree.restype = ctypes.c_int
-        L.htree_b200_build_tree.argtypes = [ctypes.POINTER(HtreeShape), vp, vp, vp, vp, vp, vp, vp]
+        L.htree_b200_build_tree.argtypes = [ctypes.POINTER(HtreeShape), vp, vp, vp, vp, vp, vp, vp, vp]
         L.htree_b200_rotate_keys.restype = ctypes.c_int
         L.htree_b200_rotate_keys.argtypes = [ctypes.POINTER(HtreeShape), vp, vp, vp, vp, vp]
         L.htree_b200_block_values.restype = ctypes.c_int
         L.htree_b200_block_values.argtypes = [ctypes.POINTER(HtreeShape), vp, vp, vp]
+        L.htree_b200_block_keys.restype = ctypes.c_int
+        L.htree_b200_block_keys.argtypes = [ctypes.POINTER(HtreeShape), vp, vp, vp]
         L.htree_b200_forward.restype = ctypes.c_int
-        L.htree_b200_forward.argtypes = [ctypes.POINTER(HtreeShape), vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, f32, vp, vp, vp, vp,
+        L.htree_b200_forward.argtypes = [ctypes.POINTER(HtreeShape), vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, f32, vp, vp, vp, vp,
                                          ctypes.POINTER(HtreeTrace), vp, u32, vp]
         L.htree_b200_level_forward.restype = ctypes.c_int
         L.htree_b200_level_forward.argtypes = [ctypes.POINTER(HtreeShape), i32, i32, vp, vp, vp, vp, vp, vp, i32, f32, vp, vp, vp, vp,

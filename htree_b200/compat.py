@@ -78,7 +78,7 @@ def _build(child_k, child_v, parent_k, parent_v, *, N_child, N_parent, B, H_kv, 
     with torch.cuda.device(child_k.device):
         _lib.check(_lib.lib().htree_b200_build_tree(
             ctypes.byref(shape), _lib.ptr_array([child_k.data_ptr(), parent_k.data_ptr()]),
-            _lib.ptr_array([child_v.data_ptr(), parent_v.data_ptr()]), None, None, None, None, _stream()), "htree_build_kernel")
+            _lib.ptr_array([child_v.data_ptr(), parent_v.data_ptr()]), None, None, None, None, None, _stream()), "htree_build_kernel")
 
 
 def _level(q, k_layer, v_layer, prev_selected_parents, cos_cache, sin_cache, layer_max, layer_sum, layer_output,

@@ -113,8 +113,8 @@ int htree_b200_level_sizes(int32_t T, int32_t CR, int32_t MTN, int32_t* sizes, i
 }
 
 int htree_b200_build_tree(const HtreeShape* shape, void* const* layers_k, void* const* layers_v,
-                          void* const* layers_k_rot, void* const* layers_v_blk, const float* cos_cache,
-                          const float* sin_cache, void* stream) {
+                          void* const* layers_k_rot, void* const* layers_k_blk, void* const* layers_v_blk,
+                          const float* cos_cache, const float* sin_cache, void* stream) {
     int32_t ln[HTREE_MAX_LEVELS];
     const int L = check_shape(shape, ln, false);   // top_k plays no role in the tree
     if (L < 0) return L;
@@ -142,12 +142,35 @@ int htree_b200_build_tree(const HtreeShape* shape, void* const* layers_k, void* 
             if (!aligned32(layers_v_blk[l])) return HTREE_E_ALIGN;
         }
     }
+    if (layers_k_blk) {
+        if (!layers_k_rot) return HTREE_E_NULL;       // the blocked keys are built from the rotated keys
+        if (shape->dtype == HTREE_F32 || shape->K != 128 || shape->compression_rate != 16) return HTREE_E_UNSUPPORTED;
+        for (int l = 0; l < L; ++l) {
+            if (!layers_k_blk[l]) return HTREE_E_NULL;
+            if (!aligned32(layers_k_blk[l])) return HTREE_E_ALIGN;
+        }
+    }
     int rc = launch_tree_build(*shape, L, ln, layers_k, layers_v, (cudaStream_t)stream);
     if (rc == 0 && layers_k_rot)
         rc = launch_rotate_keys(*shape, L, ln, layers_k, layers_k_rot, cos_cache, sin_cache, (cudaStream_t)stream);
+    if (rc == 0 && layers_k_blk)
+        rc = launch_block_keys(*shape, L, ln, layers_k_rot, layers_k_blk, (cudaStream_t)stream);
     if (rc == 0 && layers_v_blk)
         rc = launch_block_values(*shape, L, ln, layers_v, layers_v_blk, (cudaStream_t)stream);
     return rc;
+}
+
+int htree_b200_block_keys(const HtreeShape* shape, void* const* layers_k_rot, void* const* layers_k_blk, void* stream) {
+    int32_t ln[HTREE_MAX_LEVELS];
+    const int L = check_shape(shape, ln, false);
+    if (L < 0) return L;
+    if (!layers_k_rot || !layers_k_blk) return HTREE_E_NULL;
+    if (shape->dtype == HTREE_F32 || shape->K != 128 || shape->compression_rate != 16) return HTREE_E_UNSUPPORTED;
+    for (int l = 0; l < L; ++l) {
+        if (!layers_k_rot[l] || !layers_k_blk[l]) return HTREE_E_NULL;
+        if (!aligned16(layers_k_rot[l]) || !aligned32(layers_k_blk[l])) return HTREE_E_ALIGN;
+    }
+    return launch_block_keys(*shape, L, ln, layers_k_rot, layers_k_blk, (cudaStream_t)stream);
 }
 
 int htree_b200_block_values(const HtreeShape* shape, void* const* layers_v, void* const* layers_v_blk, void* stream) {
@@ -180,7 +203,8 @@ int htree_b200_rotate_keys(const HtreeShape* shape, void* const* layers_k, void*
 }
 
 int htree_b200_forward(const HtreeShape* shape, const void* q, void* const* layers_k, void* const* layers_v,
-                       void* const* layers_k_rot, void* const* layers_v_blk, const float* cos_cache, const float* sin_cache, const void* cos_half,
+                       void* const* layers_k_rot, void* const* layers_k_blk, void* const* layers_v_blk, const float* cos_cache,
+                       const float* sin_cache, const void* cos_half,
                        const void* sin_half, int32_t n_pos, float scale, void* out,
                        float* gmax, float* gsum, int32_t* const* parents, const HtreeTrace* trace, int32_t* status,
                        uint32_t flags, void* stream) {
@@ -211,6 +235,8 @@ int htree_b200_forward(const HtreeShape* shape, const void* q, void* const* laye
                 if (!layers_v_blk || !layers_v_blk[l] || !aligned32(layers_v_blk[l])) all = false;
                 else p.lvb[l] = layers_v_blk[l];
             }
+            // optional: with the blocked keys of every level the pipelined kernels run (bulk copies need 16-byte alignment)
+            if (layers_k_blk && layers_k_blk[l] && aligned32(layers_k_blk[l])) p.lkb[l] = layers_k_blk[l];
         }
         all = all && aligned32(q) && aligned32(cos_cache) && aligned32(sin_cache);
         if (all && fwd_mma_supported(p, shape->dtype)) return launch_fwd_mma(p, shape->dtype, (cudaStream_t)stream);

@@ -20,6 +20,7 @@ struct AttnParams {
     const void* lv[HTREE_MAX_LEVELS];
     const void* lkr[HTREE_MAX_LEVELS];   // keys pre-rotated by their child index (16-bit storage types only), or NULL
     const void* lvb[HTREE_MAX_LEVELS];   // values re-laid-out per parent block for the P.V fragments (tree.cu), or NULL
+    const void* lkb[HTREE_MAX_LEVELS];   // pre-rotated keys per parent block in fragment-major order (tree.cu), or NULL
     int32_t ln[HTREE_MAX_LEVELS];   // N_l
     int64_t lpow[HTREE_MAX_LEVELS]; // CR^l
     const float* cosc;
@@ -139,6 +140,13 @@ int launch_merge_to_global(const float* lmax, const float* lsum, const float* lo
                            int64_t rows, int V, cudaStream_t st);
 int launch_final_normalize(const float* gout, const float* gsum, void* out, int dtype, int64_t rows, int V, cudaStream_t st);
 int launch_block_values(const HtreeShape& s, int L, const int32_t* ln, void* const* lv, void* const* lvb, cudaStream_t st);
+int launch_block_keys(const HtreeShape& s, int L, const int32_t* ln, void* const* lkr, void* const* lkb, cudaStream_t st);
+
+// Element order inside a block of the blocked values: fragment-major ([16-byte piece][lane]) for 128-wide heads with 16
+// children per parent and a 16-bit storage type (read through shared memory by the pipelined forward), lane-major
+// (each lane's pieces consecutive) otherwise.
+template <int D, int CR, bool SPLIT>
+constexpr bool kFragmentMajor = (D == 128 && CR == 16 && !SPLIT);
 bool fwd_mma_supported(const AttnParams& p, int dtype);
 int launch_fwd_mma(const AttnParams& p, int dtype, cudaStream_t st);
 bool bwd_mma_supported(const AttnParams& p, int dtype);

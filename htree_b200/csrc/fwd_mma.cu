@@ -28,6 +28,7 @@
 //    The leaf level is a single pass.  One running (max, sum, out) state spans all levels, which is the same
 //    softmax as the reference's per-level states merged afterwards (src/naive.py:215-223).
 #include "mma_common.cuh"
+#include "pipe.cuh"
 
 namespace htree {
 
@@ -51,24 +52,87 @@ struct MmaSmem {   // per warp
     int32_t* par;    // [2][TK]
 };
 
-__host__ __device__ inline size_t mma_smem_per_warp(int TK, int CR) {
+#ifndef HTREE_SEL_MIN_BLOCKS
+#define HTREE_SEL_MIN_BLOCKS 4   // the selection kernel carries no accumulators: 128 registers, 16 warps per SM
+#endif
+// Shared memory of one warp: the selection scratch (importance per candidate, per-chunk maxima; not needed by the
+// accumulation kernel), the kept-candidate bit mask and two parent lists, rounded up to 128 bytes; `pipe_bytes` more for
+// the operand ring of the pipelined kernels.
+__host__ __device__ inline size_t mma_smem_per_warp(int TK, int CR, bool selection_scratch = true, size_t pipe_bytes = 0) {
     const size_t maxc = (size_t)TK * CR;
-    size_t b = sizeof(float) * maxc + sizeof(float) * TK + sizeof(uint32_t) * ((maxc + 31) / 32) + sizeof(int32_t) * 2 * TK;
-    return (b + 15) & ~size_t(15);
+    size_t b = sizeof(uint32_t) * ((maxc + 31) / 32) + sizeof(int32_t) * 2 * TK;
+    if (selection_scratch) b += sizeof(float) * maxc + sizeof(float) * TK;
+    b = (b + 127) & ~size_t(127);
+    return b + pipe_bytes;
+}
+
+// Pipelined kernels (128-wide heads, 16 children per parent, 16-bit types; selection kernel and accumulation kernel): what
+// a chunk needs - the parent's blocked keys (4 KB), when accumulating its blocked values (4 KB), and the rows of the rotary
+// tables for the chunk's rotation - arrives in a per-warp ring in shared memory by asynchronous bulk copies that the warp
+// itself issues a few chunks ahead, each completing on the slot's mbarrier; fragments are then read with conflict-free
+// 16-byte shared loads right before the MMAs that consume them.  Against gathering into registers this keeps loads in
+// flight without holding registers for them, and takes the L2 latency of keys, values AND table rows (the tables do not
+// stay in what is left of L1) off the start of every chunk's dependency chain.
+#ifndef HTREE_PIPE_STAGES_SEL
+#define HTREE_PIPE_STAGES_SEL 2
+#endif
+#ifndef HTREE_PIPE_STAGES_ACC
+#define HTREE_PIPE_STAGES_ACC 2
+#endif
+#ifndef HTREE_PIPE_SEL_WARPS
+#define HTREE_PIPE_SEL_WARPS 5      // selection kernel: 3 blocks of 5 warps per SM (the ring costs shared memory)
+#endif
+#ifndef HTREE_PIPE_SEL_BLOCKS
+#define HTREE_PIPE_SEL_BLOCKS 3
+#endif
+#ifndef HTREE_PIPE_ACC_WARPS
+#define HTREE_PIPE_ACC_WARPS 3      // accumulation kernel: 3 blocks of 3 warps per SM (227 registers each)
+#endif
+#ifndef HTREE_PIPE_ACC_BLOCKS
+#define HTREE_PIPE_ACC_BLOCKS 3
+#endif
+constexpr int kPipeWaitCap = 1 << 16;   // attempts per wait before the kernel gives up and reports status bit 16
+// bytes of one ring slot: blocked keys, blocked values (accumulation), table rows (fp32 cos + sin: 2 * 256 bytes where the
+// query is rotated in fp32 - always in the selection kernel -, packed-half cos + sin: 2 * 128 bytes otherwise)
+__host__ __device__ constexpr uint32_t pipe_slot_bytes(int mode, bool rot16) {
+    return (mode == 1 ? 4096u : 8192u) + ((mode == 1 || !rot16) ? 512u : 256u);
+}
+__host__ __device__ constexpr size_t pipe_bytes_per_warp(int mode, bool rot16) {
+    return (size_t)(mode == 1 ? HTREE_PIPE_STAGES_SEL : HTREE_PIPE_STAGES_ACC) * pipe_slot_bytes(mode, rot16) + 128;
+}
+#ifndef HTREE_SEL_WARPS
+#define HTREE_SEL_WARPS HTREE_FWD_WARPS
+#endif
+// Measured on B200, cfg3 (B=4, T=65536, H=64, H_kv=4, D=128, bf16), ms per launch: selection kernel 56.20 gathering into
+// registers (4 blocks x 4 warps) vs 56.27 pipelined (3 x 5 warps) vs 59.2 (2 x 7); accumulation kernel 107.2 gathering
+// (2 x 4 warps) / 104.2 (3 x 3) vs pipelined 117.7 (2 x 4, 3 stages) / 102.8 (3 x 3, 2 stages) / 117.7 (4 x 2).  Neither
+// kernel is bound by the latency of its gathers: the selection kernel keeps its register path (more resident warps, no
+// ring), the accumulation kernel takes the pipelined one.
+#ifndef HTREE_PIPE_SEL
+#define HTREE_PIPE_SEL 0     // 1: the selection kernel streams its operands too
+#endif
+#ifndef HTREE_PIPE_ACC
+#define HTREE_PIPE_ACC 1     // 0: the accumulation kernel always gathers into registers
+#endif
+__host__ __device__ constexpr int fwd_warps_per_block(int mode, bool pipe) {
+    return pipe ? (mode == 1 ? HTREE_PIPE_SEL_WARPS : HTREE_PIPE_ACC_WARPS) : (mode == 1 ? HTREE_SEL_WARPS : HTREE_FWD_WARPS);
+}
+__host__ __device__ constexpr int fwd_blocks_per_sm(int mode, bool pipe, bool x3) {
+    return pipe ? (mode == 1 ? HTREE_PIPE_SEL_BLOCKS : HTREE_PIPE_ACC_BLOCKS) : (mode == 1 ? (x3 ? 3 : HTREE_SEL_MIN_BLOCKS) : HTREE_FWD_MIN_BLOCKS);
 }
 
 // MODE 0: whole forward in one kernel.  MODE 1: selections only (no accumulator state, so far fewer registers and more
 // resident warps); MODE 2: accumulation only, reading the per-level parent lists that a MODE 1 launch wrote.  When the
 // caller provides parent buffers the forward runs as MODE 1 + MODE 2.
-#ifndef HTREE_SEL_MIN_BLOCKS
-#define HTREE_SEL_MIN_BLOCKS 4   // the selection kernel carries no accumulators: 128 registers, 16 warps per SM
-#endif
 // NR = 1: groups of at most 8 heads (rows g+8 of every fragment are padding and their ALU work is skipped).
 // T = float: split-half products (mma_common.cuh), 64-wide heads; K' and the blocked values then hold a hi and a lo plane.
-template <typename T, int D, bool ROT16, int MODE, int NR, int CR>
-__global__ void __launch_bounds__(MW * 32, MODE == 1 ? (std::is_same<T, float>::value ? 3 : HTREE_SEL_MIN_BLOCKS) : HTREE_FWD_MIN_BLOCKS)
+template <typename T, int D, bool ROT16, int MODE, int NR, int CR, bool PIPE = false>
+__global__ void __launch_bounds__(fwd_warps_per_block(MODE, PIPE) * 32, fwd_blocks_per_sm(MODE, PIPE, std::is_same<T, float>::value))
 fwd_mma_kernel(const __grid_constant__ AttnParams p) {
     constexpr bool X3 = std::is_same<T, float>::value;
+    constexpr int MWK = fwd_warps_per_block(MODE, PIPE);   // warps (= queries) per block
+    static_assert(!PIPE || (D == 128 && CR == 16 && !X3 && (MODE == 1 || MODE == 2)), "pipelined kernels: 128-wide heads, 16 children, 16-bit types");
+    constexpr bool FRAGV = kFragmentMajor<D, CR, X3>;   // element order of the blocked values
     constexpr uint32_t kAllChildren = (1u << CR) - 1u;   // CR = children per parent: 16, or 8 (then tile 1 stays empty)
     constexpr int HALF = D / 2;
     constexpr int KS = D / 16;        // k-steps of the score product
@@ -81,18 +145,87 @@ fwd_mma_kernel(const __grid_constant__ AttnParams p) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, r = lane & 3;
-    const int tl = blockIdx.x * MW + warp;
+    const int tl = blockIdx.x * MWK + warp;
     if (tl >= p.Tq) return;                        // warps are independent: only __syncwarp below
     const int t = p.t0 + tl;
     const int b = blockIdx.y / p.Hkv, hk = blockIdx.y % p.Hkv;
     const int G = p.G, TK = p.TK, L = p.L;
     const int maxc = TK * CR;
-    unsigned char* wbase = smem_raw + (size_t)warp * mma_smem_per_warp(TK, CR);
+    constexpr bool kScratch = MODE != 2;           // the accumulation kernel keeps no importance array
+    unsigned char* wbase = smem_raw + (size_t)warp * mma_smem_per_warp(TK, CR, kScratch, PIPE ? pipe_bytes_per_warp(MODE, ROT16) : 0);
     float* imp = reinterpret_cast<float*>(wbase);
-    float* cmax = imp + maxc;
-    uint32_t* selw = reinterpret_cast<uint32_t*>(cmax + TK);
+    float* cmax = imp + (kScratch ? maxc : 0);
+    uint32_t* selw = reinterpret_cast<uint32_t*>(cmax + (kScratch ? TK : 0));
     int32_t* par = reinterpret_cast<int32_t*>(selw + (maxc + 31) / 32);
     int32_t* nxt = par + TK;
+
+    // ---- operand ring of the pipelined kernels ----
+    constexpr int NSTG = MODE == 1 ? HTREE_PIPE_STAGES_SEL : HTREE_PIPE_STAGES_ACC;
+    constexpr uint32_t SLOT = pipe_slot_bytes(MODE, ROT16);
+    constexpr uint32_t TAB_OFF = MODE == 1 ? 4096u : 8192u;                 // table rows follow the operand blocks
+    constexpr bool kTabF32 = MODE == 1 || !ROT16;                           // fp32 rows (256 B each) or packed-half rows (128 B each)
+    constexpr uint32_t TAB_ROW = kTabF32 ? 256u : 128u;
+    unsigned char* ring = wbase + mma_smem_per_warp(TK, CR, kScratch);      // 128-byte aligned
+    uint64_t* bars = reinterpret_cast<uint64_t*>(ring + (size_t)NSTG * SLOT);
+    uint32_t pn = 0, pissued = 0;     // chunks consumed / issued by this warp so far: slot = n % NSTG, phase parity = (n / NSTG) & 1
+    const unsigned char* kblk = nullptr;    // this level's blocked keys / values of (b, hk); parents are blk_stride bytes apart
+    const unsigned char* vblk = nullptr;
+    int64_t blk_stride = 0;
+    int blk_count = 0, pipe_rp = 0;         // pipe_rp: rotation position of the level (the chunk at slot a rotates by rp - CR*a)
+    if constexpr (PIPE) {
+        if (lane == 0) {
+            for (int i = 0; i < NSTG; ++i) mbar_init(&bars[i], 1);
+            fence_barrier_init();
+        }
+        __syncwarp();
+    }
+    auto pipe_issue = [&](uint32_t n, int a) {       // lane 0: start the copies for the chunk at parent slot a into ring slot n % NSTG
+        int pb = par[a];
+        if (pb < 0 || pb >= blk_count) pb = 0;       // flagged where the chunk is consumed
+        const int sl = (int)(n % NSTG);
+        unsigned char* dst = ring + (size_t)sl * SLOT;
+        mbar_arrive_expect_tx(&bars[sl], SLOT);
+        bulk_copy_g2s(dst, kblk + (int64_t)pb * blk_stride, 4096u, &bars[sl]);
+        if (MODE == 2) bulk_copy_g2s(dst + 4096, vblk + (int64_t)pb * blk_stride, 4096u, &bars[sl]);
+        const int64_t row = (int64_t)(pipe_rp - CR * a);
+        if (kTabF32) {
+            bulk_copy_g2s(dst + TAB_OFF, p.cosc + row * HALF, TAB_ROW, &bars[sl]);
+            bulk_copy_g2s(dst + TAB_OFF + TAB_ROW, p.sinc + row * HALF, TAB_ROW, &bars[sl]);
+        } else {
+            bulk_copy_g2s(dst + TAB_OFF, p.cosh + row * HALF, TAB_ROW, &bars[sl]);
+            bulk_copy_g2s(dst + TAB_OFF + TAB_ROW, p.sinh + row * HALF, TAB_ROW, &bars[sl]);
+        }
+    };
+    // Give up after a wait ran out: flag it, wait (bounded again) for the copies still in flight into this warp's ring, and
+    // leave.  Never taken unless something is badly wrong; it keeps the kernel from spinning forever.
+    auto pipe_abort = [&]() {
+        if (lane == 0 && p.status) atomicOr(p.status, 16);
+        for (uint32_t n = pn; n < pissued; ++n) mbar_wait_bounded(&bars[n % NSTG], (n / NSTG) & 1u, kPipeWaitCap);
+    };
+    // before the first chunk of a loop over `count` parents (par[0 .. count)): fill the ring
+    auto pipe_begin = [&](int count) {
+        __syncwarp();
+        const int ahead = count < NSTG - 1 ? count : NSTG - 1;
+        if (lane == 0) {
+            fence_proxy_async();
+            for (int j = 0; j < ahead; ++j) pipe_issue(pn + j, j);
+        }
+        pissued = pn + ahead;
+    };
+    // chunk a of `count`: refill the slot the previous chunk used, then wait for this chunk's block(s).  Returns the slot,
+    // or nullptr after a wait ran out (the caller returns).
+    auto pipe_next = [&](int a, int count) -> const unsigned char* {
+        __syncwarp();                                   // every lane is done reading the slot that is refilled now
+        if (a + NSTG - 1 < count) {
+            if (lane == 0) { fence_proxy_async(); pipe_issue(pn + NSTG - 1, a + NSTG - 1); }
+            pissued = pn + NSTG;
+        }
+        const int sl = (int)(pn % NSTG);
+        if (!mbar_wait_bounded(&bars[sl], (pn / NSTG) & 1u, kPipeWaitCap)) { pipe_abort(); return nullptr; }
+        ++pn;
+        return ring + (size_t)sl * SLOT;
+    };
+    const unsigned char* slot = nullptr;                // operand blocks of the chunk being computed
 
     constexpr bool kSelectKernel = MODE == 1, kAccumulateKernel = MODE == 2;
     const bool select_only = kSelectKernel || (MODE == 0 && (p.flags & HTREE_FWD_SELECT_ONLY) != 0);
@@ -152,10 +285,24 @@ fwd_mma_kernel(const __grid_constant__ AttnParams p) {
         const int64_t vb_stride = (int64_t)p.Hkv * (CR * D / 2);     // 32-bit words between consecutive parents
         const int64_t vb_plane = (int64_t)p.B * ((Nl + CR - 1) / CR) * vb_stride;   // fp32 storage: words from the hi plane to the lo plane
         const uint32_t* vbq = reinterpret_cast<const uint32_t*>(p.lvb[l]) +
-                              ((int64_t)b * ((Nl + CR - 1) / CR) * p.Hkv + hk) * (CR * D / 2) + (8 * r + g) * (NOT * (CR / 8));
+                              ((int64_t)b * ((Nl + CR - 1) / CR) * p.Hkv + hk) * (CR * D / 2) +
+                              (FRAGV ? 4 * lane : (8 * r + g) * (NOT * (CR / 8)));
+        if constexpr (PIPE) {
+            blk_count = (Nl + CR - 1) / CR;
+            blk_stride = (int64_t)p.Hkv * (CR * D * 2);
+            pipe_rp = rp;
+            kblk = reinterpret_cast<const unsigned char*>(p.lkb[l]) + ((int64_t)b * blk_count * p.Hkv + hk) * (CR * D * 2);
+            vblk = reinterpret_cast<const unsigned char*>(p.lvb[l]) + ((int64_t)b * blk_count * p.Hkv + hk) * (CR * D * 2);
+        }
         auto score = [&](int a, float (&S0)[4], float (&S1)[4], bool select) {
             int node0 = par[a] * CR;
             if (node0 < 0 || node0 >= Nl) { if (p.status) atomicOr(p.status, 4); node0 = 0; }
+            if constexpr (PIPE) {
+                // the rotation of a chunk is fixed by the kernel: fp32 tables where the Top-K is decided (selection kernel) or
+                // no packed-half tables were given, packed-half tables otherwise; its table rows are in the slot
+                score_chunk_sm<D, !kTabF32, NR>(p, reinterpret_cast<const uint4*>(slot), slot + TAB_OFF, lane, qraw, S0, S1);
+                return;
+            }
 #ifdef HTREE_KNOCK_L1ROWS   // timing experiments only: every gather hits the same rows (wrong results, no L2 latency)
             node0 = 0;
 #endif
@@ -181,7 +328,23 @@ fwd_mma_kernel(const __grid_constant__ AttnParams p) {
             // that ARE the B fragments of the P.V products; the warp reads the block front to back
             constexpr int NB = CR / 8, CHW = NOT * NB;
             uint32_t vw[CHW], vl[X3 ? CHW : 1];     // fp32 storage: hi plane and lo plane
-            {
+            if constexpr (PIPE) {
+                // piece i of this lane = the fragments of output tiles 2i and 2i+1, read from the chunk's slot
+                const uint4* vs = reinterpret_cast<const uint4*>(slot + 4096);
+#pragma unroll
+                for (int i = 0; i < CHW / 4; ++i) {
+                    const uint4 x = lds128(vs + i * 32 + lane);
+                    vw[4 * i] = x.x; vw[4 * i + 1] = x.y; vw[4 * i + 2] = x.z; vw[4 * i + 3] = x.w;
+                }
+            } else if constexpr (FRAGV) {
+                // fragment-major blocks read straight from global memory (the one-kernel forward): 16-byte pieces
+                const uint4* src = reinterpret_cast<const uint4*>(vbq + (int64_t)pblk * vb_stride);
+#pragma unroll
+                for (int i = 0; i < CHW / 4; ++i) {
+                    const uint4 x = stream_rows ? ldg16_stream(src + i * 32) : ldg16(src + i * 32);
+                    vw[4 * i] = x.x; vw[4 * i + 1] = x.y; vw[4 * i + 2] = x.z; vw[4 * i + 3] = x.w;
+                }
+            } else {
                 const uint32_t* src = vbq + (int64_t)pblk * vb_stride;
 #pragma unroll
                 for (int i = 0; i < CHW / 8; ++i) {
@@ -274,7 +437,9 @@ fwd_mma_kernel(const __grid_constant__ AttnParams p) {
                     }
                 }
                 __syncwarp();
+                if constexpr (PIPE) pipe_begin(np);
                 for (int a = 0; a < np; ++a) {
+                    if constexpr (PIPE) { slot = pipe_next(a, np); if (!slot) return; }
                     const uint32_t kept = (selw[(a * CR) >> 5] >> ((a * CR) & 31)) & kAllChildren;
                     const uint32_t valid = a == np - 1 ? ((2u << rc) - 1u) : kAllChildren;
                     const uint32_t mask = ~kept & valid;
@@ -290,7 +455,9 @@ fwd_mma_kernel(const __grid_constant__ AttnParams p) {
                 for (int j = lane; j < TK; j += 32) nxt[j] = j < nc ? par[j / CR] * CR + j % CR : -1;
             } else {
                 // ---- pass 1: shared importance of every candidate ----
+                if constexpr (PIPE) pipe_begin(np);
                 for (int a = 0; a < np; ++a) {
+                    if constexpr (PIPE) { slot = pipe_next(a, np); if (!slot) return; }
                     float S0[4], S1[4];
                     score(a, S0, S1, true);
                     const int jb = a * CR;
@@ -393,7 +560,9 @@ fwd_mma_kernel(const __grid_constant__ AttnParams p) {
             __syncwarp();
             int32_t* tmp = par; par = nxt; nxt = tmp;
         } else {
+            if constexpr (PIPE) pipe_begin(np);
             for (int a = 0; a < np; ++a) {
+                if constexpr (PIPE) { slot = pipe_next(a, np); if (!slot) return; }
                 const uint32_t valid = a == np - 1 ? ((2u << rc) - 1u) : kAllChildren;
                 float S0[4], S1[4];
                 score(a, S0, S1, false);
@@ -444,12 +613,31 @@ fwd_mma_kernel(const __grid_constant__ AttnParams p) {
 
 template <typename T, int D, bool ROT16, int MODE, int NR, int CR>
 static int launch_mma_mode_cr(const AttnParams& p, cudaStream_t st) {
-    const size_t smem = mma_smem_per_warp(p.TK, CR) * MW;
+    // pipelined variant where the shape has one and the caller provided the blocked keys
+    constexpr bool kHasPipe = D == 128 && CR == 16 && !std::is_same<T, float>::value &&
+                              ((MODE == 1 && HTREE_PIPE_SEL) || (MODE == 2 && HTREE_PIPE_ACC));
+    if constexpr (kHasPipe) {
+        bool pipe = !(p.flags & HTREE_FWD_NO_PIPELINE);
+        for (int l = 0; l < p.L; ++l) pipe = pipe && p.lkb[l] != nullptr && (MODE == 1 || p.lvb[l] != nullptr);
+        constexpr int W = fwd_warps_per_block(MODE, true);
+        const size_t psmem = mma_smem_per_warp(p.TK, CR, MODE != 2, pipe_bytes_per_warp(MODE, ROT16)) * W;
+        // the ring must leave room for the intended number of resident blocks (1 KB per block is reserved by the system)
+        if (pipe && (psmem + 1024) * fwd_blocks_per_sm(MODE, true, false) <= 227 * 1024) {
+            cudaError_t e = cudaFuncSetAttribute(fwd_mma_kernel<T, D, ROT16, MODE, NR, CR, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)psmem);
+            if (e != cudaSuccess) return (int)e;
+            dim3 grid((p.Tq + W - 1) / W, p.B * p.Hkv);
+            fwd_mma_kernel<T, D, ROT16, MODE, NR, CR, true><<<grid, W * 32, psmem, st>>>(p);
+            note_launch();
+            return (int)cudaGetLastError();
+        }
+    }
+    constexpr int W0 = fwd_warps_per_block(MODE, false);
+    const size_t smem = mma_smem_per_warp(p.TK, CR, MODE != 2) * W0;
     if (smem > 200 * 1024) return HTREE_E_UNSUPPORTED;
     cudaError_t e = cudaFuncSetAttribute(fwd_mma_kernel<T, D, ROT16, MODE, NR, CR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    dim3 grid((p.Tq + MW - 1) / MW, p.B * p.Hkv);
-    fwd_mma_kernel<T, D, ROT16, MODE, NR, CR><<<grid, MW * 32, smem, st>>>(p);
+    dim3 grid((p.Tq + W0 - 1) / W0, p.B * p.Hkv);
+    fwd_mma_kernel<T, D, ROT16, MODE, NR, CR><<<grid, W0 * 32, smem, st>>>(p);
     note_launch();
     return (int)cudaGetLastError();
 }

@@ -4,6 +4,7 @@
 #include <type_traits>
 
 #include "common.cuh"
+#include "pipe.cuh"
 
 namespace htree {
 
@@ -240,6 +241,90 @@ __device__ __forceinline__ void score_chunk(const AttnParams& p, const __half* k
     }
 }
 
+// score_chunk with the key fragments read from shared memory: `ks4` is a parent's blocked keys in fragment-major order
+// (tree.cu: piece [ks][lane] = the four B-fragment registers of k-step ks), so each 16-byte shared load feeds the two
+// MMAs of one k-step.  Same arithmetic, operand values and accumulation order as score_chunk.
+template <int D, bool ROT16, int NR>
+__device__ __forceinline__ void score_chunk_sm(const AttnParams& p, const uint4* ks4, const unsigned char* tab, int lane,
+                                               const uint32_t (&qraw)[2][2][D / 16], float (&S0)[4], float (&S1)[4]) {
+    // tab: the chunk's table rows in shared memory: ROT16 ? [cos*scale | sin*scale] as IEEE half (D/2 each)
+    //                                                      : [cos | sin] as fp32 (D/2 each)
+    constexpr int HALF = D / 2, KS = D / 16, PPT = HALF / 4;
+    using FS = Frag<__half>;
+    const int r = lane & 3;
+    S0[0] = S0[1] = S0[2] = S0[3] = 0.f;
+    S1[0] = S1[1] = S1[2] = S1[3] = 0.f;
+    float T0[4] = {0.f, 0.f, 0.f, 0.f}, U1[4] = {0.f, 0.f, 0.f, 0.f};
+    if (ROT16) {
+        uint32_t ch[KS], sh[KS];   // (cos, sin) * scale of pairs (2ks, 2ks+1), packed half2: this lane's PPT pairs
+#pragma unroll
+        for (int i = 0; i < KS / 4; ++i) {
+            const uint4 c4 = lds128(tab + 2 * (PPT * r) + 16 * i);
+            const uint4 s4 = lds128(tab + 2 * HALF + 2 * (PPT * r) + 16 * i);
+            ch[4 * i] = c4.x; ch[4 * i + 1] = c4.y; ch[4 * i + 2] = c4.z; ch[4 * i + 3] = c4.w;
+            sh[4 * i] = s4.x; sh[4 * i + 1] = s4.y; sh[4 * i + 2] = s4.z; sh[4 * i + 3] = s4.w;
+        }
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+            const uint4 kb = lds128(ks4 + ks * 32 + lane);
+            uint32_t a[4];
+            const __half2 c2 = *reinterpret_cast<const __half2*>(&ch[ks]), s2 = *reinterpret_cast<const __half2*>(&sh[ks]);
+            a[1] = 0u; a[3] = 0u;
+#pragma unroll
+            for (int rr = 0; rr < NR; ++rr) {
+                const __half2 lo = *reinterpret_cast<const __half2*>(&qraw[rr][0][ks]);
+                const __half2 hi = *reinterpret_cast<const __half2*>(&qraw[rr][1][ks]);
+                const __half2 x = __hfma2(lo, c2, __hneg2(__hmul2(hi, s2)));
+                const __half2 y = __hfma2(hi, c2, __hmul2(lo, s2));
+                a[rr] = *reinterpret_cast<const uint32_t*>(&x);
+                a[2 + rr] = *reinterpret_cast<const uint32_t*>(&y);
+            }
+            if (ks & 1) {
+                FS::mma(T0, a[0], a[1], a[2], a[3], kb.x, kb.y);
+                FS::mma(U1, a[0], a[1], a[2], a[3], kb.z, kb.w);
+            } else {
+                FS::mma(S0, a[0], a[1], a[2], a[3], kb.x, kb.y);
+                FS::mma(S1, a[0], a[1], a[2], a[3], kb.z, kb.w);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { S0[i] += T0[i]; S1[i] += U1[i]; }
+        return;
+    }
+    const unsigned char* cp = tab + 4 * (PPT * r);
+    const unsigned char* sp = tab + 4 * HALF + 4 * (PPT * r);
+#pragma unroll
+    for (int ks2 = 0; ks2 < KS; ks2 += 2) {
+        const uint4 c4 = lds128(cp + 8 * ks2);
+        const uint4 s4 = lds128(sp + 8 * ks2);
+        const float cs[4] = {__uint_as_float(c4.x), __uint_as_float(c4.y), __uint_as_float(c4.z), __uint_as_float(c4.w)};
+        const float sn[4] = {__uint_as_float(s4.x), __uint_as_float(s4.y), __uint_as_float(s4.z), __uint_as_float(s4.w)};
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int ks = ks2 + u;
+            const uint4 kb = lds128(ks4 + ks * 32 + lane);
+            uint32_t a[4];
+            a[1] = 0u; a[3] = 0u;
+#pragma unroll
+            for (int rr = 0; rr < NR; ++rr) {
+                const float2 lo = FS::unpack(qraw[rr][0][ks]), hi = FS::unpack(qraw[rr][1][ks]);
+                const float c0 = cs[2 * u], c1 = cs[2 * u + 1], s0 = sn[2 * u], s1 = sn[2 * u + 1];
+                a[rr] = FS::pack(lo.x * c0 - hi.x * s0, lo.y * c1 - hi.y * s1);
+                a[2 + rr] = FS::pack(lo.x * s0 + hi.x * c0, lo.y * s1 + hi.y * c1);
+            }
+            if (u) {
+                FS::mma(T0, a[0], a[1], a[2], a[3], kb.x, kb.y);
+                FS::mma(U1, a[0], a[1], a[2], a[3], kb.z, kb.w);
+            } else {
+                FS::mma(S0, a[0], a[1], a[2], a[3], kb.x, kb.y);
+                FS::mma(S1, a[0], a[1], a[2], a[3], kb.z, kb.w);
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { S0[i] = (S0[i] + T0[i]) * p.scale; S1[i] = (S1[i] + U1[i]) * p.scale; }
+}
+
 // Raw rows g and g+8 of a [heads, D] block in the fragment order used above (zero for rows beyond the group).
 template <typename T, int D>
 __device__ __forceinline__ void load_rows(const T* base, int g, int r, const bool (&row_ok)[2], uint32_t (&raw)[2][2][D / 16]) {
@@ -360,14 +445,21 @@ __device__ __forceinline__ void score_chunk_x3(const AttnParams& p, const __half
                 kr[tl][1][2 * ks] = khx * c0 - klx * s0; kr[tl][1][2 * ks + 1] = khy * c1 - kly * s1;
             }
         }
-        FS::mma(A0, ah[0], ah[1], ah[2], ah[3], kh[0][0][ks], kh[0][1][ks]);
+        // The hi*hi product of every k-step starts from a zero accumulator and is added to the running sum with an ordinary
+        // (round-to-nearest) fp32 add: inside the MMA the 16 products and the accumulator are aligned to the largest of
+        // them and truncated, so a running score of magnitude 2^6 in the accumulator would cost 8x the rounding error of
+        // the products alone, and always in the same direction.  The hi*lo chains are 2^-11 smaller: no such concern.
+        float h0[4] = {0.f, 0.f, 0.f, 0.f}, h1[4] = {0.f, 0.f, 0.f, 0.f};
+        FS::mma(h0, ah[0], ah[1], ah[2], ah[3], kh[0][0][ks], kh[0][1][ks]);
         FS::mma(B0, ah[0], ah[1], ah[2], ah[3], kl[0][0][ks], kl[0][1][ks]);
         FS::mma(C0, al[0], al[1], al[2], al[3], kh[0][0][ks], kh[0][1][ks]);
         if (T1) {
-            FS::mma(A1, ah[0], ah[1], ah[2], ah[3], kh[1][0][ks], kh[1][1][ks]);
+            FS::mma(h1, ah[0], ah[1], ah[2], ah[3], kh[1][0][ks], kh[1][1][ks]);
             FS::mma(B1, ah[0], ah[1], ah[2], ah[3], kl[1][0][ks], kl[1][1][ks]);
             FS::mma(C1, al[0], al[1], al[2], al[3], kh[1][0][ks], kh[1][1][ks]);
         }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { A0[i] += h0[i]; A1[i] += h1[i]; }
     }
 #pragma unroll
     for (int i = 0; i < 4; ++i) { S0[i] = A0[i] + (B0[i] + C0[i]); S1[i] = A1[i] + (B1[i] + C1[i]); }

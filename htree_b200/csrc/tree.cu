@@ -305,6 +305,23 @@ __global__ void __launch_bounds__(256) block_values_kernel(const __grid_constant
                 }
             }
         }
+    if (kFragmentMajor<D, CR, SPLIT>) {
+        // fragment-major order (128-wide heads, 16 children, 16-bit types): 16-byte piece i of lane (g, r) sits at
+        // [i][4g + r], so that a warp reading piece i from shared memory touches 512 consecutive bytes, and piece i is
+        // exactly what output tiles 2i and 2i+1 need: {b0(2i), b1(2i), b0(2i+1), b1(2i+1)}
+        uint4* d4 = reinterpret_cast<uint4*>(reinterpret_cast<uint32_t*>(a.dst) + blk * (int64_t)(CR * D / 2));
+        const int lane = 4 * g + r;
+#pragma unroll
+        for (int i = 0; i < CHW / 4; ++i) {
+            uint32_t o4[4];
+#pragma unroll
+            for (int u = 0; u < 2; ++u)
+#pragma unroll
+                for (int j = 0; j < NB; ++j) o4[u * NB + j] = (uint32_t)e[j][0][2 * i + u] | ((uint32_t)e[j][1][2 * i + u] << 16);
+            d4[i * 32 + lane] = make_uint4(o4[0], o4[1], o4[2], o4[3]);
+        }
+        return;
+    }
     uint32_t* dst = reinterpret_cast<uint32_t*>(a.dst) + blk * (int64_t)(CR * D / 2) + (int64_t)slot * CHW;
 #pragma unroll
     for (int pl = 0; pl < (SPLIT ? 2 : 1); ++pl) {
@@ -319,6 +336,57 @@ __global__ void __launch_bounds__(256) block_values_kernel(const __grid_constant
 #pragma unroll
         for (int i = 0; i < CHW / 4; ++i) reinterpret_cast<uint4*>(d)[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
     }
+}
+
+// K'^ ("blocked keys", 128-wide heads, 16 children, 16-bit types): the pre-rotated key rows of one parent's children in
+// fragment-major order.  Block (b, p, h) starts at ((b*NBLK + p)*Hkv + h) * 16*128 halves; its 16-byte piece [ks][4g + r]
+// holds, for k-step ks of the score product, the four B-fragment registers of lane (g, r):
+//   { K'[16p + g][16r + 2ks, +1],  K'[16p + g][64 + 16r + 2ks, +1],  K'[16p + 8 + g][16r + 2ks, +1],  K'[16p + 8 + g][64 + 16r + 2ks, +1] }
+// (tile 0 low half, tile 0 high half, tile 1 low half, tile 1 high half).  Rows past the end of the level are zero.
+__global__ void __launch_bounds__(256) block_keys_kernel(const __grid_constant__ BlkArgs a) {
+    constexpr int D = 128, CR = 16, KS = 8;
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= a.total) return;
+    const int lane = (int)(idx & 31), g = lane >> 2, r = lane & 3;
+    const int64_t blk = idx >> 5;
+    const int h = (int)(blk % a.Hkv);
+    const int p = (int)((blk / a.Hkv) % a.NBLK);
+    const int64_t b = blk / ((int64_t)a.Hkv * a.NBLK);
+    const uint32_t* src = reinterpret_cast<const uint32_t*>(a.src);      // half pairs
+    uint32_t kb[2][2][KS];
+#pragma unroll
+    for (int tl = 0; tl < 2; ++tl) {
+        const int row = p * CR + 8 * tl + g;
+        const bool ok = row < a.N;
+        const int64_t off = (((b * a.N + (ok ? row : 0)) * a.Hkv + h) * (int64_t)D + 16 * r) / 2;   // in 32-bit words
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf)
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                uint4 x = make_uint4(0u, 0u, 0u, 0u);
+                if (ok) x = __ldg(reinterpret_cast<const uint4*>(src + off + hf * (D / 4)) + i);
+                kb[tl][hf][4 * i] = x.x; kb[tl][hf][4 * i + 1] = x.y; kb[tl][hf][4 * i + 2] = x.z; kb[tl][hf][4 * i + 3] = x.w;
+            }
+    }
+    uint4* d4 = reinterpret_cast<uint4*>(reinterpret_cast<uint32_t*>(a.dst) + blk * (int64_t)(CR * D / 2));
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) d4[ks * 32 + lane] = make_uint4(kb[0][0][ks], kb[0][1][ks], kb[1][0][ks], kb[1][1][ks]);
+}
+
+int launch_block_keys(const HtreeShape& s, int L, const int32_t* ln, void* const* lkr, void* const* lkb, cudaStream_t st) {
+    if (s.dtype == HTREE_F32 || s.K != 128 || s.compression_rate != 16) return HTREE_E_UNSUPPORTED;
+    for (int l = 0; l < L; ++l) {
+        BlkArgs a;
+        a.src = lkr[l]; a.dst = lkb[l];
+        a.Hkv = s.H_kv; a.N = ln[l]; a.NBLK = (ln[l] + 15) / 16;
+        a.total = (int64_t)s.B * a.NBLK * s.H_kv * 32;
+        a.plane = 0;
+        block_keys_kernel<<<(unsigned)((a.total + 255) / 256), 256, 0, st>>>(a);
+        note_launch();
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return (int)e;
+    }
+    return 0;
 }
 
 int launch_block_values(const HtreeShape& s, int L, const int32_t* ln, void* const* lv, void* const* lvb, cudaStream_t st) {

@@ -204,6 +204,6 @@ def htree_forward_sequence_parallel(q_local: torch.Tensor, k: torch.Tensor, v: t
     from .ops import block_values, rotate_keys
     layers_k, layers_v = build_tree_sequence_parallel(k, v, compression_rate, max_top_nodes, group, ranges=ranges)
     layers_kr = rotate_keys(layers_k, compression_rate, max_top_nodes, rope_base)   # local work on the gathered levels
-    layers_vb = block_values(layers_v, compression_rate, max_top_nodes) if layers_kr is not None else None
+    layers_vb = block_values(layers_v, compression_rate, max_top_nodes, layers_kr) if layers_kr is not None else None
     return htree_forward(q_local, k, v, compression_rate, max_top_nodes, top_k_per_layer, scale, rope_base,
                          _q_offset=t0, _layers=(layers_k, layers_v, layers_kr, layers_vb))

@@ -179,6 +179,8 @@ def build_tree(k: torch.Tensor, v: torch.Tensor, compression_rate: int, max_top_
     layers_kr = [_rotated_like(x) for x in layers_k] if want_rot else None
     want_blk = want_rot and _blockable(V, compression_rate)
     layers_vb = [_blocked_like(x, compression_rate) for x in layers_v] if want_blk else None
+    want_kblk = want_blk and _pipelined(k.dtype, K, compression_rate)
+    layers_kb = [_blocked_like(x, compression_rate) for x in layers_kr] if want_kblk else None
     if len(sizes) > 1 or want_rot:
         shape = _lib.HtreeShape(B, T, H_kv, H_kv, K, V, int(compression_rate), 1, int(max_top_nodes),
                                 _DTYPES[k.dtype])   # H and top_k play no role in the tree
@@ -188,12 +190,27 @@ def build_tree(k: torch.Tensor, v: torch.Tensor, compression_rate: int, max_top_
         with torch.cuda.device(k.device):
             _lib.check(_lib.lib().htree_b200_build_tree(
                 ctypes.byref(shape), _ptrs(layers_k), _ptrs(layers_v), _ptrs(layers_kr) if want_rot else None,
-                _ptrs(layers_vb) if want_blk else None,
+                _ptrs(layers_kb) if want_kblk else None, _ptrs(layers_vb) if want_blk else None,
                 cos_c.data_ptr() if want_rot else None, sin_c.data_ptr() if want_rot else None, _stream()),
                 "build_tree")
     if rope_base is not None:
-        return layers_k, layers_v, layers_kr, layers_vb
+        return layers_k, layers_v, layers_kr, OperandBlocks(layers_vb, layers_kb) if layers_vb is not None else None
     return layers_k, layers_v
+
+
+class OperandBlocks(list):
+    """The blocked values of every level (the list itself) together with the blocked keys of every level (`.keys`, or
+    None where the pipelined kernels do not apply): the per-parent operand copies of the tensor-core forward."""
+
+    def __init__(self, values, keys=None):
+        super().__init__(values)
+        self.keys = keys
+
+
+def _pipelined(dtype, K: int, compression_rate: int) -> bool:
+    """Shapes with a pipelined forward (operand blocks streamed through shared memory): 16-bit types, 128-wide heads,
+    16 children per parent."""
+    return dtype != torch.float32 and K == 128 and int(compression_rate) == 16
 
 
 def build_tree_into(k: torch.Tensor, v: torch.Tensor, out_k, out_v, compression_rate: int, max_top_nodes: int) -> None:
@@ -214,7 +231,7 @@ def build_tree_into(k: torch.Tensor, v: torch.Tensor, out_k, out_v, compression_
     shape = _lib.HtreeShape(B, T, H_kv, H_kv, K, V, int(compression_rate), 1, int(max_top_nodes), _DTYPES[k.dtype])
     with torch.cuda.device(k.device):
         _lib.check(_lib.lib().htree_b200_build_tree(ctypes.byref(shape), _ptrs(layers_k), _ptrs(layers_v), None, None, None, None,
-                                                    _stream()), "build_tree")
+                                                    None, _stream()), "build_tree")
 
 
 def _split_half(dtype, K: int, V: int, compression_rate: int) -> bool:
@@ -244,17 +261,22 @@ def _blocked_like(x: torch.Tensor, compression_rate: int) -> torch.Tensor:
     return torch.empty(B, (N + cr - 1) // cr * cr, H_kv, V, dtype=x.dtype, device=x.device)
 
 
-def block_values(layers_v, compression_rate: int, max_top_nodes: int):
-    """Blocked copies of existing value levels (see build_tree); None for fp32 or shapes the tensor-core forward does not cover."""
+def block_values(layers_v, compression_rate: int, max_top_nodes: int, layers_k_rot=None):
+    """Blocked copies of existing value levels (see build_tree) and, given the K' levels, of the keys where the pipelined
+    forward applies; None for shapes the tensor-core forward does not cover."""
     v = layers_v[0]
     B, T, H_kv, V = v.shape
     if not _blockable(V, compression_rate) or (v.dtype == torch.float32 and V != 64):
         return None
     out = [_blocked_like(x, compression_rate) for x in layers_v]
     shape = _lib.HtreeShape(B, T, H_kv, H_kv, V, V, int(compression_rate), 1, int(max_top_nodes), _DTYPES[v.dtype])
+    keys = None
     with torch.cuda.device(v.device):
         _lib.check(_lib.lib().htree_b200_block_values(ctypes.byref(shape), _ptrs(layers_v), _ptrs(out), _stream()), "block_values")
-    return out
+        if layers_k_rot is not None and _pipelined(v.dtype, layers_k_rot[0].shape[-1], compression_rate):
+            keys = [_blocked_like(x, compression_rate) for x in layers_k_rot]
+            _lib.check(_lib.lib().htree_b200_block_keys(ctypes.byref(shape), _ptrs(layers_k_rot), _ptrs(keys), _stream()), "block_keys")
+    return OperandBlocks(out, keys)
 
 
 def rotate_keys(layers_k, compression_rate: int, max_top_nodes: int, rope_base: float):
@@ -278,7 +300,9 @@ def _run_forward(shape, q, layers_k, layers_v, cos_cache, sin_cache, scale, out,
     with torch.cuda.device(q.device):
         rc = _lib.lib().htree_b200_forward(
             ctypes.byref(shape), q.data_ptr(), _ptrs(layers_k), _ptrs(layers_v),
-            _ptrs(layers_kr) if layers_kr is not None else None, _ptrs(layers_vb) if layers_vb is not None else None,
+            _ptrs(layers_kr) if layers_kr is not None else None,
+            _ptrs(layers_vb.keys) if getattr(layers_vb, "keys", None) is not None else None,
+            _ptrs(layers_vb) if layers_vb is not None else None,
             cos_cache.data_ptr(), sin_cache.data_ptr(),
             half_tables[0].data_ptr() if half_tables else None, half_tables[1].data_ptr() if half_tables else None,
             cos_cache.shape[0], float(scale),
@@ -294,7 +318,7 @@ def htree_forward(
     scale: Optional[float] = None, rope_base: float = 10000.0,
     _save_for_backward: bool = False, _save_parents: bool = True,
     return_trace: bool = False, _force_generic: bool = False, _q_offset: Optional[int] = None, _layers=None,
-    _fused: bool = False, _tiled: bool = False,
+    _fused: bool = False, _tiled: bool = False, _no_pipeline: bool = False,
 ):
     """htree forward.  q [B,T,H,K], k [B,T,H_kv,K], v [B,T,H_kv,V] -> out [B,T,H,V] in q's dtype.
 
@@ -316,7 +340,7 @@ def htree_forward(
         layers_kr = _layers[2] if len(_layers) > 2 else None
         layers_vb = _layers[3] if len(_layers) > 3 else None
         if layers_kr is not None and layers_vb is None:
-            layers_vb = block_values(layers_v, compression_rate, max_top_nodes)
+            layers_vb = block_values(layers_v, compression_rate, max_top_nodes, layers_kr)
     else:
         layers_k, layers_v, layers_kr, layers_vb = build_tree(k, v, compression_rate, max_top_nodes, rope_base)
     if layers_vb is None:
@@ -342,6 +366,8 @@ def htree_forward(
     flags = _lib.FWD_GENERIC if (_force_generic or return_trace) else (_lib.FWD_FUSED if _fused else 0)
     if _tiled:
         flags |= _lib.FWD_TILED
+    if _no_pipeline:
+        flags |= _lib.FWD_NO_PIPELINE
     flags |= _parents_flag(parents)
     half_tables = rope_cache_half(K, cos_cache.shape[0], rope_base, scale, dev) if layers_kr is not None else None
     _run_forward(shape, q, layers_k, layers_v, cos_cache, sin_cache, scale, out, gmax, gsum, parents, trace, flags,
@@ -373,7 +399,7 @@ def htree_forward(
 
 
 def recompute_parents(q, layers_k, layers_v, cos_cache, sin_cache, compression_rate, top_k_per_layer,
-                      max_top_nodes, scale, layers_k_rot=None, _force_generic=False) -> Dict[int, torch.Tensor]:
+                      max_top_nodes, scale, layers_k_rot=None, _force_generic=False, layers_v_blk=None) -> Dict[int, torch.Tensor]:
     """Selection-only replay of the forward (the reference's _recompute_parents, src/backward.py:881-934)."""
     B, T, H, K = q.shape
     H_kv, V = layers_k[0].shape[2], layers_v[0].shape[-1]
@@ -384,7 +410,7 @@ def recompute_parents(q, layers_k, layers_v, cos_cache, sin_cache, compression_r
                for _ in range(L)]
     _run_forward(shape, q.contiguous(), layers_k, layers_v, cos_cache, sin_cache, scale, None, None, None, parents,
                  None, _lib.FWD_SELECT_ONLY | (_lib.FWD_GENERIC if _force_generic else 0) | _parents_flag(parents),
-                 layers_k_rot)
+                 layers_k_rot, None, layers_v_blk)
     return {l: parents[l] for l in range(L)}
 
 
@@ -423,7 +449,7 @@ def htree_backward(dO: torch.Tensor, q: torch.Tensor, output: torch.Tensor, bwd_
     parents = bwd_ctx.get("per_layer_parents")
     if parents is None:
         parents = recompute_parents(q, layers_k, layers_v, cos_cache, sin_cache, CR, TK, MTN, scale,
-                                    bwd_ctx.get("layers_k_rot"))
+                                    bwd_ctx.get("layers_k_rot"), layers_v_blk=bwd_ctx.get("layers_v_blk"))
     flags = 0
     if _window is None:
         shape = _lib.HtreeShape(B, T, H, H_kv, K, V, int(CR), int(TK), int(MTN), _DTYPES[q.dtype])

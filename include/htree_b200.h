@@ -22,7 +22,7 @@
 extern "C" {
 #endif
 
-#define HTREE_B200_VERSION 2
+#define HTREE_B200_VERSION 3
 #define HTREE_MAX_LEVELS 12
 
 /* storage types */
@@ -53,6 +53,8 @@ extern "C" {
                                     int32 (-1 = none): half the saved-selection memory.  Needs every pooled level to have at
                                     most 65535 nodes (else HTREE_E_UNSUPPORTED).  The reference keeps int32
                                     (src/parallel.py:1044; docs/backward_derivation.md:355-372 names the cost). */
+#define HTREE_FWD_NO_PIPELINE 128u /* tensor-core forward: gather operands into registers instead of streaming the blocked
+                                    keys / values through shared memory (the kernels used where no blocked keys are given) */
 #define HTREE_FWD_FUSED 4u       /* tensor-core forward: keep selection and accumulation in ONE kernel even when parent
                                     buffers are provided (default then: a selection kernel followed by an accumulation kernel) */
 
@@ -123,6 +125,10 @@ int htree_b200_level_sizes(int32_t T, int32_t compression_rate, int32_t max_top_
  *                 (rows of 64 columns interleave 8-column pieces of the two halves).  The tensor-core forward reads K' (16-bit storage
  *                 types only; needs cos_cache/sin_cache with at least compression_rate rows, and K % 16 == 0).
  *                 Pass NULL for fp32 or when only the generic kernels are wanted.
+ *   layers_k_blk  NULL, or (bf16/fp16, K = 128, compression_rate 16 only; needs layers_k_rot) L pointers to buffers of
+ *                 B * ceil(N_l / 16) * H_kv * 16 * K halves (32-byte aligned) that receive K' grouped by parent in the order
+ *                 in which the pipelined tensor-core forward consumes it: with them that forward streams whole parent blocks
+ *                 into shared memory with asynchronous bulk copies instead of gathering rows into registers.
  *   layers_v_blk  NULL, or L pointers to buffers of B * ceil(N_l / compression_rate) * H_kv * compression_rate * V
  *                 elements of `dtype` (level 0 included; 32-byte aligned) that receive the values of every level grouped by
  *                 parent: the compression_rate children of one parent and KV head form one block whose element order is
@@ -130,8 +136,8 @@ int htree_b200_level_sizes(int32_t T, int32_t compression_rate, int32_t max_top_
  *                 past the end of a level are zero.  The tensor-core forward accumulates from these blocks instead of
  *                 gathering value rows.  16-bit storage types, V in {64,128}, compression_rate 8 or 16 only. */
 int htree_b200_build_tree(const HtreeShape* shape, void* const* layers_k, void* const* layers_v,
-                          void* const* layers_k_rot, void* const* layers_v_blk, const float* cos_cache,
-                          const float* sin_cache, void* stream);
+                          void* const* layers_k_rot, void* const* layers_k_blk, void* const* layers_v_blk,
+                          const float* cos_cache, const float* sin_cache, void* stream);
 
 /* K' levels alone, from tree levels that already exist (e.g. levels assembled by an all-gather in sequence-sharded
  * runs): layers_k_rot[l][node] = R(node % compression_rate) layers_k[l][node] for every level.  16-bit storage types
@@ -139,15 +145,18 @@ int htree_b200_build_tree(const HtreeShape* shape, void* const* layers_k, void* 
 int htree_b200_rotate_keys(const HtreeShape* shape, void* const* layers_k, void* const* layers_k_rot,
                            const float* cos_cache, const float* sin_cache, void* stream);
 
-/* The blocked values alone (layers_v_blk of htree_b200_build_tree), from tree levels that already exist.  No counterpart
- * in the reference. */
+/* The blocked values / blocked keys alone (layers_v_blk, layers_k_blk of htree_b200_build_tree), from tree levels and K' levels
+ * that already exist.  No counterpart in the reference. */
 int htree_b200_block_values(const HtreeShape* shape, void* const* layers_v, void* const* layers_v_blk, void* stream);
+int htree_b200_block_keys(const HtreeShape* shape, void* const* layers_k_rot, void* const* layers_k_blk, void* stream);
 
 /* Fused forward over all levels: replaces the per-level launches of htree_select_accumulate_gqa_kernel,
  * htree_bottom_accumulate_gqa_kernel, htree_merge_to_global_kernel and htree_final_normalize_kernel together with
  * the host-side state and virtual-parent initialisation (src/parallel.py:995-1134), and — with
  * HTREE_FWD_SELECT_ONLY — htree_recompute_selection_kernel / _recompute_parents (src/parallel.py:1167-1399,
  * src/backward.py:881-934).
+ *   layers_k_blk  NULL or the blocked keys of htree_b200_build_tree: selects the pipelined variant of the tensor-core kernels
+ *                 (status bit 16 reports a bulk copy that did not complete within the kernels' bounded waits)
  *   layers_k_rot, layers_v_blk  NULL or the K' levels and blocked values written by htree_b200_build_tree; when present
  *                 (and the shape qualifies: bf16/fp16, K == V in {64,128}, H/H_kv <= 16, compression_rate 16 or 8, and q,
  *                 every level of layers_k_rot / layers_v_blk and the tables 32-byte aligned; the backward also wants
@@ -164,7 +173,8 @@ int htree_b200_block_values(const HtreeShape* shape, void* const* layers_v, void
  *   status   NULL or one int32 on the device, OR-ed with a non-zero code if a kernel met an out-of-range node index
  */
 int htree_b200_forward(const HtreeShape* shape, const void* q, void* const* layers_k, void* const* layers_v,
-                       void* const* layers_k_rot, void* const* layers_v_blk, const float* cos_cache, const float* sin_cache, const void* cos_half,
+                       void* const* layers_k_rot, void* const* layers_k_blk, void* const* layers_v_blk, const float* cos_cache,
+                       const float* sin_cache, const void* cos_half,
                        const void* sin_half, int32_t n_pos, float scale, void* out,
                        float* gmax, float* gsum, int32_t* const* parents, const HtreeTrace* trace, int32_t* status,
                        uint32_t flags, void* stream);

@@ -25,7 +25,7 @@ def test_library_exports_every_declared_symbol():
     lib = _lib.lib()
     for name in declared_symbols():
         assert hasattr(lib, name), name
-    assert lib.htree_b200_version() == 2      # HTREE_B200_VERSION of the header
+    assert lib.htree_b200_version() == 3      # HTREE_B200_VERSION of the header
 
 
 def test_level_sizes_follow_the_reference_loop():
@@ -49,7 +49,7 @@ def _shape(**kw):
 def _fwd(shape, q=16, lk=None, n_pos=2048):
     lib = _lib.lib()
     dummy = (ctypes.c_void_p * 12)(*[ctypes.c_void_p(4096)] * 12)
-    return lib.htree_b200_forward(ctypes.byref(shape), q, lk if lk is not None else dummy, dummy, None, None, 4096, 4096, None, None, n_pos,
+    return lib.htree_b200_forward(ctypes.byref(shape), q, lk if lk is not None else dummy, dummy, None, None, None, 4096, 4096, None, None, n_pos,
                                   0.25, 4096, 4096, 4096, None, None, None, 0, None)
 
 

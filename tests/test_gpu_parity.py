@@ -665,3 +665,30 @@ def test_typed_gradients_equal_the_cast_of_the_fp32_ones(dtype, B, T, H, Hkv, D,
             ops.htree_backward(dO.float(), q, out, ctx)
         else:
             raise ValueError
+
+
+@pytest.mark.parametrize("name", ["bf16_D128_G16_T6000_tk64", "bf16_D128_G8_T3000"])
+def test_pipelined_forward_equals_the_register_gather_forward(name):
+    """128-wide heads with 16 children per parent run the pipelined kernels (operand blocks streamed into shared memory by
+    asynchronous bulk copies); with HTREE_FWD_NO_PIPELINE the same kernels gather the rows into registers.  Same operands,
+    same instruction order: identical bits, selections included; also for a query window and the selection-only replay."""
+    ops = _ops()
+    c = MMA_CASES.get(name) or dict(B=2, T=3000, H=16, H_kv=2, K=128, V=128, CR=16, TK=32, MTN=64, dtype="bfloat16", seed=95)
+    q, k, v, _ = (x.to(DEV) for x in parity.case_inputs(c))
+    a, ctx_a = ops.htree_forward(q, k, v, c["CR"], c["MTN"], c["TK"], _save_for_backward=True)
+    b, ctx_b = ops.htree_forward(q, k, v, c["CR"], c["MTN"], c["TK"], _save_for_backward=True, _no_pipeline=True)
+    torch.cuda.synchronize(); ops.check_status()
+    assert ctx_a["layers_v_blk"].keys is not None
+    assert torch.equal(a, b)
+    assert torch.equal(ctx_a["global_max"], ctx_b["global_max"]) and torch.equal(ctx_a["global_sum"], ctx_b["global_sum"])
+    for l in range(ctx_a["num_layers"]):
+        assert torch.equal(ctx_a["per_layer_parents"][l], ctx_b["per_layer_parents"][l])
+    t0, t1 = c["T"] // 3, c["T"] - 5
+    layers = (ctx_a["layers_k"], ctx_a["layers_v"], ctx_a["layers_k_rot"], ctx_a["layers_v_blk"])
+    w = ops.htree_forward(q[:, t0:t1].contiguous(), k, v, c["CR"], c["MTN"], c["TK"], _q_offset=t0, _layers=layers)
+    assert torch.equal(w, a[:, t0:t1])
+    from htree_b200 import ops as hops
+    again = hops.recompute_parents(q, ctx_a["layers_k"], ctx_a["layers_v"], ctx_a["cos_cache"], ctx_a["sin_cache"], c["CR"], c["TK"],
+                                   c["MTN"], ctx_a["scale"], ctx_a["layers_k_rot"], layers_v_blk=ctx_a["layers_v_blk"])
+    for l in range(ctx_a["num_layers"]):
+        assert torch.equal(again[l], ctx_a["per_layer_parents"][l])
