@@ -552,6 +552,7 @@ def main():
 
         e2e_step()
         barrier()
+        ht.check_status(dev)
         n_e2e = max(1, min(args.steps, 3))
         a = torch.cuda.Event(enable_timing=True); b_ = torch.cuda.Event(enable_timing=True)
         a.record()
@@ -579,7 +580,10 @@ def main():
     if world > 1 and not args.no_workloads and not seq_mode and args.t_scale == 1:
         del q, k, v, dO
         torch.cuda.empty_cache()
-        mode_b = measure_mode_b(dev, world, rank, max_over_ranks, barrier)
+        try:
+            mode_b = measure_mode_b(dev, world, rank, max_over_ranks, barrier)
+        except Exception as e:     # every rank raises or none does (same code, same shapes): the headline survives
+            mode_b = {"error": f"{type(e).__name__}: {e}"[:400]}
 
     if rank != 0:
         if world > 1:

@@ -86,7 +86,10 @@ __host__ __device__ inline size_t mma_smem_per_warp(int TK, int CR, bool selecti
 #define HTREE_PIPE_SEL_BLOCKS 3
 #endif
 #ifndef HTREE_PIPE_ACC_WARPS
-#define HTREE_PIPE_ACC_WARPS 3      // accumulation kernel: 3 blocks of 3 warps per SM (227 registers each)
+#define HTREE_PIPE_ACC_WARPS 3      // accumulation kernel, groups of at most 8 heads: 3 blocks of 3 warps per SM (227 registers)
+#endif
+#ifndef HTREE_PIPE_ACC_WARPS_G16
+#define HTREE_PIPE_ACC_WARPS_G16 4  // groups of 9..16 heads: 3 blocks of 4 warps (168 registers, 12 bytes of spills)
 #endif
 #ifndef HTREE_PIPE_ACC_BLOCKS
 #define HTREE_PIPE_ACC_BLOCKS 3
@@ -107,15 +110,18 @@ __host__ __device__ constexpr size_t pipe_bytes_per_warp(int mode, bool rot16) {
 // registers (4 blocks x 4 warps) vs 56.27 pipelined (3 x 5 warps) vs 59.2 (2 x 7); accumulation kernel 107.2 gathering
 // (2 x 4 warps) / 104.2 (3 x 3) vs pipelined 117.7 (2 x 4, 3 stages) / 102.8 (3 x 3, 2 stages) / 117.7 (4 x 2).  Neither
 // kernel is bound by the latency of its gathers: the selection kernel keeps its register path (more resident warps, no
-// ring), the accumulation kernel takes the pipelined one.
+// ring), the accumulation kernel takes the pipelined one, whose short-lived operand registers also make 12 warps per SM
+// possible (the register path spilled there): whole forward, pipelined accumulation at 3 x 3 / 3 x 4 / 2 x 6 / 4 x 3 warps:
+// cfg3 (groups of 16 heads) 158.8 / 154.5 / 155.6 / 155.5 ms, cfg4 (groups of 8) 399.8 / 403.0 / 403.7 / 404.4 ms.
 #ifndef HTREE_PIPE_SEL
 #define HTREE_PIPE_SEL 0     // 1: the selection kernel streams its operands too
 #endif
 #ifndef HTREE_PIPE_ACC
 #define HTREE_PIPE_ACC 1     // 0: the accumulation kernel always gathers into registers
 #endif
-__host__ __device__ constexpr int fwd_warps_per_block(int mode, bool pipe) {
-    return pipe ? (mode == 1 ? HTREE_PIPE_SEL_WARPS : HTREE_PIPE_ACC_WARPS) : (mode == 1 ? HTREE_SEL_WARPS : HTREE_FWD_WARPS);
+__host__ __device__ constexpr int fwd_warps_per_block(int mode, bool pipe, int nr = 1) {
+    return pipe ? (mode == 1 ? HTREE_PIPE_SEL_WARPS : (nr == 2 ? HTREE_PIPE_ACC_WARPS_G16 : HTREE_PIPE_ACC_WARPS))
+                : (mode == 1 ? HTREE_SEL_WARPS : HTREE_FWD_WARPS);
 }
 __host__ __device__ constexpr int fwd_blocks_per_sm(int mode, bool pipe, bool x3) {
     return pipe ? (mode == 1 ? HTREE_PIPE_SEL_BLOCKS : HTREE_PIPE_ACC_BLOCKS) : (mode == 1 ? (x3 ? 3 : HTREE_SEL_MIN_BLOCKS) : HTREE_FWD_MIN_BLOCKS);
@@ -127,10 +133,10 @@ __host__ __device__ constexpr int fwd_blocks_per_sm(int mode, bool pipe, bool x3
 // NR = 1: groups of at most 8 heads (rows g+8 of every fragment are padding and their ALU work is skipped).
 // T = float: split-half products (mma_common.cuh), 64-wide heads; K' and the blocked values then hold a hi and a lo plane.
 template <typename T, int D, bool ROT16, int MODE, int NR, int CR, bool PIPE = false>
-__global__ void __launch_bounds__(fwd_warps_per_block(MODE, PIPE) * 32, fwd_blocks_per_sm(MODE, PIPE, std::is_same<T, float>::value))
+__global__ void __launch_bounds__(fwd_warps_per_block(MODE, PIPE, NR) * 32, fwd_blocks_per_sm(MODE, PIPE, std::is_same<T, float>::value))
 fwd_mma_kernel(const __grid_constant__ AttnParams p) {
     constexpr bool X3 = std::is_same<T, float>::value;
-    constexpr int MWK = fwd_warps_per_block(MODE, PIPE);   // warps (= queries) per block
+    constexpr int MWK = fwd_warps_per_block(MODE, PIPE, NR);   // warps (= queries) per block
     static_assert(!PIPE || (D == 128 && CR == 16 && !X3 && (MODE == 1 || MODE == 2)), "pipelined kernels: 128-wide heads, 16 children, 16-bit types");
     constexpr bool FRAGV = kFragmentMajor<D, CR, X3>;   // element order of the blocked values
     constexpr uint32_t kAllChildren = (1u << CR) - 1u;   // CR = children per parent: 16, or 8 (then tile 1 stays empty)
@@ -619,7 +625,7 @@ static int launch_mma_mode_cr(const AttnParams& p, cudaStream_t st) {
     if constexpr (kHasPipe) {
         bool pipe = !(p.flags & HTREE_FWD_NO_PIPELINE);
         for (int l = 0; l < p.L; ++l) pipe = pipe && p.lkb[l] != nullptr && (MODE == 1 || p.lvb[l] != nullptr);
-        constexpr int W = fwd_warps_per_block(MODE, true);
+        constexpr int W = fwd_warps_per_block(MODE, true, NR);
         const size_t psmem = mma_smem_per_warp(p.TK, CR, MODE != 2, pipe_bytes_per_warp(MODE, ROT16)) * W;
         // the ring must leave room for the intended number of resident blocks (1 KB per block is reserved by the system)
         if (pipe && (psmem + 1024) * fwd_blocks_per_sm(MODE, true, false) <= 227 * 1024) {

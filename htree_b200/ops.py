@@ -39,6 +39,10 @@ SAVE_SELECTIONS_FOR_BACKWARD = True
 # pattern, 0xFFFF = none; decode_parents() converts) and needs every pooled level to have at most 65535 nodes.
 SELECTION_STORAGE = "int32"
 
+# Largest temporary the forward may allocate for handing selections from its selection kernel to its accumulation
+# kernel when the caller does not keep them (see htree_forward); above it the fused single-kernel forward runs.
+SPLIT_FORWARD_MAX_BYTES = 4 << 30
+
 
 def _parents_dtype(layers_k, top_k: int):
     if SELECTION_STORAGE == "int32":
@@ -351,10 +355,18 @@ def htree_forward(
     gmax = torch.empty(B, T, H, dtype=torch.float32, device=dev)
     gsum = torch.empty(B, T, H, dtype=torch.float32, device=dev)
     want_parents = (_save_for_backward and _save_parents) or return_trace
-    # the tensor-core forward is faster as selection kernel + accumulation kernel, which hand the selections over in
-    # these buffers; so they are allocated there even when the caller does not keep them
+    # The tensor-core forward is faster as selection kernel + accumulation kernel, which hand the selections over in
+    # buffers of L * B * T * H_kv * top_k ids (cfg3: 805 MB as int32; 2.1 GB per level at the reference's default top_k of
+    # 512 with the same shape).  A caller who does not keep the selections gets them only as temporaries, in int32
+    # whatever SELECTION_STORAGE says, and only up to SPLIT_FORWARD_MAX_BYTES: beyond it the single fused kernel runs,
+    # which needs no buffers and gives identical results.
     split_forward = layers_kr is not None and not (_force_generic or return_trace or _fused)
-    pdt = _parents_dtype(layers_k, top_k_per_layer)
+    if want_parents:
+        pdt = _parents_dtype(layers_k, top_k_per_layer)
+    else:
+        pdt = torch.int32
+        if split_forward and L * B * q.shape[1] * H_kv * top_k_per_layer * 4 > SPLIT_FORWARD_MAX_BYTES:
+            split_forward = False
     parents = [torch.empty(B, q.shape[1], H_kv, top_k_per_layer, dtype=pdt, device=dev) for _ in range(L)] \
         if (want_parents or split_forward) else None
     trace = tr = None

@@ -692,3 +692,20 @@ def test_pipelined_forward_equals_the_register_gather_forward(name):
                                    c["MTN"], ctx_a["scale"], ctx_a["layers_k_rot"], layers_v_blk=ctx_a["layers_v_blk"])
     for l in range(ctx_a["num_layers"]):
         assert torch.equal(again[l], ctx_a["per_layer_parents"][l])
+
+
+def test_inference_forward_falls_back_to_the_fused_kernel_above_its_byte_budget(monkeypatch):
+    """A plain forward (selections not kept) hands them from the selection kernel to the accumulation kernel through
+    temporaries; above ops.SPLIT_FORWARD_MAX_BYTES it runs the fused kernel instead, with identical results, and it never
+    trips over SELECTION_STORAGE settings that only matter for kept selections."""
+    ops = _ops()
+    from htree_b200 import ops as hops
+    c = MMA_CASES["bf16_D128_G16_T2048"]
+    q, k, v, _ = (x.to(DEV) for x in parity.case_inputs(c))
+    a = ops.htree_forward(q, k, v, c["CR"], c["MTN"], c["TK"])
+    monkeypatch.setattr(hops, "SPLIT_FORWARD_MAX_BYTES", 1024)
+    monkeypatch.setattr(hops, "SELECTION_STORAGE", "no-such-format")
+    b = ops.htree_forward(q, k, v, c["CR"], c["MTN"], c["TK"])
+    assert torch.equal(a, b)
+    with pytest.raises(ValueError):
+        ops.htree_forward(q, k, v, c["CR"], c["MTN"], c["TK"], _save_for_backward=True)
