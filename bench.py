@@ -625,8 +625,9 @@ def main():
     n_rows = B * Hkv if (seq_mode or world == 1) else len(units)
     tree_bytes = es * n_rows * 2 * D * sum(lv_sizes[i] + lv_sizes[i + 1] for i in range(len(lv_sizes) - 1))     # pool K and V
     if es == 2:
-        tree_bytes += 2 * 2 * n_rows * D * sum(lv_sizes)                                                         # K -> K'
-    streaming = {"kernels": "tree_build_kernel + rotate_keys_kernel (all levels, rank 0)", "ms": tree_ms,
+        copies = 1 + (1 if D in (64, 128) and CR in (8, 16) else 0) + (1 if D == 128 and CR == 16 else 0)     # K -> K', V -> V^, K' -> K'^
+        tree_bytes += copies * 2 * 2 * n_rows * D * sum(lv_sizes)                                                # each: read + write of every level
+    streaming = {"kernels": "tree_build_kernel + rotate_keys / block_values / block_keys kernels (all levels, rank 0)", "ms": tree_ms,
                  "algorithmic_bytes": tree_bytes, "achieved": tree_bytes / (tree_ms * 1e-3) / 1e9, "unit": "GB/s",
                  "peak": pk["hbm_gbs"], "frac": tree_bytes / (tree_ms * 1e-3) / 1e9 / pk["hbm_gbs"],
                  "note": "CUDA events around 10 back-to-back builds, includes launch gaps between the per-level kernels"}
