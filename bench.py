@@ -361,7 +361,8 @@ def side_workload(name: str, dev, pk: dict, steps: int = 3, warmup: int = 3) -> 
     peak = pk.get("bf16_tflops_sustained", FALLBACK_PEAKS["bf16_tflops_sustained"])
     res.update(ms=ms, tokens_per_s=c["B"] * c["T"] / (ms * 1e-3), tflops=flops / (ms * 1e-3) / 1e12,
                roofline_frac=flops / (ms * 1e-3) / 1e12 / peak,
-               arithmetic="fp32 inputs: see DESIGN" if c["dtype"] == "float32" else "bf16/half tensor cores")
+               arithmetic=("fp32 storage: split-half tensor-core kernels (64-wide heads; hi + lo half pairs, three MMAs per product)"
+                           if c["dtype"] == "float32" else "bf16/half tensor cores"))
     del q, k, v, dO
     torch.cuda.empty_cache()
     return res
@@ -567,7 +568,34 @@ def main():
             tt = torch.tensor([h2d, d2h], device=dev, dtype=torch.float64)
             tdist.all_reduce(tt)
             h2d, d2h = int(tt[0].item()), int(tt[1].item())
-        e2e = {"value": B * T / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
+        # the copy ceilings of this run: every rank moves its own inputs up and its own results down, all ranks at once,
+        # nothing else running; e2e cannot be faster than the slower direction (or than the kernels)
+        link = None
+        try:
+            dev_in = [torch.empty(h.shape, dtype=h.dtype, device=dev) for h in host_in]
+            dev_out = [torch.empty(h.shape, dtype=h.dtype, device=dev) for h in host_out]
+            for d_, h_ in zip(dev_in, host_in):
+                d_.copy_(h_, non_blocking=True)
+            barrier()
+            ev_l = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+            ev_l[0].record()
+            for d_, h_ in zip(dev_in, host_in):
+                d_.copy_(h_, non_blocking=True)
+            ev_l[1].record()
+            for d_, h_ in zip(dev_out, host_out):
+                h_.copy_(d_, non_blocking=True)
+            ev_l[2].record()
+            barrier()
+            up_ms = max_over_ranks(ev_l[0].elapsed_time(ev_l[1])); down_ms = max_over_ranks(ev_l[1].elapsed_time(ev_l[2]))
+            bytes_in = sum(h.numel() * h.element_size() for h in host_in)
+            bytes_out = sum(h.numel() * h.element_size() for h in host_out)
+            link = {"h2d_ms_all_ranks_at_once": up_ms, "d2h_ms_all_ranks_at_once": down_ms,
+                    "h2d_gbs_per_rank": bytes_in / (up_ms * 1e-3) / 1e9, "d2h_gbs_per_rank": bytes_out / (down_ms * 1e-3) / 1e9,
+                    "note": "contiguous copies of this rank's pinned tensors, one direction at a time; max over ranks"}
+            del dev_in, dev_out
+        except Exception as e:
+            link = {"error": f"{type(e).__name__}: {e}"[:200]}
+        e2e = {"value": B * T / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms, "copy_ceiling": link,
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": n_e2e,
                "host_tensors": cfg_desc.get("tensors"),
                "api": ("htree_forward_sequence_parallel with pinned host tensors copied in and out around the call" if seq_mode

@@ -121,7 +121,8 @@ def _status(device) -> torch.Tensor:
 
 
 def check_status(device=None) -> None:
-    """Synchronise and raise if a kernel flagged an out-of-range node index since the last check."""
+    """Synchronise and raise if a kernel flagged a problem since the last check: an out-of-range node index (bits 0-3), or a
+    bounded wait of the pipelined forward that ran out (bit 4)."""
     device = torch.device(device if device is not None else torch.cuda.current_device())
     if device.type == "cuda" and device.index is None:
         device = torch.device("cuda", torch.cuda.current_device())
@@ -130,7 +131,13 @@ def check_status(device=None) -> None:
         v = int(w.item())
         if v:
             w.zero_()
-            raise RuntimeError(f"htree_b200 kernels reported device-side status 0x{v:x} (node index out of range)")
+            what = []
+            if v & 0xF:
+                what.append("a node index outside its tree level (clamped)")
+            if v & 16:
+                what.append("an asynchronous operand copy of the pipelined forward did not complete within its bounded wait "
+                            "(the affected outputs were not written)")
+            raise RuntimeError(f"htree_b200 kernels reported device-side status 0x{v:x}: " + "; ".join(what or ["unknown bits"]))
 
 
 def _stream() -> int:

@@ -19,7 +19,8 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 DEST = os.path.join(HERE, "_ref")
-DEFAULT_SOURCE = os.environ.get("HTREE_REFERENCE", "/root/reference")
+# the checkout: $HTREE_REFERENCE, else a directory named "reference" beside this repository
+DEFAULT_SOURCE = os.environ.get("HTREE_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
 FILES = ["src/parallel.py", "src/backward.py", "src/naive.py",
          "ref_nsa/__init__.py", "ref_nsa/nsa_parallel.py", "ref_nsa/nsa_compression.py", "ref_nsa/nsa_utils.py"]
 
