@@ -40,6 +40,30 @@ template <> struct Frag<__half> {
     }
 };
 
+// Packed fp32 arithmetic of sm_100 (two IEEE round-to-nearest operations per instruction): the fp32 query rotation of the
+// pass that decides the Top-K is the largest block of scalar work in the selection kernel.
+__device__ __forceinline__ float2 fmul2(float2 a, float2 b) {
+    float2 d;
+    asm("{\n.reg .b64 ra, rb, rd;\nmov.b64 ra, {%2, %3};\nmov.b64 rb, {%4, %5};\nmul.rn.f32x2 rd, ra, rb;\nmov.b64 {%0, %1}, rd;\n}\n"
+        : "=f"(d.x), "=f"(d.y)
+        : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+    return d;
+}
+__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
+    float2 d;
+    asm("{\n.reg .b64 ra, rb, rc, rd;\nmov.b64 ra, {%2, %3};\nmov.b64 rb, {%4, %5};\nmov.b64 rc, {%6, %7};\nfma.rn.f32x2 rd, ra, rb, rc;\nmov.b64 {%0, %1}, rd;\n}\n"
+        : "=f"(d.x), "=f"(d.y)
+        : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+    return d;
+}
+// Half-split rotation of the pair-of-pairs (lo, hi) by (cos, sin): x = lo*cos - hi*sin, y = lo*sin + hi*cos, each as one
+// product and one fused multiply-add (nsn = -sin).  One definition for every kernel that rotates in fp32, so that they
+// all round alike.
+__device__ __forceinline__ void rotate_pairs_f32(float2 lo, float2 hi, float2 cs, float2 sn, float2 nsn, float2& x, float2& y) {
+    x = ffma2(hi, nsn, fmul2(lo, cs));
+    y = ffma2(hi, cs, fmul2(lo, sn));
+}
+
 __device__ __forceinline__ uint4 ldg16(const void* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
 // 32 bytes with one 256-bit load (sm_100a); address must be 32-byte aligned.
 __device__ __forceinline__ void ldg32(const void* p, uint32_t (&o)[8]) {
@@ -208,11 +232,14 @@ __device__ __forceinline__ void score_chunk(const AttnParams& p, const __half* k
             uint32_t a[4];
             a[1] = 0u; a[3] = 0u;
 #pragma unroll
+            const float2 c2 = make_float2(cs[2 * u], cs[2 * u + 1]), s2 = make_float2(sn[2 * u], sn[2 * u + 1]);
+            const float2 ns2 = make_float2(-s2.x, -s2.y);
+#pragma unroll
             for (int rr = 0; rr < NR; ++rr) {
-                const float2 lo = FS::unpack(qraw[rr][0][ks]), hi = FS::unpack(qraw[rr][1][ks]);
-                const float c0 = cs[2 * u], c1 = cs[2 * u + 1], s0 = sn[2 * u], s1 = sn[2 * u + 1];
-                a[rr] = FS::pack(lo.x * c0 - hi.x * s0, lo.y * c1 - hi.y * s1);         // rotated low half
-                a[2 + rr] = FS::pack(lo.x * s0 + hi.x * c0, lo.y * s1 + hi.y * c1);     // rotated high half
+                float2 x, y;
+                rotate_pairs_f32(FS::unpack(qraw[rr][0][ks]), FS::unpack(qraw[rr][1][ks]), c2, s2, ns2, x, y);
+                a[rr] = FS::pack(x.x, x.y);         // rotated low half
+                a[2 + rr] = FS::pack(y.x, y.y);     // rotated high half
             }
             if (KEEP_A) { qa[KEEP_A ? ks : 0][0] = a[0]; qa[KEEP_A ? ks : 0][1] = a[1]; qa[KEEP_A ? ks : 0][2] = a[2]; qa[KEEP_A ? ks : 0][3] = a[3]; }
             if (KEEP_K) {
@@ -306,11 +333,14 @@ __device__ __forceinline__ void score_chunk_sm(const AttnParams& p, const uint4*
             uint32_t a[4];
             a[1] = 0u; a[3] = 0u;
 #pragma unroll
+            const float2 c2 = make_float2(cs[2 * u], cs[2 * u + 1]), s2 = make_float2(sn[2 * u], sn[2 * u + 1]);
+            const float2 ns2 = make_float2(-s2.x, -s2.y);
+#pragma unroll
             for (int rr = 0; rr < NR; ++rr) {
-                const float2 lo = FS::unpack(qraw[rr][0][ks]), hi = FS::unpack(qraw[rr][1][ks]);
-                const float c0 = cs[2 * u], c1 = cs[2 * u + 1], s0 = sn[2 * u], s1 = sn[2 * u + 1];
-                a[rr] = FS::pack(lo.x * c0 - hi.x * s0, lo.y * c1 - hi.y * s1);
-                a[2 + rr] = FS::pack(lo.x * s0 + hi.x * c0, lo.y * s1 + hi.y * c1);
+                float2 x, y;
+                rotate_pairs_f32(FS::unpack(qraw[rr][0][ks]), FS::unpack(qraw[rr][1][ks]), c2, s2, ns2, x, y);
+                a[rr] = FS::pack(x.x, x.y);
+                a[2 + rr] = FS::pack(y.x, y.y);
             }
             if (u) {
                 FS::mma(T0, a[0], a[1], a[2], a[3], kb.x, kb.y);
@@ -425,12 +455,15 @@ __device__ __forceinline__ void score_chunk_x3(const AttnParams& p, const __half
     for (int ks = 0; ks < KS; ++ks) {
         uint32_t ah[4] = {0u, 0u, 0u, 0u}, al[4] = {0u, 0u, 0u, 0u};
         const float c0 = cs[2 * ks], c1 = cs[2 * ks + 1], s0 = sn[2 * ks], s1 = sn[2 * ks + 1];
+        const float2 c2 = make_float2(c0, c1), s2 = make_float2(s0, s1), ns2 = make_float2(-s0, -s1);
 #pragma unroll
         for (int rr = 0; rr < NR; ++rr) {
-            const float lx = __uint_as_float(qf[rr][0][2 * ks]), ly = __uint_as_float(qf[rr][0][2 * ks + 1]);
-            const float hx = __uint_as_float(qf[rr][1][2 * ks]), hy = __uint_as_float(qf[rr][1][2 * ks + 1]);
-            split_half2(lx * c0 - hx * s0, ly * c1 - hy * s1, ah[rr], al[rr]);              // rotated low half
-            split_half2(lx * s0 + hx * c0, ly * s1 + hy * c1, ah[2 + rr], al[2 + rr]);      // rotated high half
+            const float2 lo = make_float2(__uint_as_float(qf[rr][0][2 * ks]), __uint_as_float(qf[rr][0][2 * ks + 1]));
+            const float2 hi = make_float2(__uint_as_float(qf[rr][1][2 * ks]), __uint_as_float(qf[rr][1][2 * ks + 1]));
+            float2 x, y;
+            rotate_pairs_f32(lo, hi, c2, s2, ns2, x, y);
+            split_half2(x.x, x.y, ah[rr], al[rr]);              // rotated low half
+            split_half2(y.x, y.y, ah[2 + rr], al[2 + rr]);      // rotated high half
         }
         if (KEEP) {
 #pragma unroll
