@@ -177,6 +177,7 @@ fwd_mma_kernel(const __grid_constant__ AttnParams p) {
     const unsigned char* kblk = nullptr;    // this level's blocked keys / values of (b, hk); parents are blk_stride bytes apart
     const unsigned char* vblk = nullptr;
     int64_t blk_stride = 0;
+    [[maybe_unused]] int pipe_level = 0;
     int blk_count = 0, pipe_rp = 0;         // pipe_rp: rotation position of the level (the chunk at slot a rotates by rp - CR*a)
     if constexpr (PIPE) {
         if (lane == 0) {
@@ -190,6 +191,13 @@ fwd_mma_kernel(const __grid_constant__ AttnParams p) {
         if (pb < 0 || pb >= blk_count) pb = 0;       // flagged where the chunk is consumed
         const int sl = (int)(n % NSTG);
         unsigned char* dst = ring + (size_t)sl * SLOT;
+#ifdef HTREE_FWD_KNOCK_KCOPY   // timing experiments only: upper-level chunks of the accumulation kernel bring their values alone
+        if (MODE == 2 && pipe_level > 0) {
+            mbar_arrive_expect_tx(&bars[sl], 4096u);
+            bulk_copy_g2s(dst + 4096, vblk + (int64_t)pb * blk_stride, 4096u, &bars[sl]);
+            return;
+        }
+#endif
         mbar_arrive_expect_tx(&bars[sl], SLOT);
         bulk_copy_g2s(dst, kblk + (int64_t)pb * blk_stride, 4096u, &bars[sl]);
         if (MODE == 2) bulk_copy_g2s(dst + 4096, vblk + (int64_t)pb * blk_stride, 4096u, &bars[sl]);
@@ -254,6 +262,7 @@ fwd_mma_kernel(const __grid_constant__ AttnParams p) {
     // an exact running maximum would move in most chunks and cost 64 multiplies each time.
     constexpr float kLazyMax = 8.f;
     float m_run[2] = {-1.0e30f, -1.0e30f}, m_true[2] = {-1.0e30f, -1.0e30f}, s_run[2] = {0.f, 0.f};
+    float m_run2[2] = {-1.0e30f * kLog2e, -1.0e30f * kLog2e};      // m_run in units of log 2, the form the exponentials take
 
     {   // virtual parents of the top level (src/parallel.py:1026-1038)
         int np0 = (int)(((int64_t)t / p.lpow[L - 1]) / CR) + 1;
@@ -296,22 +305,26 @@ fwd_mma_kernel(const __grid_constant__ AttnParams p) {
         if constexpr (PIPE) {
             blk_count = (Nl + CR - 1) / CR;
             blk_stride = (int64_t)p.Hkv * (CR * D * 2);
-            pipe_rp = rp;
+            pipe_rp = rp; pipe_level = l;
             kblk = reinterpret_cast<const unsigned char*>(p.lkb[l]) + ((int64_t)b * blk_count * p.Hkv + hk) * (CR * D * 2);
             vblk = reinterpret_cast<const unsigned char*>(p.lvb[l]) + ((int64_t)b * blk_count * p.Hkv + hk) * (CR * D * 2);
         }
         auto score = [&](int a, float (&S0)[4], float (&S1)[4], bool select) {
             int node0 = par[a] * CR;
             if (node0 < 0 || node0 >= Nl) { if (p.status) atomicOr(p.status, 4); node0 = 0; }
+#ifdef HTREE_FWD_KNOCK_SCORE   // timing experiments only: levels in the kernel's bit mask (selection kernel: bits 0-7,
+            // accumulation kernel: bits 8-15) are not scored; results are wrong
+            if (((kAccumulateKernel ? (HTREE_FWD_KNOCK_SCORE) >> 8 : (HTREE_FWD_KNOCK_SCORE)) >> l) & 1) {
+                S0[0] = S0[1] = S0[2] = S0[3] = S1[0] = S1[1] = S1[2] = S1[3] = 0.f;
+                return;
+            }
+#endif
             if constexpr (PIPE) {
                 // the rotation of a chunk is fixed by the kernel: fp32 tables where the Top-K is decided (selection kernel) or
                 // no packed-half tables were given, packed-half tables otherwise; its table rows are in the slot
                 score_chunk_sm<D, !kTabF32, NR>(p, reinterpret_cast<const uint4*>(slot), slot + TAB_OFF, lane, qraw, S0, S1);
                 return;
             }
-#ifdef HTREE_KNOCK_L1ROWS   // timing experiments only: every gather hits the same rows (wrong results, no L2 latency)
-            node0 = 0;
-#endif
             if constexpr (X3) {
                 score_chunk_x3<D, NR, CR>(p, kq, (int64_t)p.B * Nl * rstride, rstride, Nl, node0, rp - CR * a, g, r, qraw, S0, S1, stream_rows);
             } else {
@@ -325,9 +338,6 @@ fwd_mma_kernel(const __grid_constant__ AttnParams p) {
         auto accumulate_chunk = [&](int a, float (&S0)[4], float (&S1)[4], uint32_t mask) {
             int pblk = par[a];
             if (pblk < 0 || (int64_t)pblk * CR >= Nl) pblk = 0;
-#ifdef HTREE_KNOCK_L1ROWS
-            pblk = 0;
-#endif
             const int col[4] = {2 * r, 2 * r + 1, 8 + 2 * r, 9 + 2 * r};
             const bool cv[4] = {(mask >> col[0] & 1) != 0, (mask >> col[1] & 1) != 0, (mask >> col[2] & 1) != 0, (mask >> col[3] & 1) != 0};
             // value fragments first (longest latency): this lane's piece of the parent's blocked values, NOT*NB words
@@ -375,15 +385,17 @@ fwd_mma_kernel(const __grid_constant__ AttnParams p) {
 #pragma unroll
             for (int rr = 0; rr < NR; ++rr) {
                 float m = fmaxf(fmaxf(s[rr][0], s[rr][1]), fmaxf(s[rr][2], s[rr][3]));
-                m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
-                m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+                m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));     // (a quad-masked redux.sync measured far slower than the two
+                m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));     // shuffles: 176 ms against 98 ms per launch)
                 mr[rr] = m;
             }
             m_true[0] = fmaxf(m_true[0], mr[0]); m_true[1] = fmaxf(m_true[1], mr[1]);
             if (__any_sync(0xffffffffu, mr[0] > m_run[0] + kLazyMax || mr[1] > m_run[1] + kLazyMax)) {
                 const float n0 = fmaxf(m_run[0], mr[0]), n1 = fmaxf(m_run[1], mr[1]);
-                const float a0 = __expf(m_run[0] - n0), a1 = __expf(m_run[1] - n1);
+                const float a0 = X3 ? __expf(m_run[0] - n0) : ex2_approx(m_run2[0] - n0 * kLog2e);
+                const float a1 = X3 ? __expf(m_run[1] - n1) : ex2_approx(m_run2[1] - n1 * kLog2e);
                 m_run[0] = n0; m_run[1] = n1;
+                m_run2[0] = n0 * kLog2e; m_run2[1] = n1 * kLog2e;
                 s_run[0] *= a0; s_run[1] *= a1;
 #pragma unroll
                 for (int i = 0; i < NOT; ++i) {
@@ -396,7 +408,10 @@ fwd_mma_kernel(const __grid_constant__ AttnParams p) {
             for (int rr = 0; rr < NR; ++rr)
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
-                    pr[rr][c] = __expf(s[rr][c] - m_run[rr]);
+                    // exp(s - m_run); 16-bit storage: one multiply-add and the hardware 2^x against the reference kept in
+                    // units of log 2 (its rounding, 1e-6 relative, is common to a row but not to a re-based sum: fp32 storage
+                    // keeps the plain form)
+                    pr[rr][c] = X3 ? __expf(s[rr][c] - m_run[rr]) : ex2_approx(fmaf(s[rr][c], kLog2e, -m_run2[rr]));
                     s_run[rr] += pr[rr][c];
                 }
             // output tile w, column c <-> value column VB*c + w (the blocked layout is built for exactly this mapping);
@@ -426,6 +441,9 @@ fwd_mma_kernel(const __grid_constant__ AttnParams p) {
         };
 
         if (l > 0 && kAccumulateKernel) {
+#ifdef HTREE_FWD_KNOCK_LEVEL   // timing experiments only: the accumulation kernel leaves out the levels of this bit mask
+            if (((HTREE_FWD_KNOCK_LEVEL) >> l) & 1) continue;
+#endif
             if (nc > TK) {
                 // kept-candidate bit mask from the two sorted lists: the level's parents and the next level's parents
                 for (int i = lane; i < (nc + 31) / 32; i += 32) selw[i] = 0u;
@@ -476,11 +494,13 @@ fwd_mma_kernel(const __grid_constant__ AttnParams p) {
                     s[1][2] = (cv[2] && row_ok[1]) ? S1[2] : NINF; s[1][3] = (cv[3] && row_ok[1]) ? S1[3] : NINF;
                     float cm = fmaxf(fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[0][2], s[0][3])),
                                      fmaxf(fmaxf(s[1][0], s[1][1]), fmaxf(s[1][2], s[1][3])));
-                    cm = warp_max(cm);
+                    cm = redux_max_f32(cm, 0xffffffffu);
+                    const float cm2 = cm * kLog2e;
                     float e[4];
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {
-                        e[c] = __expf(s[0][c] - cm) + (NR == 2 ? __expf(s[1][c] - cm) : 0.f);
+                        if constexpr (X3) e[c] = __expf(s[0][c] - cm) + (NR == 2 ? __expf(s[1][c] - cm) : 0.f);
+                        else e[c] = ex2_approx(fmaf(s[0][c], kLog2e, -cm2)) + (NR == 2 ? ex2_approx(fmaf(s[1][c], kLog2e, -cm2)) : 0.f);
                         e[c] += __shfl_xor_sync(0xffffffffu, e[c], 4);
                         e[c] += __shfl_xor_sync(0xffffffffu, e[c], 8);
                         e[c] += __shfl_xor_sync(0xffffffffu, e[c], 16);

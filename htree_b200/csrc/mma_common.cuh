@@ -40,6 +40,21 @@ template <> struct Frag<__half> {
     }
 };
 
+// Maximum over the lanes of `members` in one instruction: redux.sync on fp32 is an sm_100a addition.  Use it with the
+// full-warp mask: with a different mask per quad it measured several times slower than two shuffles.
+__device__ __forceinline__ float redux_max_f32(float x, uint32_t members) {
+    float y;
+    asm volatile("redux.sync.max.f32 %0, %1, %2;" : "=f"(y) : "f"(x), "r"(members));
+    return y;
+}
+// 2^x, the hardware approximation (what __expf evaluates after its multiply by log2 e)
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+constexpr float kLog2e = 1.4426950408889634f;
+
 // Packed fp32 arithmetic of sm_100 (two IEEE round-to-nearest operations per instruction): the fp32 query rotation of the
 // pass that decides the Top-K is the largest block of scalar work in the selection kernel.
 __device__ __forceinline__ float2 fmul2(float2 a, float2 b) {
