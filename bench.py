@@ -51,6 +51,10 @@ NCU_TRAFFIC_BYTES_QUARTER_CFG3 = {"forward": (1.080238e9 + 0.194023e9) + (1.4212
 TDT = {"float32": torch.float32, "bfloat16": torch.bfloat16, "float16": torch.float16}
 
 
+def es_bytes(c: dict) -> int:
+    return 4 if c["dtype"] == "float32" else 2
+
+
 def peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -518,6 +522,27 @@ def main():
     bwd_ms = max_over_ranks(statistics.mean(e[1].elapsed_time(e[2]) for e in ev)) if bwd else None
     ht.check_status(dev)
 
+    # ---- the forward's two launches apart: the selection kernel alone (selection-only replay on the step's own tree) ----
+    sel_ms = None
+    if not (seq_mode and world > 1):
+        _, fctx = ht.htree_forward(q, k, v, CR, MTN, TK, _save_for_backward=True)
+
+        def select_only():
+            return hops.recompute_parents(q, fctx["layers_k"], fctx["layers_v"], fctx["cos_cache"], fctx["sin_cache"], CR, TK, MTN,
+                                          fctx["scale"], fctx["layers_k_rot"])
+
+        select_only()
+        torch.cuda.synchronize()
+        s0 = torch.cuda.Event(enable_timing=True); s1 = torch.cuda.Event(enable_timing=True)
+        s0.record()
+        for _ in range(3):
+            select_only()
+        s1.record()
+        torch.cuda.synchronize()
+        sel_ms = max_over_ranks(s0.elapsed_time(s1) / 3)
+        del fctx
+        torch.cuda.empty_cache()
+
     # ---- streaming kernels: mean-pool tree build + key pre-rotation, timed alone (inputs larger than L2) ----
     sa = torch.cuda.Event(enable_timing=True); sb = torch.cuda.Event(enable_timing=True)
     hops.build_tree(k, v, CR, MTN, 10000.0)
@@ -644,6 +669,19 @@ def main():
     if "l2_gather_gbs" in limits:
         limits["forward_gather_gbs"] = roofline["forward_requested_gather_gbs"]
         limits["forward_gather_frac"] = limits["forward_gather_gbs"] / limits["l2_gather_gbs"]
+    if sel_ms is not None and "l2_gather_gbs" in limits and es_bytes(c) == 2 and D == 128 and CR == 16:
+        # bytes the two kernels actually move from L2 per launch: the selection kernel gathers a chunk's pre-rotated keys
+        # and reads its two fp32 table rows; the pipelined accumulation kernel copies a chunk's blocked keys, blocked
+        # values and two packed-half table rows into shared memory
+        acc_ms = fwd_ms - tree_ms - sel_ms
+        sel_bytes = cm["selection_chunks"] / world * (CR * D * 2 + 2 * (D // 2) * 4)
+        acc_bytes = cm["accumulation_chunks"] / world * (2 * CR * D * 2 + 2 * (D // 2) * 2)
+        limits["selection_kernel_ms"] = sel_ms
+        limits["accumulation_kernel_ms"] = acc_ms
+        limits["selection_kernel_l2_gbs"] = sel_bytes / (sel_ms * 1e-3) / 1e9
+        limits["accumulation_kernel_l2_gbs"] = acc_bytes / (acc_ms * 1e-3) / 1e9
+        limits["selection_kernel_l2_frac"] = limits["selection_kernel_l2_gbs"] / limits["l2_gather_gbs"]
+        limits["accumulation_kernel_l2_frac"] = limits["accumulation_kernel_l2_gbs"] / limits["l2_gather_gbs"]
     if bwd and "l2_reduction_gbs" in limits:
         red_bytes = cm["accumulated_rows"] * 2 * D * 4 / world
         limits["backward_reduction_gbs"] = red_bytes / (bwd_ms * 1e-3) / 1e9

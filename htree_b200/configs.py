@@ -90,5 +90,11 @@ def cost_model(c: dict) -> dict:
     upper = sum(sizes[1:])
     bytes_fwd = es * B * T * H * 2 * D + 2 * es * B * T * Hkv * 2 * D + 3 * es * B * Hkv * 2 * D * upper + 8 * B * T * H
     gather_fwd = es * B * Hkv * D * (s_nc + s_acc)
+    # chunks (one parent's CR children) a (batch, position, kv head) group visits: the selection kernel scores the upper
+    # levels that have more candidates than top_k; the accumulation kernel visits those again plus the leaves
+    par = -(-nc // CR)
+    sel_chunks = int(sum(par[l][nc[l] > TK].sum() for l in range(1, L)))
+    acc_chunks = sel_chunks + int(par[0].sum())
     return dict(levels=sizes, flops_fwd=f_fwd, flops_bwd=f_bwd, bytes_fwd=bytes_fwd, gather_bytes_fwd=gather_fwd,
-                scored_rows=s_nc * B * Hkv, accumulated_rows=s_acc * B * Hkv)
+                scored_rows=s_nc * B * Hkv, accumulated_rows=s_acc * B * Hkv,
+                selection_chunks=sel_chunks * B * Hkv, accumulation_chunks=acc_chunks * B * Hkv)
