@@ -184,6 +184,9 @@ fwd_mma_kernel(const __grid_constant__ AttnParams p) {
             for (int i = 0; i < NSTG; ++i) mbar_init(&bars[i], 1);
             fence_barrier_init();
         }
+#ifdef HTREE_FWD_KNOCK_ALLCOPY
+        for (uint32_t i = lane * 16u; i < (uint32_t)NSTG * SLOT; i += 512u) *reinterpret_cast<uint4*>(ring + i) = make_uint4(0u, 0u, 0u, 0u);
+#endif
         __syncwarp();
     }
     auto pipe_issue = [&](uint32_t n, int a) {       // lane 0: start the copies for the chunk at parent slot a into ring slot n % NSTG
@@ -191,6 +194,9 @@ fwd_mma_kernel(const __grid_constant__ AttnParams p) {
         if (pb < 0 || pb >= blk_count) pb = 0;       // flagged where the chunk is consumed
         const int sl = (int)(n % NSTG);
         unsigned char* dst = ring + (size_t)sl * SLOT;
+#ifdef HTREE_FWD_KNOCK_ALLCOPY   // timing experiments only: no copies and no waits, the kernels compute on a zero-filled ring
+        return;
+#endif
 #ifdef HTREE_FWD_KNOCK_KCOPY   // timing experiments only: upper-level chunks of the accumulation kernel bring their values alone
         if (MODE == 2 && pipe_level > 0) {
             mbar_arrive_expect_tx(&bars[sl], 4096u);
@@ -235,7 +241,9 @@ fwd_mma_kernel(const __grid_constant__ AttnParams p) {
             pissued = pn + NSTG;
         }
         const int sl = (int)(pn % NSTG);
+#ifndef HTREE_FWD_KNOCK_ALLCOPY
         if (!mbar_wait_bounded(&bars[sl], (pn / NSTG) & 1u, kPipeWaitCap)) { pipe_abort(); return nullptr; }
+#endif
         ++pn;
         return ring + (size_t)sl * SLOT;
     };
