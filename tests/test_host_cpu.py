@@ -56,3 +56,30 @@ def test_backward_refuses_an_output_gradient_of_another_dtype():
                num_layers=1, compression_rate=4, top_k_per_layer=2, max_top_nodes=8, scale=0.25, cos_cache=None, sin_cache=None)
     with pytest.raises(ValueError, match="dtype"):
         ops.htree_backward(torch.zeros(1, 4, 2, 16), q, q, ctx)
+
+
+def test_cost_model_chunk_counts_match_a_walk_over_every_query():
+    """The bytes the bench charges to the forward's two kernels rest on the number of chunks (one parent's children) a
+    group visits; count them position by position for a small shape and compare with the closed form."""
+    from htree_b200 import configs
+    c = dict(B=2, T=3000, H=8, H_kv=2, D=128, CR=16, TK=8, MTN=32, dtype="bfloat16", mode="fwd")
+    cm = configs.cost_model(c)
+    sizes = configs.level_sizes(c["T"], c["CR"], c["MTN"])
+    L, CR, TK = len(sizes), c["CR"], c["TK"]
+    sel = acc = 0
+    for t in range(c["T"]):
+        n_par = min(TK, (t // CR ** (L - 1)) // CR + 1)
+        for l in range(L - 1, -1, -1):
+            nc = (n_par - 1) * CR + (t // CR ** l) % CR + 1
+            chunks = -(-nc // CR)
+            assert chunks == n_par
+            if l > 0:
+                if nc > TK:
+                    sel += chunks
+                    acc += chunks
+                n_par = min(TK, nc)
+            else:
+                acc += chunks
+    groups = c["B"] * c["H_kv"]
+    assert cm["selection_chunks"] == sel * groups
+    assert cm["accumulation_chunks"] == acc * groups
