@@ -123,8 +123,12 @@ __host__ __device__ constexpr int fwd_warps_per_block(int mode, bool pipe, int n
     return pipe ? (mode == 1 ? HTREE_PIPE_SEL_WARPS : (nr == 2 ? HTREE_PIPE_ACC_WARPS_G16 : HTREE_PIPE_ACC_WARPS))
                 : (mode == 1 ? HTREE_SEL_WARPS : HTREE_FWD_WARPS);
 }
-__host__ __device__ constexpr int fwd_blocks_per_sm(int mode, bool pipe, bool x3) {
-    return pipe ? (mode == 1 ? HTREE_PIPE_SEL_BLOCKS : HTREE_PIPE_ACC_BLOCKS) : (mode == 1 ? (x3 ? 3 : HTREE_SEL_MIN_BLOCKS) : HTREE_FWD_MIN_BLOCKS);
+// Selection kernel for groups of 9..16 heads: 3 blocks of 4 warps (152 registers, nothing spilled) measured 49.2 ms against
+// 50.5 ms for 4 blocks (128 registers, the raw query rows spilled and re-read from local memory in every chunk: two thirds
+// of that kernel's L1 wavefronts); groups of at most 8 heads fit 128 registers and keep 4 blocks (cfg4: 140 against 152 ms).
+__host__ __device__ constexpr int fwd_blocks_per_sm(int mode, bool pipe, bool x3, int nr = 1, int d = 64) {
+    return pipe ? (mode == 1 ? HTREE_PIPE_SEL_BLOCKS : HTREE_PIPE_ACC_BLOCKS)
+                : (mode == 1 ? ((x3 || (nr == 2 && d == 128)) ? 3 : HTREE_SEL_MIN_BLOCKS) : HTREE_FWD_MIN_BLOCKS);
 }
 
 // MODE 0: whole forward in one kernel.  MODE 1: selections only (no accumulator state, so far fewer registers and more
@@ -133,7 +137,7 @@ __host__ __device__ constexpr int fwd_blocks_per_sm(int mode, bool pipe, bool x3
 // NR = 1: groups of at most 8 heads (rows g+8 of every fragment are padding and their ALU work is skipped).
 // T = float: split-half products (mma_common.cuh), 64-wide heads; K' and the blocked values then hold a hi and a lo plane.
 template <typename T, int D, bool ROT16, int MODE, int NR, int CR, bool PIPE = false>
-__global__ void __launch_bounds__(fwd_warps_per_block(MODE, PIPE, NR) * 32, fwd_blocks_per_sm(MODE, PIPE, std::is_same<T, float>::value))
+__global__ void __launch_bounds__(fwd_warps_per_block(MODE, PIPE, NR) * 32, fwd_blocks_per_sm(MODE, PIPE, std::is_same<T, float>::value, NR, D))
 fwd_mma_kernel(const __grid_constant__ AttnParams p) {
     constexpr bool X3 = std::is_same<T, float>::value;
     constexpr int MWK = fwd_warps_per_block(MODE, PIPE, NR);   // warps (= queries) per block
