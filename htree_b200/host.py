@@ -95,6 +95,7 @@ def forward_backward_host(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, dO:
     return tuple(outs)
 
 
+EDGE_WINDOWS = 4          # query windows of the first and of the last unit of a call
 WINDOW_TARGET = 8192      # positions per query window of the unit pipeline; a call of n units uses at most ceil(8/n) windows per unit
 
 
@@ -120,8 +121,12 @@ def _by_units(q, k, v, dO, outs, dev, streams, compression_rate, max_top_nodes, 
     bwd = dO is not None
     if scale is None:
         scale = K ** -0.5
-    # windows shorten the exposed first upload / last download but cost launch tails; they pay when a call has few units
-    windows = _t_chunks(T, most=max(1, min(8, -(-8 // (B * H_kv)))))
+    # windows shorten the exposed first upload / last download but cost launch tails: every unit is windowed when a call
+    # has few units, otherwise only the first and the last one (whose upload / download nothing else hides)
+    n_units = B * H_kv
+    most_all = max(1, min(8, -(-8 // n_units)))
+    windows_all = _t_chunks(T, most=most_all)
+    windows_edge = _t_chunks(T, most=max(most_all, EDGE_WINDOWS))
     keep = []
 
     def held(ts):
@@ -146,6 +151,7 @@ def _by_units(q, k, v, dO, outs, dev, streams, compression_rate, max_top_nodes, 
                     layers = ops.build_tree(k_d, v_d, compression_rate, max_top_nodes, rope_base)
                 held([k_d, v_d] + [x for lv in layers if lv is not None for x in lv])
                 acc = {}
+                windows = windows_edge if b * H_kv + hk in (0, n_units - 1) else windows_all
                 for wi, (t0, t1) in enumerate(windows):
                     first, last = wi == 0, wi == len(windows) - 1
                     with torch.cuda.stream(s_in):

@@ -464,14 +464,19 @@ def test_host_buffer_pipeline_by_units():
     assert torch.equal(o2, out.cpu())
 
 
-def test_host_buffer_pipeline_with_query_windows(monkeypatch):
+@pytest.mark.parametrize("B,target", [(1, 512), (3, 256)])
+def test_host_buffer_pipeline_with_query_windows(monkeypatch, B, target):
     """The unit pipeline cuts long sequences into query windows (forward per window, backward accumulating dK/dV across
-    windows); forced here on a short sequence: three windows per unit, same results as the device calls."""
+    windows); forced here on a short sequence: three windows per unit with 2 units; with 6 units four windows in the first
+    and the last unit and two in the others.  Same results as the device calls."""
     ops = _ops()
     from htree_b200 import host
-    monkeypatch.setattr(host, "WINDOW_TARGET", 512)
-    c = dict(B=1, T=1700, H=16, H_kv=2, K=128, V=128, CR=16, TK=16, MTN=64, dtype="bfloat16", seed=64)    # 2 units: up to 4 windows each
-    assert len(host._t_chunks(c["T"], most=4)) == 3
+    monkeypatch.setattr(host, "WINDOW_TARGET", target)
+    c = dict(B=B, T=1700, H=16, H_kv=2, K=128, V=128, CR=16, TK=16, MTN=64, dtype="bfloat16", seed=64)
+    if B == 1:
+        assert len(host._t_chunks(c["T"], most=4)) == 3
+    else:
+        assert len(host._t_chunks(c["T"], most=2)) == 2 and len(host._t_chunks(c["T"], most=host.EDGE_WINDOWS)) == 4
     q, k, v, dO = parity.case_inputs(c)
     hq, hk, hv, hd = (x.pin_memory() for x in (q, k, v, dO))
     out_h, dq_h, dk_h, dv_h = host.forward_backward_host(hq, hk, hv, hd, c["CR"], c["MTN"], c["TK"], chunk="unit")
