@@ -612,11 +612,28 @@ def main():
             ev_l[2].record()
             barrier()
             up_ms = max_over_ranks(ev_l[0].elapsed_time(ev_l[1])); down_ms = max_over_ranks(ev_l[1].elapsed_time(ev_l[2]))
+            # both directions at once (uploads on a second stream), as the pipeline runs them
+            side = torch.cuda.Stream(dev)
+            ev_d = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+            barrier()
+            side.wait_stream(torch.cuda.current_stream(dev))
+            ev_d[0].record()
+            with torch.cuda.stream(side):
+                for d_, h_ in zip(dev_in, host_in):
+                    d_.copy_(h_, non_blocking=True)
+            for d_, h_ in zip(dev_out, host_out):
+                h_.copy_(d_, non_blocking=True)
+            torch.cuda.current_stream(dev).wait_stream(side)
+            ev_d[1].record()
+            barrier()
+            both_ms = max_over_ranks(ev_d[0].elapsed_time(ev_d[1]))
             bytes_in = sum(h.numel() * h.element_size() for h in host_in)
             bytes_out = sum(h.numel() * h.element_size() for h in host_out)
             link = {"h2d_ms_all_ranks_at_once": up_ms, "d2h_ms_all_ranks_at_once": down_ms,
+                    "both_directions_ms_all_ranks_at_once": both_ms,
                     "h2d_gbs_per_rank": bytes_in / (up_ms * 1e-3) / 1e9, "d2h_gbs_per_rank": bytes_out / (down_ms * 1e-3) / 1e9,
-                    "note": "contiguous copies of this rank's pinned tensors, one direction at a time; max over ranks"}
+                    "note": "contiguous copies of this rank's pinned tensors, one direction at a time and both at once; max over ranks; "
+                            "a step cannot be shorter than the both-directions time"}
             del dev_in, dev_out
         except Exception as e:
             link = {"error": f"{type(e).__name__}: {e}"[:200]}
