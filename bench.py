@@ -386,6 +386,8 @@ def main():
                     help="units: (batch, kv head) round-robin; sequence: query positions split, pooled levels all-gathered "
                          "(forward-only workloads); auto = sequence for cfg4, units otherwise")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--bind-host", action="store_true",
+                    help="end-to-end leg: keep this rank on the CPUs next to its GPU before it allocates its pinned host buffers")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-workloads", action="store_true", help="skip the other configurations / mode B / Triton legs")
     ap.add_argument("--no-triton", action="store_true")
@@ -558,6 +560,8 @@ def main():
     # ---- end-to-end timing with host buffers ----
     e2e = None
     if not args.no_e2e:
+        from htree_b200 import host as hhost
+        affinity = hhost.bind_host_to_device(dev) if args.bind_host else None
         host_in = [x.cpu().pin_memory() for x in ((q, k, v, dO) if bwd else (q, k, v))]
         outs = step(q, k, v, dO)
         host_out = [torch.empty(o.shape, dtype=tdt, pin_memory=True) for o in outs]
@@ -638,6 +642,7 @@ def main():
         except Exception as e:
             link = {"error": f"{type(e).__name__}: {e}"[:200]}
         e2e = {"value": B * T / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms, "copy_ceiling": link,
+               "host_affinity": affinity,
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": n_e2e,
                "host_tensors": cfg_desc.get("tensors"),
                "api": ("htree_forward_sequence_parallel with pinned host tensors copied in and out around the call" if seq_mode

@@ -25,6 +25,42 @@ def _streams(dev):
     return _stream_cache[key]
 
 
+def bind_host_to_device(device) -> Optional[dict]:
+    """Restrict the calling process to the CPUs next to `device` (the `local_cpulist` of its PCI function in sysfs), so
+    that host memory it allocates and first touches afterwards - pinned staging buffers above all - lands on the NUMA
+    node the GPU hangs off.  With several ranks per host, copies from the far node share the inter-socket link.
+    Returns {"cpus": n, "numa_node": k} or None where the information is not available; never raises."""
+    import os
+    try:
+        dev = torch.device(device)
+        idx = dev.index if dev.index is not None else torch.cuda.current_device()
+        pr = torch.cuda.get_device_properties(idx)
+        bdf = f"{pr.pci_domain_id:04x}:{pr.pci_bus_id:02x}:{pr.pci_device_id:02x}.0"
+        base = f"/sys/bus/pci/devices/{bdf}"
+        with open(base + "/local_cpulist") as f:
+            spec = f.read().strip()
+        cpus = set()
+        for part in spec.split(","):
+            if "-" in part:
+                a, b = part.split("-")
+                cpus.update(range(int(a), int(b) + 1))
+            elif part:
+                cpus.add(int(part))
+        cpus &= os.sched_getaffinity(0)
+        if not cpus:
+            return None
+        os.sched_setaffinity(0, cpus)
+        node = None
+        try:
+            with open(base + "/numa_node") as f:
+                node = int(f.read().strip())
+        except (OSError, ValueError):
+            pass
+        return {"cpus": len(cpus), "numa_node": node}
+    except Exception:
+        return None
+
+
 def _copy_unit(dst: torch.Tensor, src: torch.Tensor, stream) -> None:
     """dst <- src for two views of shape [1, T, heads, D] whose rows (one position: heads * D elements) are contiguous;
     either side may be a slice of a larger [B, T, H, D] tensor (rows a fixed pitch apart) in pinned host memory."""

@@ -83,3 +83,14 @@ def test_cost_model_chunk_counts_match_a_walk_over_every_query():
     groups = c["B"] * c["H_kv"]
     assert cm["selection_chunks"] == sel * groups
     assert cm["accumulation_chunks"] == acc * groups
+
+
+def test_binding_the_host_side_to_a_device_never_raises():
+    """Without a GPU (or without the sysfs entries) the helper reports None and leaves the affinity alone."""
+    from htree_b200 import host
+    before = os.sched_getaffinity(0)
+    got = host.bind_host_to_device("cuda:0")
+    assert got is None or (isinstance(got, dict) and got["cpus"] >= 1)
+    if got is None:
+        assert os.sched_getaffinity(0) == before
+    os.sched_setaffinity(0, before)
