@@ -44,9 +44,9 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 # DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum per launch, one ncu capture) of the attention kernels on
 # the default workload at a quarter of the sequence length (B=4, T=16384).  DRAM traffic grows in proportion to the number
 # of (batch, position, kv head) groups, so the bench scales the figure by the ratio of groups.
-NCU_TRAFFIC_BYTES_QUARTER_CFG3 = {"forward": (1.081671e9 + 0.194856e9) + (1.423364e9 + 1.075061e9),   # selection + accumulation
-                                  "backward": 3.928440e9 + 2.411605e9,
-                                  "capture": "kernels as of commit 3db4721"}
+NCU_TRAFFIC_BYTES_QUARTER_CFG3 = {"forward": (1.081223e9 + 0.191851e9) + (1.419880e9 + 1.077576e9),   # selection + accumulation
+                                  "backward": 3.929301e9 + 2.410741e9,
+                                  "capture": "kernels as of commit b82f34d"}
 
 TDT = {"float32": torch.float32, "bfloat16": torch.bfloat16, "float16": torch.float16}
 
